@@ -1,0 +1,125 @@
+// Output stage shared by the tensor-core kernel, the split-K reduction and the SIMT kernels.
+// Order of operations follows the reference's GEMM epilogue
+// (kernels/sass/hgemm_common_128x128.sass:183-272, documented at nervanagpu/nervanagpu.py:960-965):
+//   c = acc * alpha;  c = relu ? max(c, 0) : c;  c += beta * C_old;  round.
+#pragma once
+#include "common.cuh"
+
+namespace ngb {
+
+struct EpiArgs {
+  float alpha, beta;
+  int relu;
+  int sr_bits;
+  uint32_t seed_lo, seed_hi, rng_offset;
+};
+
+// Random bits for the 8 consecutive outputs that start at linear element index e8*8.
+// One Philox block serves 8 elements (16 bits each); formats that keep fewer than 7 mantissa
+// bits need more than 16 random bits, so a second block is drawn for them.
+__device__ __forceinline__ void sr_bits8(const EpiArgs& e, unsigned long long e8, uint32_t (&rnd)[8]) {
+  const Philox4 a = philox4x32_10(static_cast<uint32_t>(e8), static_cast<uint32_t>(e8 >> 32), e.rng_offset, 0u,
+                                  e.seed_lo, e.seed_hi);
+  if (e.sr_bits >= 7) {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rnd[2 * i] = a.v[i] & 0xffffu;
+      rnd[2 * i + 1] = a.v[i] >> 16;
+    }
+  } else {
+    const Philox4 b = philox4x32_10(static_cast<uint32_t>(e8), static_cast<uint32_t>(e8 >> 32), e.rng_offset, 1u,
+                                    e.seed_lo, e.seed_hi);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      rnd[i] = a.v[i];
+      rnd[4 + i] = b.v[i];
+    }
+  }
+}
+
+__device__ __forceinline__ float epi_scale(const EpiArgs& e, float acc) {
+  float c = acc * e.alpha;
+  if (e.relu) c = fmaxf(c, 0.0f);
+  return c;
+}
+
+// Finish 8 consecutive outputs of one row. `v` holds raw accumulators. `lin` is the logical
+// linear index of the first element (multiple of 8 when vec is true). `nvalid` <= 8.
+template <bool F32OUT>
+__device__ __forceinline__ void epi_store8(const EpiArgs& e, float (&v)[8], void* crow, const void* oldrow,
+                                           int col, unsigned long long lin, int nvalid, bool vec) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = epi_scale(e, v[i]);
+
+  if (F32OUT) {
+    float* out = static_cast<float*>(crow) + col;
+    if (e.beta != 0.0f) {
+      const float* old = static_cast<const float*>(oldrow) + col;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < nvalid) v[i] = fmaf(e.beta, old[i], v[i]);
+    }
+    if (vec && nvalid == 8) {
+      reinterpret_cast<float4*>(out)[0] = make_float4(v[0], v[1], v[2], v[3]);
+      reinterpret_cast<float4*>(out)[1] = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < nvalid) out[i] = v[i];
+    }
+    return;
+  }
+
+  __half* out = static_cast<__half*>(crow) + col;
+  if (e.beta != 0.0f) {
+    const __half* old = static_cast<const __half*>(oldrow) + col;
+    if (vec && nvalid == 8) {
+      const uint4 o = *reinterpret_cast<const uint4*>(old);
+      const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const float2 f = __half22float2(oh[i]);
+        v[2 * i] = fmaf(e.beta, f.x, v[2 * i]);
+        v[2 * i + 1] = fmaf(e.beta, f.y, v[2 * i + 1]);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (i < nvalid) v[i] = fmaf(e.beta, __half2float(old[i]), v[i]);
+    }
+  }
+  __half h[8];
+  if (e.sr_bits) {
+    uint32_t rnd[8];
+    // ragged rows can start a group off an 8-boundary: draw per element then (rare, slow path)
+    if ((lin & 7ull) == 0ull) {
+      sr_bits8(e, lin >> 3, rnd);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) h[i] = f2h_sr(v[i], rnd[i], e.sr_bits);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        uint32_t r8[8];
+        const unsigned long long li = lin + i;
+        sr_bits8(e, li >> 3, r8);
+        h[i] = f2h_sr(v[i], r8[li & 7ull], e.sr_bits);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = f2h_rn(v[i]);
+  }
+  if (vec && nvalid == 8) {
+    uint4 o;
+    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __halves2half2(h[2 * i], h[2 * i + 1]);
+    *reinterpret_cast<uint4*>(out) = o;
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (i < nvalid) out[i] = h[i];
+  }
+}
+
+}  // namespace ngb

@@ -1,0 +1,54 @@
+// Host-side internals shared by the translation units of libnervana_b200.so.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+#include "igemm_tc.cuh"
+#include "status.h"
+
+namespace ngb {
+
+// Per-device state owned by the library: SM count, device status word, split-K workspace.
+struct DeviceCtx {
+  int device = -1;
+  int sm_count = 0;
+  int* status = nullptr;     // device int written by kernels whose bounded wait gave up
+  float* ws = nullptr;       // split-K / conv scratch, grown on demand
+  size_t ws_bytes = 0;
+  bool smem_attr_set = false;
+};
+
+// Error reporting: returns `code` after storing a printf-style message for ng_last_error().
+int fail(int code, const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define NG_CUDA(expr)                                        \
+  do {                                                       \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return ::ngb::cuda_fail(_e, #expr); \
+  } while (0)
+
+// Context of the current device (initialised on first use). Null + error set on failure.
+DeviceCtx* current_ctx();
+// Ensure the workspace holds at least `bytes`; may synchronise the device when it has to grow.
+int ensure_workspace(DeviceCtx* c, size_t bytes);
+
+// Rank-5 tiled tensor map over fp16 (elem_bytes 2) data. dims[0] is the contiguous dimension;
+// strides_bytes[i] is the byte stride of dims[i+1]. Swizzle is chosen from the inner box width.
+int make_tensor_map(CUtensorMap* out, const void* base, const uint64_t dims[5], const uint64_t strides_bytes[4],
+                    const uint32_t box[5], int elem_bytes = 2);
+
+// Fill the MMA/ring fields of a parameter block and launch the tensor-core kernel (+ split-K reduce).
+struct TcOperandLayout {
+  int a_mn_major, b_mn_major;
+  int kb_rows;   // reduction rows per k-block
+};
+void tc_fill_mma(TcParams& p, const TcOperandLayout& lay);
+int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream);
+
+// Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
+int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems);
+
+}  // namespace ngb

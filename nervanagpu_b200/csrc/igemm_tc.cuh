@@ -1,0 +1,68 @@
+// Parameter block of the tcgen05 implicit-GEMM engine (one kernel serves ng.dot and the
+// three convolution passes; they differ in how the TMA producer turns a k-block into box
+// coordinates and in how work items map onto output tiles).
+#pragma once
+#include <stdint.h>
+
+namespace ngb {
+
+enum TcMode : int { TC_GEMM = 0, TC_FPROP = 1, TC_BPROP = 2, TC_UPDATE = 3 };
+
+constexpr int kTileM = 128;        // UMMA M (TMEM lanes)
+constexpr int kChunk = 64;         // fp16 elements per 128-byte swizzle row
+constexpr int kMaxStages = 8;
+constexpr int kTcThreads = 192;    // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+
+struct TcParams {
+  // ---- work decomposition: item = ((split * nz + z) * tiles_n + tile_n) * tiles_m + tile_m
+  int tiles_m, tiles_n, nz, splits;
+  int num_kb;          // k-blocks in the whole reduction
+  int kb_per_split;    // ceil(num_kb / splits)
+  int block_n;         // UMMA N: 64, 128 or 256
+  int M, N;            // logical output extent (rows, cols)
+
+  // ---- MMA descriptors (host-built)
+  uint32_t idesc;
+  uint32_t a_desc_lo, a_desc_hi;   // lo: LBO field only; start address is or-ed in per stage
+  uint32_t b_desc_lo, b_desc_hi;
+  uint32_t a_kstep, b_kstep;       // start-address increment (16-byte units) per K=16 MMA
+  int mma_per_kb;                  // kb_rows / 16
+
+  // ---- shared-memory ring
+  int stages;
+  uint32_t stage_bytes;            // bytes landed per stage (= expect_tx)
+  uint32_t a_bytes;                // B region starts at this offset inside a stage
+  int a_boxes, b_boxes;            // TMA boxes per stage per operand
+  uint32_t a_box_bytes, b_box_bytes;
+
+  // ---- producer
+  int mode;
+  int a_mn_major, b_mn_major;
+  int kb_rows;                     // reduction rows per k-block (64, or 16..64 for small C in fprop)
+  int a_zmul, b_zmul;              // batched GEMM: coordinate in dim 2 = z * zmul
+  // conv geometry (unused by TC_GEMM)
+  int red_chunks;                  // fprop: ceil(C/kb_rows); bprop: ceil(K/64)
+  int RS, S;                       // filter taps
+  int pad_d, pad_h, pad_w;
+  int str_d, str_h, str_w;
+  int inner_tap;                   // N in flattened-(W,N) mode else 0
+  int x_tap;                       // 0 in flattened mode else 1
+  int dec_cpi, dec_q, dec_p, dec_m;  // chunk decode of the pixel space the chunks walk
+  int oob_y;                       // a y/p coordinate that is out of range (forces zero fill)
+
+  // ---- epilogue
+  void* C;                         // fp16 or fp32 output
+  const void* Cold;                // source of the beta term (same type/shape as C) or null
+  long long ldc;                   // elements
+  long long c_zstride;             // elements, per z
+  float alpha, beta;
+  int relu;
+  int sr_bits;                     // 0 = round to nearest even, else mantissa bits kept
+  int out_f32;
+  int vec_ok;                      // rows are 16-byte aligned for vector access
+  uint32_t seed_lo, seed_hi, rng_offset;
+  float* ws;                       // split-K partials [split][z][M][N] when splits > 1
+  int* status;                     // device status word
+};
+
+}  // namespace ngb

@@ -1,0 +1,393 @@
+// tcgen05 / TMEM / TMA implicit-GEMM engine for sm_100a.
+//
+// One persistent, warp-specialised kernel computes D[M x N] = A[M x Kred] * B[Kred x N] with fp16
+// operands staged in 128-byte-swizzled shared memory by TMA, fp32 accumulation in tensor memory
+// and a fused epilogue (alpha, ReLU, beta*C, round-to-nearest or stochastic rounding, fp16 or
+// fp32 store, or raw fp32 split-K partials).
+//
+//   warp 0      TMA producer: up to six lanes each issue one box per k-block
+//   warp 1      allocates TMEM, one lane issues tcgen05.mma and the commits
+//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, convert, store
+//
+// The accumulator is double-buffered in TMEM (2 x block_n columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.  All waits are bounded (see mbar_wait).
+//
+// It replaces the reference's register-tiled FFMA kernels: hgemm_{nn,nt,tn}_* for ng.dot
+// (nervanagpu/nervanagpu.py:959-1105), hconv_fprop_K64_N64, hconv_bprop_C64_N64/C32_N64 and
+// hconv_updat_C128_K64/K128 for the convolution passes (nervanagpu/nervanagpu.py:642-734).
+#pragma once
+#include "igemm_tc.cuh"
+
+#include "common.cuh"
+#include "epilogue.cuh"
+
+namespace ngb {
+
+namespace {
+
+struct ChunkPos {
+  int inner0, q, p, m;
+  bool valid;
+};
+
+// Position of 64-element chunk `chunk` in a (m, p, q, n) pixel space. In flattened mode the
+// (q, n) pair is one dimension of extent Q*N and dec_q == 1.
+__device__ __forceinline__ ChunkPos decode_chunk(const TcParams& p, int chunk) {
+  ChunkPos c;
+  const int g = chunk / p.dec_cpi;
+  c.inner0 = (chunk - g * p.dec_cpi) * kChunk;
+  const int g2 = g / p.dec_q;
+  c.q = g - g2 * p.dec_q;
+  c.m = g2 / p.dec_p;
+  c.p = g2 - c.m * p.dec_p;
+  c.valid = c.m < p.dec_m;
+  return c;
+}
+
+struct Tap {
+  int t, r, s;
+};
+__device__ __forceinline__ Tap decode_tap(const TcParams& p, int trs) {
+  Tap tp;
+  tp.t = trs / p.RS;
+  const int rs = trs - tp.t * p.RS;
+  tp.r = rs / p.S;
+  tp.s = rs - tp.r * p.S;
+  return tp;
+}
+
+// Exact division for the strided gather of the backward pass: returns false when `num` is not
+// a multiple of `den` (that tap does not touch this pixel).
+__device__ __forceinline__ bool div_exact(int num, int den, int& out) {
+  if (den == 1) {
+    out = num;
+    return true;
+  }
+  if (num < 0) {
+    out = -1;  // out of range either way
+    return true;
+  }
+  out = num / den;
+  return out * den == num;
+}
+
+struct WorkItem {
+  int tile_m, tile_n, z, split, kb0, kb1;
+};
+__device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
+  WorkItem it;
+  it.tile_m = w % p.tiles_m;
+  int r = w / p.tiles_m;
+  it.tile_n = r % p.tiles_n;
+  r /= p.tiles_n;
+  it.z = r % p.nz;
+  it.split = r / p.nz;
+  it.kb0 = it.split * p.kb_per_split;
+  it.kb1 = min(p.num_kb, it.kb0 + p.kb_per_split);
+  return it;
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(kTcThreads, 1)
+igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
+                const __grid_constant__ TcParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // ring buffer must be 1024-byte aligned for the 128-byte swizzle pattern
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
+  const uint32_t ring_bytes = static_cast<uint32_t>(p.stages) * p.stage_bytes;
+
+  // control block after the ring
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + ring_bytes);
+  const uint32_t bar_base = smem_base + ring_bytes;
+  auto full_bar = [&](int s) { return bar_base + 8u * s; };
+  auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
+  auto accf_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
+  auto acce_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + 2 + a); };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * kMaxStages + 4);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total_work = p.tiles_m * p.tiles_n * p.nz * p.splits;
+  const uint32_t tmem_cols = 512;  // 2 accumulators of up to 256 columns
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < p.stages; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(accf_bar(a), 1);
+      mbar_init(acce_bar(a), 4);
+    }
+    *abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 0 && lane == 0) {
+    tma_prefetch_desc(&mapA);
+    tma_prefetch_desc(&mapB);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // =========================== TMA producer ===========================
+    const int nboxes = p.a_boxes + p.b_boxes;
+    const bool active = lane < nboxes;
+    const bool is_a = lane < p.a_boxes;
+    const int bi = is_a ? lane : lane - p.a_boxes;
+    const CUtensorMap* map = is_a ? &mapA : &mapB;
+    const uint32_t box_off = is_a ? bi * p.a_box_bytes : p.a_bytes + bi * p.b_box_bytes;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      const WorkItem it = decode_work(p, w);
+      const int m0 = it.tile_m * kTileM;
+      const int n0 = it.tile_n * p.block_n;
+      // per-tile state of this lane's box
+      ChunkPos cp = {0, 0, 0, 0, true};
+      Tap ztap = {0, 0, 0};
+      if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
+        if (!is_a) cp = decode_chunk(p, n0 / kChunk + bi);
+      } else if (p.mode == TC_UPDATE) {
+        ztap = decode_tap(p, it.z);
+      }
+      for (int kb = it.kb0; kb < it.kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(full_bar(stage), p.stage_bytes);
+        __syncwarp();
+        if (active) {
+          int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
+          if (p.mode == TC_GEMM) {
+            const int k0 = kb * kChunk;
+            if (is_a) {
+              if (p.a_mn_major) { c0 = m0 + kChunk * bi; c1 = k0; } else { c0 = k0; c1 = m0; }
+              c2 = it.z * p.a_zmul;
+            } else {
+              if (p.b_mn_major) { c0 = n0 + kChunk * bi; c1 = k0; } else { c0 = k0; c1 = n0; }
+              c2 = it.z * p.b_zmul;
+            }
+          } else if (p.mode == TC_FPROP) {
+            const int trs = kb / p.red_chunks;
+            const int cc = kb - trs * p.red_chunks;
+            if (is_a) {  // filter rows c of tap trs, 64 output channels wide
+              c0 = m0 + kChunk * bi; c1 = trs; c2 = cc * p.kb_rows;
+            } else {     // input pixels of this chunk shifted by the tap
+              const Tap tp = decode_tap(p, trs);
+              c0 = cp.inner0 + (tp.s - p.pad_w) * p.inner_tap;
+              c1 = (cp.q * p.str_w - p.pad_w + tp.s) * p.x_tap;
+              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tp.r : p.oob_y;
+              c3 = cp.m * p.str_d - p.pad_d + tp.t;
+              c4 = cc * p.kb_rows;
+            }
+          } else if (p.mode == TC_BPROP) {
+            const int trs = kb / p.red_chunks;
+            const int kc = kb - trs * p.red_chunks;
+            if (is_a) {  // filter rows c0.., 64 output channels k of tap trs
+              c0 = kc * kChunk; c1 = trs; c2 = m0;
+            } else {     // error pixels that reach this input pixel through tap trs
+              const Tap tp = decode_tap(p, trs);
+              bool v = cp.valid;
+              int q = 0, pp = 0, mm = 0;
+              if (p.x_tap) {
+                v &= div_exact(cp.q + p.pad_w - tp.s, p.str_w, q);
+                c0 = cp.inner0;
+              } else {
+                c0 = cp.inner0 + (p.pad_w - tp.s) * p.inner_tap;
+              }
+              v &= div_exact(cp.p + p.pad_h - tp.r, p.str_h, pp);
+              v &= div_exact(cp.m + p.pad_d - tp.t, p.str_d, mm);
+              c1 = q; c2 = v ? pp : p.oob_y; c3 = mm; c4 = kc * kChunk;
+            }
+          } else {  // TC_UPDATE: k-block = one 64-element chunk of the (m,p,q,n) space
+            const ChunkPos ep = decode_chunk(p, kb);
+            if (is_a) {  // input pixels under tap z, 128 channels c
+              c0 = ep.inner0 + (ztap.s - p.pad_w) * p.inner_tap;
+              c1 = (ep.q * p.str_w - p.pad_w + ztap.s) * p.x_tap;
+              c2 = ep.p * p.str_h - p.pad_h + ztap.r;
+              c3 = ep.m * p.str_d - p.pad_d + ztap.t;
+              c4 = m0;
+            } else {     // error pixels, block_n output channels k
+              c0 = ep.inner0; c1 = ep.q * p.x_tap; c2 = ep.p; c3 = ep.m; c4 = n0;
+            }
+          }
+          tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
+        }
+        if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+      }
+    }
+  } else if (warp == 1) {
+    // =========================== MMA issuer ===========================
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int local = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++local) {
+        const WorkItem it = decode_work(p, w);
+        const int acc = local & 1;
+        const uint32_t acc_phase = (local >> 1) & 1u;
+        if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.block_n);
+        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
+          const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
+          for (int k = 0; k < p.mma_per_kb; ++k) {
+            const uint64_t adesc = (static_cast<uint64_t>(p.a_desc_hi) << 32) |
+                                   (p.a_desc_lo | ((sa + k * p.a_kstep) & 0x3fffu));
+            const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
+                                   (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
+            tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, (kb > it.kb0 || k > 0) ? 1u : 0u);
+          }
+          tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs have read it
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (ok) tc_commit(accf_bar(acc));  // accumulator complete
+      }
+    }
+    __syncwarp();
+  } else {
+    // =========================== epilogue ===========================
+    const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) are visible to this warp
+    EpiArgs ea;
+    ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
+    ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
+    EpiArgs raw = ea;  // split-K partials: untouched accumulators
+    raw.alpha = 1.0f; raw.beta = 0.0f; raw.relu = 0; raw.sr_bits = 0;
+    int local = 0;
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++local) {
+      const WorkItem it = decode_work(p, w);
+      const int acc = local & 1;
+      const uint32_t acc_phase = (local >> 1) & 1u;
+      if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
+      tc_fence_after();
+      const int row = it.tile_m * kTileM + lane_group * 32 + lane;
+      const int n0 = it.tile_n * p.block_n;
+      const bool row_ok = row < p.M;
+      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                             static_cast<uint32_t>(acc * p.block_n);
+      const bool partial = p.splits > 1;
+      // row base pointers
+      uint8_t* crow = nullptr;
+      const uint8_t* oldrow = nullptr;
+      unsigned long long lin_row = 0;
+      if (partial) {
+        const long long off = ((static_cast<long long>(it.split) * p.nz + it.z) * p.M + row) * p.N;
+        crow = reinterpret_cast<uint8_t*>(p.ws + off);
+      } else {
+        const long long off = it.z * p.c_zstride + static_cast<long long>(row) * p.ldc;
+        const int esz = p.out_f32 ? 4 : 2;
+        crow = static_cast<uint8_t*>(p.C) + off * esz;
+        oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
+        lin_row = (static_cast<unsigned long long>(it.z) * p.M + row) * static_cast<unsigned long long>(p.N);
+      }
+      for (int c = 0; c < p.block_n / 32; ++c) {
+        uint32_t r[32];
+        tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
+        tc_wait_ld();
+        const int col0 = n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int col = col0 + g * 8;
+            const int nvalid = min(8, p.N - col);
+            if (nvalid <= 0) break;
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+            if (partial) {
+              epi_store8<true>(raw, v, crow, nullptr, col, 0ull, nvalid, (p.N & 3) == 0);
+            } else if (p.out_f32) {
+              epi_store8<true>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+            } else {
+              epi_store8<false>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acce_bar(acc));
+    }
+  }
+
+  // =========================== teardown ===========================
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a wait gave up: give copies that may still be in flight time to land before the
+    // shared memory and TMEM are handed back
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, tmem_cols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// split-K second stage: sum the partials in fixed order, then the fused epilogue.
+// One thread finishes 8 consecutive columns of one row.
+// ------------------------------------------------------------------------------------------
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int nz, int M, int N, void* C,
+                                     const void* Cold, long long ldc, long long c_zstride, int out_f32,
+                                     int vec_ok, EpiArgs ea) {
+  const int groups_per_row = (N + 7) / 8;
+  const long long total = static_cast<long long>(nz) * M * groups_per_row;
+  const long long slice = static_cast<long long>(nz) * M * N;
+  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int g = static_cast<int>(i % groups_per_row);
+    const long long zr = i / groups_per_row;
+    const int row = static_cast<int>(zr % M);
+    const int z = static_cast<int>(zr / M);
+    const int col = g * 8;
+    const int nvalid = min(8, N - col);
+    float v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+    const float* src = ws + zr * N + col;
+    const bool v4 = (N & 3) == 0 && nvalid == 8;
+    for (int s = 0; s < splits; ++s, src += slice) {
+      if (v4) {
+        const float4 a = reinterpret_cast<const float4*>(src)[0];
+        const float4 b = reinterpret_cast<const float4*>(src)[1];
+        v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
+        v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+      } else {
+        for (int j = 0; j < nvalid; ++j) v[j] += src[j];
+      }
+    }
+    const long long off = z * c_zstride + static_cast<long long>(row) * ldc;
+    const int esz = out_f32 ? 4 : 2;
+    uint8_t* crow = static_cast<uint8_t*>(C) + off * esz;
+    const uint8_t* oldrow = Cold ? static_cast<const uint8_t*>(Cold) + off * esz : nullptr;
+    const unsigned long long lin = (static_cast<unsigned long long>(z) * M + row) * static_cast<unsigned long long>(N) + col;
+    if (out_f32)
+      epi_store8<true>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
+    else
+      epi_store8<false>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
+  }
+}
+
+}  // namespace ngb

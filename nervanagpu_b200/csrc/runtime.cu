@@ -1,0 +1,308 @@
+// Runtime services of the C-ABI: device selection, memory, copies, memsets, streams, events,
+// error strings. They stand in for the PyCUDA calls the reference's host code makes
+// (nervanagpu/nervanagpu.py:133,145,298-311,712-729,1333-1350; nervanagpu/layers.py:775-778).
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+#include <string>
+
+#include "../../include/nervana_b200.h"
+#include "host.h"
+
+namespace ngb {
+
+static thread_local std::string g_last_error;
+
+int fail(int code, const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof(buf), fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return code;
+}
+
+int cuda_fail(cudaError_t e, const char* what) {
+  return fail(NG_ERR_CUDA, "CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
+}
+
+static std::mutex g_ctx_mutex;
+static DeviceCtx g_ctx[64];
+
+DeviceCtx* current_ctx() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaGetDevice");
+    return nullptr;
+  }
+  if (dev < 0 || dev >= 64) {
+    fail(NG_ERR_INVALID_ARG, "device index %d out of range", dev);
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(g_ctx_mutex);
+  DeviceCtx* c = &g_ctx[dev];
+  if (c->device == dev) return c;
+  cudaDeviceProp prop;
+  e = cudaGetDeviceProperties(&prop, dev);
+  if (e != cudaSuccess) {
+    cuda_fail(e, "cudaGetDeviceProperties");
+    return nullptr;
+  }
+  if (prop.major != 10) {
+    fail(NG_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only", dev, prop.major,
+         prop.minor);
+    return nullptr;
+  }
+  e = cudaMalloc(&c->status, sizeof(int));
+  if (e == cudaSuccess) e = cudaMemset(c->status, 0, sizeof(int));
+  if (e != cudaSuccess) {
+    cuda_fail(e, "status word allocation");
+    return nullptr;
+  }
+  c->sm_count = prop.multiProcessorCount;
+  c->device = dev;
+  return c;
+}
+
+int ensure_workspace(DeviceCtx* c, size_t bytes) {
+  if (bytes <= c->ws_bytes) return NG_OK;
+  // growing: earlier launches may still read the old buffer
+  NG_CUDA(cudaDeviceSynchronize());
+  if (c->ws) NG_CUDA(cudaFree(c->ws));
+  c->ws = nullptr;
+  c->ws_bytes = 0;
+  size_t want = bytes + (bytes >> 2);
+  want = (want + (1u << 20) - 1) & ~((size_t(1) << 20) - 1);
+  NG_CUDA(cudaMalloc(&c->ws, want));
+  c->ws_bytes = want;
+  return NG_OK;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+int make_tensor_map(CUtensorMap* out, const void* base, const uint64_t dims[5], const uint64_t strides_bytes[4],
+                    const uint32_t box[5], int elem_bytes) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return fail(NG_ERR_CUDA, "cuTensorMapEncodeTiled entry point not available from the driver");
+  cuuint64_t gdim[5], gstr[4];
+  cuuint32_t bdim[5], estr[5];
+  for (int i = 0; i < 5; ++i) {
+    gdim[i] = dims[i];
+    bdim[i] = box[i];
+    estr[i] = 1;
+  }
+  for (int i = 0; i < 4; ++i) gstr[i] = strides_bytes[i];
+  const uint32_t inner_bytes = box[0] * elem_bytes;
+  CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
+  if (inner_bytes == 128) sw = CU_TENSOR_MAP_SWIZZLE_128B;
+  else if (inner_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;
+  else if (inner_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  CUresult r = fn(out, dt, 5, const_cast<void*>(base), gdim, gstr, bdim, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, sw,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return fail(NG_ERR_CUDA,
+                "cuTensorMapEncodeTiled failed (%d): base=%p dims=(%llu,%llu,%llu,%llu,%llu) strides=(%llu,%llu,%llu,%llu) "
+                "box=(%u,%u,%u,%u,%u)",
+                static_cast<int>(r), base, (unsigned long long)dims[0], (unsigned long long)dims[1],
+                (unsigned long long)dims[2], (unsigned long long)dims[3], (unsigned long long)dims[4],
+                (unsigned long long)strides_bytes[0], (unsigned long long)strides_bytes[1],
+                (unsigned long long)strides_bytes[2], (unsigned long long)strides_bytes[3], box[0], box[1], box[2],
+                box[3], box[4]);
+  return NG_OK;
+}
+
+}  // namespace ngb
+
+using namespace ngb;
+
+namespace {
+template <typename T>
+__global__ void fill_kernel(T* dst, T value, size_t count) {
+  for (size_t i = blockIdx.x * static_cast<size_t>(blockDim.x) + threadIdx.x; i < count;
+       i += static_cast<size_t>(gridDim.x) * blockDim.x)
+    dst[i] = value;
+}
+template <typename T>
+int fill(void* dst, T value, size_t count, void* stream) {
+  if (count == 0) return NG_OK;
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  const int threads = 256;
+  size_t blocks = (count + threads - 1) / threads;
+  const size_t cap = static_cast<size_t>(c->sm_count) * 16;
+  if (blocks > cap) blocks = cap;
+  fill_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<T*>(dst), value, count);
+  NG_CUDA(cudaGetLastError());
+  return NG_OK;
+}
+}  // namespace
+
+extern "C" {
+
+const char* ng_last_error(void) { return g_last_error.c_str(); }
+
+int ng_init(int device) {
+  NG_CUDA(cudaSetDevice(device));
+  return current_ctx() ? NG_OK : NG_ERR_CUDA;
+}
+
+int ng_device_count(int* count) {
+  if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
+  NG_CUDA(cudaGetDeviceCount(count));
+  return NG_OK;
+}
+
+int ng_sm_count(int* count) {
+  if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  *count = c->sm_count;
+  return NG_OK;
+}
+
+int ng_malloc(void** ptr, size_t bytes) {
+  if (!ptr) return fail(NG_ERR_INVALID_ARG, "ptr is null");
+  NG_CUDA(cudaMalloc(ptr, bytes ? bytes : 1));
+  return NG_OK;
+}
+
+int ng_free(void* ptr) {
+  if (ptr) NG_CUDA(cudaFree(ptr));
+  return NG_OK;
+}
+
+int ng_host_alloc(void** ptr, size_t bytes) {
+  if (!ptr) return fail(NG_ERR_INVALID_ARG, "ptr is null");
+  NG_CUDA(cudaHostAlloc(ptr, bytes ? bytes : 1, cudaHostAllocDefault));
+  return NG_OK;
+}
+
+int ng_host_free(void* ptr) {
+  if (ptr) NG_CUDA(cudaFreeHost(ptr));
+  return NG_OK;
+}
+
+int ng_mem_info(size_t* free_bytes, size_t* total_bytes) {
+  NG_CUDA(cudaMemGetInfo(free_bytes, total_bytes));
+  return NG_OK;
+}
+
+int ng_memcpy_h2d_async(void* dst, const void* src, size_t bytes, void* stream) {
+  NG_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyHostToDevice, static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_memcpy_d2h_async(void* dst, const void* src, size_t bytes, void* stream) {
+  NG_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToHost, static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_memcpy_d2d_async(void* dst, const void* src, size_t bytes, void* stream) {
+  NG_CUDA(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_memset_d8_async(void* dst, unsigned char value, size_t count, void* stream) {
+  NG_CUDA(cudaMemsetAsync(dst, value, count, static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+
+int ng_memset_d16_async(void* dst, unsigned short value, size_t count, void* stream) {
+  if (value == 0) return ng_memset_d8_async(dst, 0, count * 2, stream);
+  return fill<unsigned short>(dst, value, count, stream);
+}
+
+int ng_memset_d32_async(void* dst, unsigned int value, size_t count, void* stream) {
+  if (value == 0) return ng_memset_d8_async(dst, 0, count * 4, stream);
+  return fill<unsigned int>(dst, value, count, stream);
+}
+
+int ng_stream_create(void** stream) {
+  cudaStream_t s;
+  NG_CUDA(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking));
+  *stream = s;
+  return NG_OK;
+}
+
+int ng_stream_destroy(void* stream) {
+  NG_CUDA(cudaStreamDestroy(static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_stream_sync(void* stream) {
+  NG_CUDA(cudaStreamSynchronize(static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_stream_wait_event(void* stream, void* event) {
+  NG_CUDA(cudaStreamWaitEvent(static_cast<cudaStream_t>(stream), static_cast<cudaEvent_t>(event), 0));
+  return NG_OK;
+}
+
+int ng_event_create(void** event) {
+  cudaEvent_t e;
+  NG_CUDA(cudaEventCreate(&e));
+  *event = e;
+  return NG_OK;
+}
+
+int ng_event_destroy(void* event) {
+  NG_CUDA(cudaEventDestroy(static_cast<cudaEvent_t>(event)));
+  return NG_OK;
+}
+
+int ng_event_record(void* event, void* stream) {
+  NG_CUDA(cudaEventRecord(static_cast<cudaEvent_t>(event), static_cast<cudaStream_t>(stream)));
+  return NG_OK;
+}
+
+int ng_event_sync(void* event) {
+  NG_CUDA(cudaEventSynchronize(static_cast<cudaEvent_t>(event)));
+  return NG_OK;
+}
+
+int ng_event_elapsed_ms(void* start, void* end, float* ms) {
+  NG_CUDA(cudaEventElapsedTime(ms, static_cast<cudaEvent_t>(start), static_cast<cudaEvent_t>(end)));
+  return NG_OK;
+}
+
+int ng_device_status(int* code) {
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  int v = 0;
+  NG_CUDA(cudaMemcpy(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code) *code = v;
+  if (v != 0) {
+    cudaMemset(c->status, 0, sizeof(int));
+    return fail(NG_ERR_TIMEOUT, "a kernel gave up a bounded wait (site %d)", v);
+  }
+  return NG_OK;
+}
+
+int ng_sync(void) {
+  NG_CUDA(cudaDeviceSynchronize());
+  return ng_device_status(nullptr);
+}
+
+}  // extern "C"
