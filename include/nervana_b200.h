@@ -85,6 +85,110 @@ int ng_hgemm_batched(const void* A, const void* B, void* C, int a_t, int b_t, in
                      unsigned int rng_offset, int batch_grid, int batch_loops, long long ldaz, long long ldbz,
                      long long ldcz, void* stream);
 
+/* ---- convolution ---------------------------------------------------------------------------
+ * Activations are (C,D,H,W,N), filters (C,T,R,S,K), outputs (K,M,P,Q,N), all fp16, N innermost.
+ * The descriptor carries what ConvLayer stores (nervanagpu/layers.py:281-313); output
+ * dimensions are M,P,Q = ceil((X - f + 1 + 2*pad) / stride) (nervanagpu/layers.py:297-301).
+ * N and K must be multiples of 8 (nervanagpu/layers.py:291-292). */
+typedef struct ng_conv_desc {
+  int N, C, K;
+  int D, H, W;
+  int T, R, S;
+  int pad_d, pad_h, pad_w;
+  int str_d, str_h, str_w;
+} ng_conv_desc;
+
+/* Kernel family selector, for tests and benchmarks. AUTO picks the tensor-core path whenever
+ * the shape allows it; the others fail with NG_ERR_UNSUPPORTED rather than switch silently. */
+#define NG_PATH_AUTO 0
+#define NG_PATH_TENSOR 1   /* tcgen05 implicit GEMM fed by TMA */
+#define NG_PATH_SIMT 2     /* plain CUDA-core kernel, any legal shape */
+#define NG_PATH_IM2COL 3   /* update only: im2col buffer + tensor-core GEMM */
+
+int ng_conv_output_dims(const ng_conv_desc* desc, int* M, int* P, int* Q);
+/* O = RN16(relu?(alpha * conv(I, F))). Replaces hconv_fprop_K64_N64 via NervanaGPU.fprop_conv
+ * (nervanagpu/nervanagpu.py:642-650,671-734). */
+int ng_conv_fprop(const ng_conv_desc* desc, const void* I, const void* F, void* O, float alpha, int relu, int path,
+                  void* stream);
+/* gradI = RN16(alpha * conv_transpose(E, F)). Replaces hconv_bprop_C64_N64 / hconv_bprop_C32_N64
+ * and their dimShuffle / transpose + zero-fill pre-passes (nervanagpu/nervanagpu.py:652-659,685-693). */
+int ng_conv_bprop(const ng_conv_desc* desc, const void* F, const void* E, void* gradI, float alpha, int path,
+                  void* stream);
+/* gradF = alpha * sum over (m,p,q,n) of I patches x E; gradF is fp32 (out_f32 = 1, what ConvLayer
+ * uses, nervanagpu/layers.py:289) or fp16. Replaces hconv_updat_C128_K64 / _K128, their zero-fill
+ * and fp32_convert passes (nervanagpu/nervanagpu.py:661-669,695-698,715-724). The summation
+ * order is fixed (split partials in library workspace, then one ordered reduction), unlike the
+ * reference's atomics. */
+int ng_conv_update(const ng_conv_desc* desc, const void* I, const void* E, void* gradF, int out_f32, float alpha,
+                   int path, void* stream);
+
+/* ---- pooling -------------------------------------------------------------------------------
+ * Max pooling over windows (J,T,R,S) of (C,D,H,W); what PoolLayer stores
+ * (nervanagpu/layers.py:542-584). K,M,P,Q = ceil((X - f + 1 + 2*pad) / stride). */
+typedef struct ng_pool_desc {
+  int N, C;
+  int D, H, W;
+  int J, T, R, S;
+  int pad_j, pad_d, pad_h, pad_w;
+  int str_j, str_d, str_h, str_w;
+} ng_pool_desc;
+
+int ng_pool_output_dims(const ng_pool_desc* desc, int* K, int* M, int* P, int* Q);
+/* dtype_bytes: 2 = fp16 (hpool_max), 4 = fp32 (spool_max). Replaces the mode-0 launch of
+ * NervanaGPU._execute_pool (nervanagpu/nervanagpu.py:773-778,789-818). */
+int ng_pool_fprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, void* O, void* stream);
+/* gradI[argmax of each window] += E, every other element 0 (no zero-fill pass needed). Replaces
+ * the mode-1 launch and the B.fill(0) before it (nervanagpu/nervanagpu.py:780-787,811). */
+int ng_pool_bprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, const void* E, void* gradI, void* stream);
+
+/* ---- generated element-wise kernels -----------------------------------------------------------
+ * Replace pycuda.compiler.SourceModule / Function.prepare / prepared_async_call for the CUDA-C
+ * source emitted by the float_ew compiler (nervanagpu/float_ew.py:1030-1035,1314). `args` is an
+ * array of pointers to the argument values, in kernel-parameter order. */
+int ng_ew_compile(const char* source, const char* kernel_name, int fast_math, void** handle);
+const char* ng_ew_compile_log(void);
+int ng_ew_launch(void* handle, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
+                 unsigned shared_bytes, void** args, void* stream);
+int ng_ew_release(void* handle);
+
+/* ---- multi-GPU (one process per GPU) ------------------------------------------------------------
+ * No counterpart in the single-GPU reference (nervanagpu/nervanagpu.py:491); used to sum the
+ * fp32 weight gradients of update_conv / dW GEMMs over the ranks that share a minibatch. */
+int ng_comm_unique_id_bytes(void);
+int ng_comm_unique_id(void* id_out);
+int ng_comm_init(void** comm, int nranks, int rank, const void* id_bytes);
+int ng_comm_allreduce_f32(void* comm, void* buf, size_t count, void* stream);
+int ng_comm_async_error(void* comm);
+int ng_comm_destroy(void* comm);
+
+/* ---- the reference's own C interface ---------------------------------------------------------
+ * Same names and signatures as nervanagpu/kernels/C_interface/nervana_c_api.h:31-128 (bool
+ * result, message on stderr). CUstream is passed as void* here; the ABI is identical.
+ * hgemm is served by ng_hgemm; the fp32 sgemm entry points report failure. */
+#ifndef NERVANA_B200_NO_LEGACY_DECLS
+#ifdef __cplusplus
+#define NG_BOOL bool
+#else
+#include <stdbool.h>
+#define NG_BOOL bool
+#endif
+NG_BOOL nervana_loadKernels(const char* const base_path);
+NG_BOOL nervana_unloadKernels(void);
+size_t nervana_randStateSizeBytes(void);
+NG_BOOL nervana_hgemm(short* A, short* B, short* C, NG_BOOL a_t, NG_BOOL b_t, int m, int n, int k, int lda, int ldb,
+                      int ldc, float alpha, float beta, unsigned int* rand_state, NG_BOOL stochastic_round,
+                      NG_BOOL apply_relu, void* stream, int grid);
+NG_BOOL nervana_hgemm_colmajor(short* A, short* B, short* C, NG_BOOL a_t, NG_BOOL b_t, int m, int n, int k, int lda,
+                               int ldb, int ldc, float alpha, float beta, unsigned int* rand_state,
+                               NG_BOOL stochastic_round, NG_BOOL apply_relu, void* stream, int grid);
+NG_BOOL nervana_sgemm(float* A, float* B, float* C, NG_BOOL a_t, NG_BOOL b_t, int m, int n, int k, int lda, int ldb,
+                      int ldc, float alpha, float beta, unsigned int* rand_state, NG_BOOL stochastic_round,
+                      NG_BOOL apply_relu, void* stream, int grid);
+NG_BOOL nervana_sgemm_colmajor(float* A, float* B, float* C, NG_BOOL a_t, NG_BOOL b_t, int m, int n, int k, int lda,
+                               int ldb, int ldc, float alpha, float beta, unsigned int* rand_state,
+                               NG_BOOL stochastic_round, NG_BOOL apply_relu, void* stream, int grid);
+#endif
+
 #ifdef __cplusplus
 }
 #endif

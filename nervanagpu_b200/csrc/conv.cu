@@ -1,0 +1,435 @@
+// Convolution passes on CDHWN activations / CTRSK filters / KMPQN outputs (fp16 storage).
+//   fprop :  O = RN16(relu?(alpha * F (*) I))          nervanagpu/nervanagpu.py:642-650
+//   bprop :  dI = RN16(alpha * F^T (*)^T E)             nervanagpu/nervanagpu.py:652-659
+//   update:  dF = alpha * sum_{m,p,q,n} Ipatch * E^T    nervanagpu/nervanagpu.py:661-669
+// Dimensions follow ConvLayer (nervanagpu/layers.py:281-325): M,P,Q = ceil((X - f + 1 + 2 pad)/stride).
+//
+// Fast path: the tcgen05 implicit-GEMM engine, fed straight from the activation tensors by TMA
+// (padding = out-of-bounds zero fill, no im2col buffer, no filter shuffle):
+//   fprop   D[K x MPQN]   = F[crs][k]^T (MN-major A)  *  I patches (MN-major B)
+//   bprop   D[C x DHWN]   = F[c][k] per tap (K-major A)  *  E pixels reached through the tap (MN-major B)
+//   update  D[C x K]/tap  = I pixels under the tap (K-major A)  *  E (K-major B), reduction over (m,p,q,n)
+// A 64-element chunk of the pixel space is either 64 images of one pixel (N % 64 == 0) or, when
+// the W stride is 1, 64 consecutive elements of the flattened (x, n) dimension.
+// Small-C weight updates run as im2col + tensor-core GEMM; shapes neither path can address run
+// on plain SIMT kernels so that every legal call still executes on the GPU.
+#include <algorithm>
+
+#include "../../include/nervana_b200.h"
+#include "epilogue.cuh"
+#include "host.h"
+
+namespace ngb {
+
+namespace {
+
+struct Geo {
+  int N, C, K, D, H, W, T, R, S, M, P, Q;
+  int pad_d, pad_h, pad_w, str_d, str_h, str_w;
+  __host__ __device__ long long sizeI() const { return 1ll * C * D * H * W * N; }
+  __host__ __device__ long long sizeF() const { return 1ll * C * T * R * S * K; }
+  __host__ __device__ long long sizeO() const { return 1ll * K * M * P * Q * N; }
+};
+
+int out_dim(int x, int f, int pad, int str) {
+  // ceil((x - f + 1 + 2 pad) / str), as nervanagpu/layers.py:297-301
+  const int num = x - f + 1 + 2 * pad;
+  return (num + str - 1) / str;
+}
+
+int make_geo(const ng_conv_desc* d, Geo& g) {
+  if (!d) return fail(NG_ERR_INVALID_ARG, "conv descriptor is null");
+  g.N = d->N; g.C = d->C; g.K = d->K; g.D = d->D; g.H = d->H; g.W = d->W; g.T = d->T; g.R = d->R; g.S = d->S;
+  g.pad_d = d->pad_d; g.pad_h = d->pad_h; g.pad_w = d->pad_w;
+  g.str_d = d->str_d; g.str_h = d->str_h; g.str_w = d->str_w;
+  if (g.N < 1 || g.C < 1 || g.K < 1 || g.D < 1 || g.H < 1 || g.W < 1 || g.T < 1 || g.R < 1 || g.S < 1 ||
+      g.str_d < 1 || g.str_h < 1 || g.str_w < 1 || g.pad_d < 0 || g.pad_h < 0 || g.pad_w < 0)
+    return fail(NG_ERR_INVALID_ARG, "conv descriptor has a non-positive dimension");
+  if (g.N % 8 != 0) return fail(NG_ERR_INVALID_ARG, "N dim must be multiple of 8");
+  if (g.K % 8 != 0) return fail(NG_ERR_INVALID_ARG, "K dim must be multiple of 8");
+  g.M = out_dim(g.D, g.T, g.pad_d, g.str_d);
+  g.P = out_dim(g.H, g.R, g.pad_h, g.str_h);
+  g.Q = out_dim(g.W, g.S, g.pad_w, g.str_w);
+  if (g.M < 1 || g.P < 1 || g.Q < 1) return fail(NG_ERR_INVALID_ARG, "filter larger than padded input");
+  if (g.sizeI() > 0x7fffffffll * 8 || g.sizeO() > 0x7fffffffll * 8) return fail(NG_ERR_TOO_LARGE, "tensor too large");
+  return NG_OK;
+}
+
+bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// chunking of a (m,p,q,n)-like pixel space with innermost extents (xdim, N)
+enum ChunkMode { CH_NONE = 0, CH_PIXEL = 1, CH_FLAT = 2 };
+ChunkMode pick_chunk_mode(int N, int xdim, int str_w) {
+  if (N % kChunk == 0) return CH_PIXEL;
+  if (str_w == 1 && (1ll * xdim * N) % kChunk == 0) return CH_FLAT;
+  return CH_NONE;
+}
+
+// tensor map over an activation tensor (chan, z, y, x, n) seen as (n | x*n, x | 1, y, z, chan)
+int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, ChunkMode mode, uint32_t box_chan) {
+  uint64_t dims[5], str[4];
+  const uint64_t xn = 1ull * X * N * 2;
+  if (mode == CH_PIXEL) {
+    dims[0] = N; dims[1] = X; str[0] = 1ull * N * 2;
+  } else {
+    dims[0] = 1ull * X * N; dims[1] = 1; str[0] = xn;
+  }
+  dims[2] = Y; dims[3] = Z; dims[4] = chan;
+  str[1] = xn; str[2] = xn * Y; str[3] = xn * Y * Z;
+  const uint32_t box[5] = {kChunk, 1, 1, 1, box_chan};
+  return make_tensor_map(m, base, dims, str, box);
+}
+
+// tensor map over the filter (C, TRS, K) seen as (k, trs, c)
+int filter_map(CUtensorMap* m, const void* base, const Geo& g, uint32_t box_c) {
+  const int RST = g.T * g.R * g.S;
+  uint64_t dims[5] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(RST), static_cast<uint64_t>(g.C), 1, 1};
+  uint64_t str[4];
+  str[0] = 1ull * g.K * 2; str[1] = str[0] * RST; str[2] = str[1] * g.C; str[3] = str[2];
+  const uint32_t box[5] = {kChunk, 1, box_c, 1, 1};
+  return make_tensor_map(m, base, dims, str, box);
+}
+
+void fill_taps(TcParams& p, const Geo& g, ChunkMode mode) {
+  p.RS = g.R * g.S; p.S = g.S;
+  p.pad_d = g.pad_d; p.pad_h = g.pad_h; p.pad_w = g.pad_w;
+  p.str_d = g.str_d; p.str_h = g.str_h; p.str_w = g.str_w;
+  p.inner_tap = mode == CH_FLAT ? g.N : 0;
+  p.x_tap = mode == CH_FLAT ? 0 : 1;
+}
+
+void fill_decode(TcParams& p, int N, int X, int Y, int Z, ChunkMode mode) {
+  p.dec_cpi = mode == CH_FLAT ? (X * N) / kChunk : N / kChunk;
+  p.dec_q = mode == CH_FLAT ? 1 : X;
+  p.dec_p = Y;
+  p.dec_m = Z;
+}
+
+int pick_kb_rows(int C) {
+  int best = 64, best_pad = ((C + 63) / 64) * 64;
+  for (int r : {48, 32, 16}) {
+    const int pad = ((C + r - 1) / r) * r;
+    if (pad < best_pad) { best = r; best_pad = pad; }
+  }
+  return best;
+}
+
+// ------------------------------------------------------------------------------------------
+// SIMT fall-backs (one thread per output element, fp32 accumulation)
+// ------------------------------------------------------------------------------------------
+__global__ void conv_fprop_simt(Geo g, const __half* __restrict__ I, const __half* __restrict__ F, __half* O,
+                                float alpha, int relu) {
+  const long long total = g.sizeO();
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int n = r % g.N; r /= g.N;
+    const int q = r % g.Q; r /= g.Q;
+    const int p = r % g.P; r /= g.P;
+    const int m = r % g.M; r /= g.M;
+    const int k = static_cast<int>(r);
+    float acc = 0.0f;
+    for (int c = 0; c < g.C; ++c)
+      for (int t = 0; t < g.T; ++t) {
+        const int z = m * g.str_d - g.pad_d + t;
+        if (z < 0 || z >= g.D) continue;
+        for (int rr = 0; rr < g.R; ++rr) {
+          const int y = p * g.str_h - g.pad_h + rr;
+          if (y < 0 || y >= g.H) continue;
+          for (int s = 0; s < g.S; ++s) {
+            const int x = q * g.str_w - g.pad_w + s;
+            if (x < 0 || x >= g.W) continue;
+            const float iv = __half2float(I[(((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + n]);
+            const float fv = __half2float(F[(((1ll * c * g.T + t) * g.R + rr) * g.S + s) * g.K + k]);
+            acc = fmaf(iv, fv, acc);
+          }
+        }
+      }
+    acc *= alpha;
+    if (relu) acc = fmaxf(acc, 0.0f);
+    O[i] = __float2half_rn(acc);
+  }
+}
+
+__global__ void conv_bprop_simt(Geo g, const __half* __restrict__ F, const __half* __restrict__ E, __half* dI,
+                                float alpha) {
+  const long long total = g.sizeI();
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int n = r % g.N; r /= g.N;
+    const int x = r % g.W; r /= g.W;
+    const int y = r % g.H; r /= g.H;
+    const int z = r % g.D; r /= g.D;
+    const int c = static_cast<int>(r);
+    float acc = 0.0f;
+    for (int t = 0; t < g.T; ++t) {
+      const int mz = z + g.pad_d - t;
+      if (mz < 0 || mz % g.str_d) continue;
+      const int m = mz / g.str_d;
+      if (m >= g.M) continue;
+      for (int rr = 0; rr < g.R; ++rr) {
+        const int py = y + g.pad_h - rr;
+        if (py < 0 || py % g.str_h) continue;
+        const int p = py / g.str_h;
+        if (p >= g.P) continue;
+        for (int s = 0; s < g.S; ++s) {
+          const int qx = x + g.pad_w - s;
+          if (qx < 0 || qx % g.str_w) continue;
+          const int q = qx / g.str_w;
+          if (q >= g.Q) continue;
+          const __half* f = F + (((1ll * c * g.T + t) * g.R + rr) * g.S + s) * g.K;
+          for (int k = 0; k < g.K; ++k) {
+            const float ev = __half2float(E[(((1ll * k * g.M + m) * g.P + p) * g.Q + q) * g.N + n]);
+            acc = fmaf(__half2float(f[k]), ev, acc);
+          }
+        }
+      }
+    }
+    dI[i] = __float2half_rn(acc * alpha);
+  }
+}
+
+// one warp per filter element: lanes stride over (pixel, n), shuffle reduction
+__global__ void conv_update_simt(Geo g, const __half* __restrict__ I, const __half* __restrict__ E, void* dF,
+                                 int out_f32, float alpha) {
+  const long long total = g.sizeF();
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = (blockIdx.x * 1ll * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = (1ll * gridDim.x * blockDim.x) >> 5;
+  for (long long i = warp0; i < total; i += nwarps) {
+    long long r = i;
+    const int k = r % g.K; r /= g.K;
+    const int s = r % g.S; r /= g.S;
+    const int rr = r % g.R; r /= g.R;
+    const int t = r % g.T; r /= g.T;
+    const int c = static_cast<int>(r);
+    float acc = 0.0f;
+    const long long span = 1ll * g.M * g.P * g.Q * g.N;
+    for (long long j = lane; j < span; j += 32) {
+      long long rj = j;
+      const int n = rj % g.N; rj /= g.N;
+      const int q = rj % g.Q; rj /= g.Q;
+      const int p = rj % g.P; rj /= g.P;
+      const int m = static_cast<int>(rj);
+      const int z = m * g.str_d - g.pad_d + t, y = p * g.str_h - g.pad_h + rr, x = q * g.str_w - g.pad_w + s;
+      if (z < 0 || z >= g.D || y < 0 || y >= g.H || x < 0 || x >= g.W) continue;
+      const float iv = __half2float(I[(((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + n]);
+      const float ev = __half2float(E[1ll * k * span + j]);
+      acc = fmaf(iv, ev, acc);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (lane == 0) {
+      acc *= alpha;
+      if (out_f32) static_cast<float*>(dF)[i] = acc;
+      else static_cast<__half*>(dF)[i] = __float2half_rn(acc);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// im2col: col[crst][pixel * N + n] = I[c, z, y, x, n] (zero outside the image); 8 images per thread
+// ------------------------------------------------------------------------------------------
+__global__ void im2col_kernel(Geo g, const __half* __restrict__ I, __half* __restrict__ col) {
+  const int n8 = g.N / 8;
+  const long long mpq = 1ll * g.M * g.P * g.Q;
+  const long long total = 1ll * g.C * g.T * g.R * g.S * mpq * n8;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % n8; r /= n8;
+    const int q = r % g.Q; r /= g.Q;
+    const int p = r % g.P; r /= g.P;
+    const int m = r % g.M; r /= g.M;
+    const int s = r % g.S; r /= g.S;
+    const int rr = r % g.R; r /= g.R;
+    const int t = r % g.T; r /= g.T;
+    const int c = static_cast<int>(r);
+    const int z = m * g.str_d - g.pad_d + t, y = p * g.str_h - g.pad_h + rr, x = q * g.str_w - g.pad_w + s;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (z >= 0 && z < g.D && y >= 0 && y < g.H && x >= 0 && x < g.W)
+      v = *reinterpret_cast<const uint4*>(I + (((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + nv * 8);
+    reinterpret_cast<uint4*>(col)[i] = v;
+  }
+}
+
+int launch_1d(long long total, int threads, const DeviceCtx* c) {
+  long long blocks = (total + threads - 1) / threads;
+  return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, c->sm_count * 32ll)));
+}
+
+}  // namespace
+
+}  // namespace ngb
+
+using namespace ngb;
+
+extern "C" {
+
+int ng_conv_output_dims(const ng_conv_desc* d, int* M, int* P, int* Q) {
+  Geo g;
+  int rc = make_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (M) *M = g.M;
+  if (P) *P = g.P;
+  if (Q) *Q = g.Q;
+  return NG_OK;
+}
+
+int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, float alpha, int relu, int path,
+                  void* stream_) {
+  Geo g;
+  int rc = make_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !F || !O) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.Q, g.str_w);
+  const bool tc = path != NG_PATH_SIMT && mode != CH_NONE && aligned16(I) && aligned16(F) && aligned16(O);
+  if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
+  if (!tc) {
+    conv_fprop_simt<<<launch_1d(g.sizeO(), 256, c), 256, 0, stream>>>(
+        g, static_cast<const __half*>(I), static_cast<const __half*>(F), static_cast<__half*>(O), alpha, relu);
+    NG_CUDA(cudaGetLastError());
+    return NG_OK;
+  }
+  const int RST = g.T * g.R * g.S;
+  const long long cols = 1ll * g.M * g.P * g.Q * g.N;
+  TcParams p = {};
+  p.mode = TC_FPROP;
+  p.block_n = 256;
+  p.M = g.K; p.N = static_cast<int>(cols);
+  p.tiles_m = (g.K + kTileM - 1) / kTileM;
+  p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
+  p.nz = 1; p.splits = 1;
+  TcOperandLayout lay = {1, 1, pick_kb_rows(g.C)};
+  tc_fill_mma(p, lay);
+  p.red_chunks = (g.C + lay.kb_rows - 1) / lay.kb_rows;
+  p.num_kb = RST * p.red_chunks;
+  fill_taps(p, g, mode);
+  fill_decode(p, g.N, g.Q, g.P, g.M, mode);
+  p.oob_y = g.H;
+  p.C = O; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
+  p.alpha = alpha; p.beta = 0.0f; p.relu = relu; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
+  CUtensorMap mapA, mapB;
+  rc = filter_map(&mapA, F, g, lay.kb_rows);
+  if (rc != NG_OK) return rc;
+  rc = act_map(&mapB, I, g.C, g.D, g.H, g.W, g.N, mode, lay.kb_rows);
+  if (rc != NG_OK) return rc;
+  return tc_launch(c, mapA, mapB, p, stream);
+}
+
+int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gradI, float alpha, int path,
+                  void* stream_) {
+  Geo g;
+  int rc = make_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!F || !E || !gradI) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.W, g.str_w);
+  // in flattened mode the E row (Q*N) is addressed with the same element offsets as the dI row
+  const bool tc = path != NG_PATH_SIMT && mode != CH_NONE && aligned16(F) && aligned16(E) && aligned16(gradI);
+  if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
+  if (!tc) {
+    conv_bprop_simt<<<launch_1d(g.sizeI(), 256, c), 256, 0, stream>>>(
+        g, static_cast<const __half*>(F), static_cast<const __half*>(E), static_cast<__half*>(gradI), alpha);
+    NG_CUDA(cudaGetLastError());
+    return NG_OK;
+  }
+  const int RST = g.T * g.R * g.S;
+  const long long cols = 1ll * g.D * g.H * g.W * g.N;
+  TcParams p = {};
+  p.mode = TC_BPROP;
+  p.block_n = 256;
+  p.M = g.C; p.N = static_cast<int>(cols);
+  p.tiles_m = (g.C + kTileM - 1) / kTileM;
+  p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
+  p.nz = 1; p.splits = 1;
+  TcOperandLayout lay = {0, 1, kChunk};
+  tc_fill_mma(p, lay);
+  p.red_chunks = (g.K + kChunk - 1) / kChunk;
+  p.num_kb = RST * p.red_chunks;
+  fill_taps(p, g, mode);
+  fill_decode(p, g.N, g.W, g.H, g.D, mode);
+  p.oob_y = g.P;
+  p.C = gradI; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
+  p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
+  CUtensorMap mapA, mapB;
+  rc = filter_map(&mapA, F, g, kTileM);
+  if (rc != NG_OK) return rc;
+  rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk);
+  if (rc != NG_OK) return rc;
+  return tc_launch(c, mapA, mapB, p, stream);
+}
+
+int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gradF, int out_f32, float alpha,
+                   int path, void* stream_) {
+  Geo g;
+  int rc = make_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !E || !gradF) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.Q, g.str_w);
+  const bool al = aligned16(I) && aligned16(E) && aligned16(gradF);
+  const int RST = g.T * g.R * g.S;
+  const long long span = 1ll * g.M * g.P * g.Q * g.N;
+  const bool direct = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al &&
+                      (g.C >= 16 || path == NG_PATH_TENSOR);
+  const bool im2col = !direct && path != NG_PATH_SIMT && path != NG_PATH_TENSOR && al &&
+                      1ll * g.C * RST * span * 2 <= (6ll << 30);
+  if (path == NG_PATH_TENSOR && !direct) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
+  if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
+  if (direct) {
+    TcParams p = {};
+    p.mode = TC_UPDATE;
+    p.block_n = g.K <= 64 ? 64 : (g.K <= 128 ? 128 : 256);
+    p.M = g.C; p.N = g.K;
+    p.tiles_m = (g.C + kTileM - 1) / kTileM;
+    p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
+    p.nz = RST;
+    TcOperandLayout lay = {0, 0, kChunk};
+    tc_fill_mma(p, lay);
+    p.num_kb = static_cast<int>(span / kChunk);
+    fill_taps(p, g, mode);
+    fill_decode(p, g.N, g.Q, g.P, g.M, mode);
+    p.oob_y = g.H;
+    p.C = gradF; p.Cold = nullptr; p.ldc = 1ll * RST * g.K; p.c_zstride = g.K;
+    p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = out_f32; p.vec_ok = 1;
+    p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n * p.nz, p.num_kb, 1ll * g.C * g.K * RST);
+    CUtensorMap mapA, mapB;
+    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, kTileM);
+    if (rc != NG_OK) return rc;
+    rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, p.block_n);
+    if (rc != NG_OK) return rc;
+    return tc_launch(c, mapA, mapB, p, stream);
+  }
+  if (im2col) {
+    // dF[crst][k] = col[crst][span] * E[k][span]^T  (both K-major: an "nt" GEMM with split-K)
+    const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
+    const size_t col_off = ((static_cast<size_t>(32) * g.C * RST * g.K * 4) + 255) & ~size_t(255);  // room for partials
+    rc = ensure_workspace(c, col_off + col_bytes);
+    if (rc != NG_OK) return rc;
+    __half* col = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(c->ws) + col_off);
+    const long long total = 1ll * g.C * RST * span / 8;
+    im2col_kernel<<<launch_1d(total, 256, c), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
+    NG_CUDA(cudaGetLastError());
+    GemmCall gc = {};
+    gc.A = col; gc.B = E; gc.C = gradF; gc.a_t = 0; gc.b_t = 1;
+    gc.m = g.C * RST; gc.n = g.K;
+    if (span > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "reduction too long");
+    gc.k = static_cast<int>(span);
+    gc.lda = span; gc.ldb = span; gc.ldc = g.K;
+    gc.alpha = alpha; gc.beta = 0.0f; gc.batch = 1; gc.loops = 1; gc.out_f32 = out_f32;
+    return run_gemm(gc, stream);
+  }
+  const long long warps = g.sizeF();
+  conv_update_simt<<<launch_1d(warps * 32, 256, c), 256, 0, stream>>>(
+      g, static_cast<const __half*>(I), static_cast<const __half*>(E), gradF, out_f32, alpha);
+  NG_CUDA(cudaGetLastError());
+  return NG_OK;
+}
+
+}  // extern "C"

@@ -115,24 +115,6 @@ bool tma_ok(const void* p, long long ld) {
 
 }  // namespace
 
-struct GemmCall {
-  const void* A;
-  const void* B;
-  void* C;
-  int a_t, b_t, m, n, k;
-  long long lda, ldb, ldc;
-  float alpha, beta;
-  int relu, sr_bits;
-  unsigned long long seed;
-  unsigned rng_offset;
-  int batch;                 // independent outputs (grid z)
-  long long az, bz, cz;      // strides between them (0 = shared operand)
-  int loops;                 // batches accumulated into each output
-  long long alz, blz;
-  int out_f32;
-  int force_simt;
-};
-
 int run_gemm(const GemmCall& g, cudaStream_t stream) {
   if (!g.A || !g.B || !g.C) return fail(NG_ERR_INVALID_ARG, "null operand");
   if (g.m <= 0 || g.n <= 0 || g.k <= 0) return fail(NG_ERR_INVALID_ARG, "m, n, k must be positive");

@@ -51,4 +51,24 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
 // Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems);
 
+// One GEMM request: C[m x n] = epilogue(op(A) * op(B)); see ng_hgemm for the conventions.
+struct GemmCall {
+  const void* A;
+  const void* B;
+  void* C;
+  int a_t, b_t, m, n, k;
+  long long lda, ldb, ldc;
+  float alpha, beta;
+  int relu, sr_bits;
+  unsigned long long seed;
+  unsigned rng_offset;
+  int batch;                 // independent outputs (grid z)
+  long long az, bz, cz;      // element strides between them (0 = shared operand)
+  int loops;                 // batches accumulated into each output
+  long long alz, blz;
+  int out_f32;
+  int force_simt;
+};
+int run_gemm(const GemmCall& g, cudaStream_t stream);
+
 }  // namespace ngb

@@ -1,0 +1,250 @@
+// Max pooling over (feature map, depth, height, width) windows J,T,R,S on CDHWN tensors.
+// Replaces hpool_max / spool_max (kernels/sass/hpool_max.sass) launched by
+// NervanaGPU.fprop_pool / bprop_pool (nervanagpu/nervanagpu.py:773-818); output dimensions as
+// PoolLayer (nervanagpu/layers.py:565-569).
+//
+// Numerics follow the reference kernel: taps are scanned in j,t,r,s order with a strict '>'
+// compare so the first maximum wins (hpool_max.sass:264-281), taps outside the tensor are
+// skipped, and the backward pass adds E[k,m,p,q,n] to dI at the argmax of window (k,m,p,q).
+// Here the backward pass is a gather: each dI element visits the windows that contain it in
+// increasing (k,m,p,q) order, recomputes their argmax and sums the matching errors in fp32,
+// so overlapping windows need neither atomics nor a zero-fill pass and the result is
+// deterministic. The innermost dimension N is contiguous: each thread owns 8 images (one
+// 16-byte lane) when N % 8 == 0, else 1.
+#include <algorithm>
+#include <cfloat>
+#include <cuda_fp16.h>
+
+#include "../../include/nervana_b200.h"
+#include "host.h"
+
+namespace ngb {
+namespace {
+
+struct PoolGeo {
+  int N, C, D, H, W, J, T, R, S, K, M, P, Q;
+  int pad_j, pad_d, pad_h, pad_w, str_j, str_d, str_h, str_w;
+};
+
+int pool_out_dim(int x, int f, int pad, int str) { return (x - f + 1 + 2 * pad + str - 1) / str; }
+
+int make_pool_geo(const ng_pool_desc* d, PoolGeo& g) {
+  if (!d) return fail(NG_ERR_INVALID_ARG, "pool descriptor is null");
+  g.N = d->N; g.C = d->C; g.D = d->D; g.H = d->H; g.W = d->W;
+  g.J = d->J; g.T = d->T; g.R = d->R; g.S = d->S;
+  g.pad_j = d->pad_j; g.pad_d = d->pad_d; g.pad_h = d->pad_h; g.pad_w = d->pad_w;
+  g.str_j = d->str_j; g.str_d = d->str_d; g.str_h = d->str_h; g.str_w = d->str_w;
+  if (g.N < 1 || g.C < 1 || g.D < 1 || g.H < 1 || g.W < 1 || g.J < 1 || g.T < 1 || g.R < 1 || g.S < 1 ||
+      g.str_j < 1 || g.str_d < 1 || g.str_h < 1 || g.str_w < 1 || g.pad_j < 0 || g.pad_d < 0 || g.pad_h < 0 ||
+      g.pad_w < 0)
+    return fail(NG_ERR_INVALID_ARG, "pool descriptor has a non-positive dimension");
+  g.K = pool_out_dim(g.C, g.J, g.pad_j, g.str_j);
+  g.M = pool_out_dim(g.D, g.T, g.pad_d, g.str_d);
+  g.P = pool_out_dim(g.H, g.R, g.pad_h, g.str_h);
+  g.Q = pool_out_dim(g.W, g.S, g.pad_w, g.str_w);
+  if (g.K < 1 || g.M < 1 || g.P < 1 || g.Q < 1) return fail(NG_ERR_INVALID_ARG, "window larger than padded input");
+  return NG_OK;
+}
+
+template <typename T, int V>
+struct Vec;
+template <>
+struct Vec<__half, 8> {
+  uint4 raw;
+  __device__ float get(int i) const { return __half2float(reinterpret_cast<const __half*>(&raw)[i]); }
+  __device__ void set(int i, float v) { reinterpret_cast<__half*>(&raw)[i] = __float2half_rn(v); }
+};
+template <>
+struct Vec<__half, 1> {
+  __half raw;
+  __device__ float get(int) const { return __half2float(raw); }
+  __device__ void set(int, float v) { raw = __float2half_rn(v); }
+};
+template <>
+struct Vec<float, 4> {
+  float4 raw;
+  __device__ float get(int i) const { return reinterpret_cast<const float*>(&raw)[i]; }
+  __device__ void set(int i, float v) { reinterpret_cast<float*>(&raw)[i] = v; }
+};
+template <>
+struct Vec<float, 1> {
+  float raw;
+  __device__ float get(int) const { return raw; }
+  __device__ void set(int, float v) { raw = v; }
+};
+
+// Scan window (k,m,p,q): per image lane the max and the flat (c,z,y,x) index of its first occurrence.
+template <typename T, int V>
+__device__ __forceinline__ void window_max(const PoolGeo& g, const T* __restrict__ I, int k, int m, int p, int q,
+                                           int nv, float (&best)[V], int (&arg)[V]) {
+#pragma unroll
+  for (int i = 0; i < V; ++i) { best[i] = -FLT_MAX; arg[i] = 0; }
+  const int c0 = k * g.str_j - g.pad_j, z0 = m * g.str_d - g.pad_d, y0 = p * g.str_h - g.pad_h,
+            x0 = q * g.str_w - g.pad_w;
+  for (int j = 0; j < g.J; ++j) {
+    const int c = c0 + j;
+    if (c < 0 || c >= g.C) continue;
+    for (int t = 0; t < g.T; ++t) {
+      const int z = z0 + t;
+      if (z < 0 || z >= g.D) continue;
+      for (int r = 0; r < g.R; ++r) {
+        const int y = y0 + r;
+        if (y < 0 || y >= g.H) continue;
+        for (int s = 0; s < g.S; ++s) {
+          const int x = x0 + s;
+          if (x < 0 || x >= g.W) continue;
+          const int flat = ((c * g.D + z) * g.H + y) * g.W + x;
+          const Vec<T, V> v = *reinterpret_cast<const Vec<T, V>*>(I + (1ll * flat * g.N + nv * V));
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float f = v.get(i);
+            if (f > best[i]) { best[i] = f; arg[i] = flat; }
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int V>
+__global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restrict__ O) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.K * g.M * g.P * g.Q * nvec;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int q = r % g.Q; r /= g.Q;
+    const int p = r % g.P; r /= g.P;
+    const int m = r % g.M; r /= g.M;
+    const int k = static_cast<int>(r);
+    float best[V];
+    int arg[V];
+    window_max<T, V>(g, I, k, m, p, q, nv, best, arg);
+    Vec<T, V> out;
+#pragma unroll
+    for (int j = 0; j < V; ++j) out.set(j, best[j]);
+    *reinterpret_cast<Vec<T, V>*>(O + i * V) = out;
+  }
+}
+
+// first window index along one axis that can contain coordinate x, and the last
+__device__ __forceinline__ void window_range(int x, int pad, int f, int str, int nout, int& lo, int& hi) {
+  // windows w with w*str - pad <= x <= w*str - pad + f - 1
+  const int a = x + pad - f + 1;
+  lo = a <= 0 ? 0 : (a + str - 1) / str;
+  hi = min(nout - 1, (x + pad) / str);
+}
+
+template <typename T, int V>
+__global__ void pool_bprop_kernel(PoolGeo g, const T* __restrict__ I, const T* __restrict__ E, T* __restrict__ dI) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.C * g.D * g.H * g.W * nvec;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int flat = static_cast<int>(r);
+    const int x = r % g.W; r /= g.W;
+    const int y = r % g.H; r /= g.H;
+    const int z = r % g.D; r /= g.D;
+    const int c = static_cast<int>(r);
+    int k0, k1, m0, m1, p0, p1, q0, q1;
+    window_range(c, g.pad_j, g.J, g.str_j, g.K, k0, k1);
+    window_range(z, g.pad_d, g.T, g.str_d, g.M, m0, m1);
+    window_range(y, g.pad_h, g.R, g.str_h, g.P, p0, p1);
+    window_range(x, g.pad_w, g.S, g.str_w, g.Q, q0, q1);
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+    for (int k = k0; k <= k1; ++k)
+      for (int m = m0; m <= m1; ++m)
+        for (int p = p0; p <= p1; ++p)
+          for (int q = q0; q <= q1; ++q) {
+            float best[V];
+            int arg[V];
+            window_max<T, V>(g, I, k, m, p, q, nv, best, arg);
+            const long long o = ((((1ll * k * g.M + m) * g.P + p) * g.Q + q) * g.N) + nv * V;
+            const Vec<T, V> e = *reinterpret_cast<const Vec<T, V>*>(E + o);
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              if (arg[j] == flat) acc[j] += e.get(j);
+          }
+    Vec<T, V> out;
+#pragma unroll
+    for (int j = 0; j < V; ++j) out.set(j, acc[j]);
+    *reinterpret_cast<Vec<T, V>*>(dI + i * V) = out;
+  }
+}
+
+int grid_for(long long total, const DeviceCtx* c) {
+  const long long blocks = (total + 255) / 256;
+  return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, c->sm_count * 32ll)));
+}
+
+template <typename T, int VW>
+int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, const DeviceCtx* c,
+             cudaStream_t stream) {
+  const bool vec = g.N % VW == 0 && (reinterpret_cast<uintptr_t>(I) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(EO) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+  const long long out_elems = 1ll * g.K * g.M * g.P * g.Q * g.N;
+  const long long in_elems = 1ll * g.C * g.D * g.H * g.W * g.N;
+  if (mode == 0) {
+    T* O = static_cast<T*>(const_cast<void*>(EO));
+    if (vec) pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O);
+    else pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O);
+  } else {
+    if (vec)
+      pool_bprop_kernel<T, VW><<<grid_for(in_elems / VW, c), 256, 0, stream>>>(
+          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out));
+    else
+      pool_bprop_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(
+          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out));
+  }
+  NG_CUDA(cudaGetLastError());
+  return NG_OK;
+}
+
+}  // namespace
+}  // namespace ngb
+
+using namespace ngb;
+
+extern "C" {
+
+int ng_pool_output_dims(const ng_pool_desc* d, int* K, int* M, int* P, int* Q) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (K) *K = g.K;
+  if (M) *M = g.M;
+  if (P) *P = g.P;
+  if (Q) *Q = g.Q;
+  return NG_OK;
+}
+
+int ng_pool_fprop(const ng_pool_desc* d, int dtype_bytes, const void* I, void* O, void* stream) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !O) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  if (1ll * g.C * g.D * g.H * g.W > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many pixels");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, O, O, 0, c, static_cast<cudaStream_t>(stream));
+  if (dtype_bytes == 4) return run_pool<float, 4>(g, I, O, O, 0, c, static_cast<cudaStream_t>(stream));
+  return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+int ng_pool_bprop(const ng_pool_desc* d, int dtype_bytes, const void* I, const void* E, void* gradI, void* stream) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !E || !gradI) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  if (1ll * g.C * g.D * g.H * g.W > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many pixels");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
+  if (dtype_bytes == 4) return run_pool<float, 4>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
+  return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+}  // extern "C"

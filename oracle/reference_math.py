@@ -1,0 +1,350 @@
+"""CPU restatement (numpy) of the reference's validation math. TEST INFRASTRUCTURE ONLY.
+
+This module is the oracle that the CUDA kernels are checked against. Only tests, the smoke
+check and the bench's cpu-baseline / reference arm may import it; no product code path does.
+
+The reference (VisionSystemsInc/nervanagpu) cannot run here: its kernels are Maxwell SASS and
+its host code needs PyCUDA. What it does provide is numpy code that defines the expected
+results, inline in its benchmark scripts and its one unit test. Each function below follows
+that code and names it:
+
+  gemm        benchmarks/gemm_test.py:52-59, benchmarks/gemm_test2.py:52-59 (np.dot on fp32
+              copies, .T for transposed operands); inputs quantised to fp16 first as
+              benchmarks/batched_dot_test.py:38-40; epilogue order alpha -> relu -> + beta*C
+              -> round from nervanagpu/nervanagpu.py:960-965 and
+              kernels/sass/hgemm_common_128x128.sass:183-272.
+  conv        benchmarks/conv_test.py:53-55 (slicable), :72 (zero pad row), :99-130
+              (pixel_indices), :147-167 (the three np.dot lines); output dims
+              nervanagpu/layers.py:297-301.
+  pool        benchmarks/pool_test.py:45-56, :71-104 (pixel_indices), :117-140 (first-hit
+              np.argmax, bprop += at the argmax, finfo.min pad row).
+  elementwise nervanagpu/tests/test_tensor.py:46-57 (compute in fp32; integers np.around +
+              clip; cast), mean/var per nervanagpu/nervanagpu.py:1191-1208.
+  stochastic  nervanagpu/float_ew.py:126-130,181-201 and hgemm_common_128x128.sass:281-343:
+  rounding    add a uniform below one target ulp to the magnitude, truncate toward zero, so
+              the result is one of the two neighbours of the fp32 value.
+
+Pinning: the reference stores no golden files and seeds nothing. Its known-answer cases (all
+ones GEMM == k, all zeros == 0: kernels/C_interface/test.cu:27-55,70 and
+benchmarks/gemm_test2.py:30-43; ones switches in conv_test.py:58-61) and its own unit-test
+recipe are reproduced in tests/test_oracle.py; stochastic rounding has no reference test
+(parity unpinned for that mode; checked by the neighbour + unbiasedness properties).
+"""
+from math import ceil
+
+import numpy as np
+
+
+# ---------------------------------------------------------------------------------------------
+# GEMM
+# ---------------------------------------------------------------------------------------------
+def gemm(A, B, a_t=False, b_t=False, alpha=1.0, beta=0.0, relu=False, C=None):
+    """fp32 result of relu?(alpha * op(A) @ op(B)) + beta * C before the final rounding."""
+    a = np.asarray(A, dtype=np.float32)
+    b = np.asarray(B, dtype=np.float32)
+    if a_t:
+        a = a.T
+    if b_t:
+        b = b.T
+    c = np.dot(a, b) * np.float32(alpha)
+    if relu:
+        c = np.maximum(c, np.float32(0))
+    if beta != 0.0:
+        c = c + np.float32(beta) * np.asarray(C, dtype=np.float32)
+    return c.astype(np.float32)
+
+
+def gemm_abs(A, B, a_t=False, b_t=False):
+    """|op(A)| @ |op(B)|: scale of the rounding-error bound of a length-k dot product."""
+    return gemm(np.abs(np.asarray(A, np.float32)), np.abs(np.asarray(B, np.float32)), a_t, b_t)
+
+
+# ---------------------------------------------------------------------------------------------
+# convolution
+# ---------------------------------------------------------------------------------------------
+class ConvDims(object):
+    """Shape bookkeeping of ConvLayer (nervanagpu/layers.py:281-325)."""
+
+    def __init__(self, N, C, K, D=1, H=1, W=1, T=1, R=1, S=1, pad_d=0, pad_h=0, pad_w=0,
+                 str_d=1, str_h=1, str_w=1):
+        self.N, self.C, self.K = N, C, K
+        self.DHW = (D, H, W)
+        self.TRS = (T, R, S)
+        self.padding = (pad_d, pad_h, pad_w)
+        self.strides = (str_d, str_h, str_w)
+        M = int(ceil(float(D - T + 1 + 2 * pad_d) / str_d))
+        P = int(ceil(float(H - R + 1 + 2 * pad_h) / str_h))
+        Q = int(ceil(float(W - S + 1 + 2 * pad_w) / str_w))
+        self.MPQ = (M, P, Q)
+        self.dimI = (C, D, H, W, N)
+        self.dimF = (C, T, R, S, K)
+        self.dimO = (K, M, P, Q, N)
+        self.flops = M * P * Q * K * N * C * T * R * S * 2.0
+
+
+def _slicable(dim, pad=0):
+    """Collapse all but the last dimension; optionally one extra padding row (conv_test.py:53-55)."""
+    rows = 1
+    for d in dim[:-1]:
+        rows *= d
+    return (rows + pad, dim[-1])
+
+
+def _conv_pixel_rows(cd, mt, pr, qs):
+    """Row numbers (c,z,y,x) of the collapsed input that one output pixel reads, in (c,t,r,s)
+    order; out-of-image taps point at the padding row (conv_test.py:99-130)."""
+    T, R, S = cd.TRS
+    D, H, W = cd.DHW
+    C = cd.C
+    HW, DHW = H * W, D * H * W
+    pad_row = C * DHW
+    rows = []
+    for c in range(C):
+        for t in range(T):
+            z = mt + t
+            z_ok = 0 <= z < D
+            for r in range(R):
+                y = pr + r
+                y_ok = z_ok and 0 <= y < H
+                for s in range(S):
+                    x = qs + s
+                    if y_ok and 0 <= x < W:
+                        rows.append(c * DHW + z * HW + y * W + x)
+                    else:
+                        rows.append(pad_row)
+    return rows
+
+
+def _conv_pixels(cd):
+    M, P, Q = cd.MPQ
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    for m in range(M):
+        for p in range(P):
+            for q in range(Q):
+                yield m, p, q, _conv_pixel_rows(cd, m * str_d - pad_d, p * str_h - pad_h, q * str_w - pad_w)
+
+
+def _padded_input(cd, I):
+    buf = np.zeros(_slicable(cd.dimI, 1), dtype=np.float32)
+    buf[:-1, :] = np.asarray(I, dtype=np.float32).reshape(_slicable(cd.dimI))
+    return buf
+
+
+def conv_fprop(cd, I, F, alpha=1.0, relu=False):
+    """Per-pixel loop of conv_test.py:147-161: O[:,m,p,q,:] = F2d.T @ I2d[rows]."""
+    I2 = _padded_input(cd, I)
+    F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
+    O = np.zeros(cd.dimO, dtype=np.float32)
+    for m, p, q, rows in _conv_pixels(cd):
+        O[:, m, p, q, :] = np.dot(F2.T, I2[rows, :])
+    O *= np.float32(alpha)
+    if relu:
+        O = np.maximum(O, np.float32(0))
+    return O
+
+
+def conv_bprop(cd, F, E, alpha=1.0):
+    """conv_test.py:163-164: gradI2d[rows] += F2d @ E[:,m,p,q,:]."""
+    F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
+    E = np.asarray(E, dtype=np.float32).reshape(cd.dimO)
+    B = np.zeros(_slicable(cd.dimI, 1), dtype=np.float32)
+    for m, p, q, rows in _conv_pixels(cd):
+        # rows of one pixel are distinct except for the shared padding row, which is dropped
+        np.add.at(B, rows, np.dot(F2, E[:, m, p, q, :]))
+    return (B[:-1, :] * np.float32(alpha)).reshape(cd.dimI)
+
+
+def conv_update(cd, I, E, alpha=1.0):
+    """conv_test.py:166-167: gradF2d += I2d[rows] @ E[:,m,p,q,:].T."""
+    I2 = _padded_input(cd, I)
+    E = np.asarray(E, dtype=np.float32).reshape(cd.dimO)
+    U = np.zeros(_slicable(cd.dimF), dtype=np.float32)
+    for m, p, q, rows in _conv_pixels(cd):
+        U += np.dot(I2[rows, :], E[:, m, p, q, :].T)
+    return (U * np.float32(alpha)).reshape(cd.dimF)
+
+
+def _im2col(cd, I):
+    """All pixels at once: (C*T*R*S, M*P*Q*N) patch matrix, zero outside the image."""
+    C, D, H, W, N = cd.dimI
+    T, R, S = cd.TRS
+    M, P, Q = cd.MPQ
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    Ip = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
+    Ip[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] = np.asarray(I, dtype=np.float32).reshape(cd.dimI)
+    col = np.empty((C, T, R, S, M, P, Q, N), dtype=np.float32)
+    for t in range(T):
+        for r in range(R):
+            for s in range(S):
+                col[:, t, r, s] = Ip[:, t:t + M * str_d:str_d, r:r + P * str_h:str_h, s:s + Q * str_w:str_w, :]
+    return col.reshape(C * T * R * S, M * P * Q * N)
+
+
+def conv_fprop_fast(cd, I, F, alpha=1.0, relu=False):
+    """Vectorised variant (one matmul) for the large configurations; the same sums as
+    conv_fprop in a different association order. Cross-checked against it in tests."""
+    col = _im2col(cd, I)
+    F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
+    O = np.dot(F2.T, col).reshape(cd.dimO) * np.float32(alpha)
+    if relu:
+        O = np.maximum(O, np.float32(0))
+    return O
+
+
+def conv_update_fast(cd, I, E, alpha=1.0):
+    col = _im2col(cd, I)
+    E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, -1)
+    return (np.dot(col, E2.T) * np.float32(alpha)).reshape(cd.dimF)
+
+
+def conv_bprop_fast(cd, F, E, alpha=1.0):
+    C, D, H, W, N = cd.dimI
+    T, R, S = cd.TRS
+    M, P, Q = cd.MPQ
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
+    E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, -1)
+    colg = np.dot(F2, E2).reshape(C, T, R, S, M, P, Q, N)
+    Bp = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
+    for t in range(T):
+        for r in range(R):
+            for s in range(S):
+                Bp[:, t:t + M * str_d:str_d, r:r + P * str_h:str_h, s:s + Q * str_w:str_w, :] += colg[:, t, r, s]
+    return Bp[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] * np.float32(alpha)
+
+
+# ---------------------------------------------------------------------------------------------
+# pooling
+# ---------------------------------------------------------------------------------------------
+class PoolDims(object):
+    """Shape bookkeeping of PoolLayer (nervanagpu/layers.py:542-584)."""
+
+    def __init__(self, N, C, D=1, H=1, W=1, J=1, T=1, R=1, S=1, pad_j=0, pad_d=0, pad_h=0, pad_w=0,
+                 str_j=None, str_d=None, str_h=None, str_w=None):
+        str_j = J if str_j is None else str_j
+        str_d = T if str_d is None else str_d
+        str_h = R if str_h is None else str_h
+        str_w = S if str_w is None else str_w
+        self.N, self.C = N, C
+        self.DHW = (D, H, W)
+        self.JTRS = (J, T, R, S)
+        self.padding = (pad_j, pad_d, pad_h, pad_w)
+        self.strides = (str_j, str_d, str_h, str_w)
+        K = int(ceil(float(C - J + 1 + 2 * pad_j) / str_j))
+        M = int(ceil(float(D - T + 1 + 2 * pad_d) / str_d))
+        P = int(ceil(float(H - R + 1 + 2 * pad_h) / str_h))
+        Q = int(ceil(float(W - S + 1 + 2 * pad_w) / str_w))
+        self.K = K
+        self.MPQ = (M, P, Q)
+        self.dimI = (C, D, H, W, N)
+        self.dimO = (K, M, P, Q, N)
+
+
+def _pool_pixel_rows(pd, kj, mt, pr, qs):
+    C = pd.C
+    J, T, R, S = pd.JTRS
+    D, H, W = pd.DHW
+    HW, DHW = H * W, D * H * W
+    pad_row = C * DHW
+    rows = []
+    for j in range(J):
+        c = kj + j
+        c_ok = 0 <= c < C
+        for t in range(T):
+            z = mt + t
+            z_ok = c_ok and 0 <= z < D
+            for r in range(R):
+                y = pr + r
+                y_ok = z_ok and 0 <= y < H
+                for s in range(S):
+                    x = qs + s
+                    rows.append(c * DHW + z * HW + y * W + x if (y_ok and 0 <= x < W) else pad_row)
+    return rows
+
+
+def pool_max(pd, I, E=None):
+    """Max-pool forward, and backward when E is given (pool_test.py:117-140).
+
+    Returns (O, gradI). The padding row holds finfo.min so it never wins; np.argmax returns the
+    first maximum in (j,t,r,s) order. gradI accumulates E (the reference script passes its own
+    output as E) in fp32, window after window in (k,m,p,q) order."""
+    N = pd.N
+    I2 = np.empty(_slicable(pd.dimI, 1), dtype=np.float32)
+    I2[:-1, :] = np.asarray(I, dtype=np.float32).reshape(_slicable(pd.dimI))
+    I2[-1, :] = np.finfo(np.float32).min
+    O = np.empty(pd.dimO, dtype=np.float32)
+    B = np.zeros(_slicable(pd.dimI, 1), dtype=np.float32)
+    if E is not None:
+        E = np.asarray(E, dtype=np.float32).reshape(pd.dimO)
+    M, P, Q = pd.MPQ
+    pad_j, pad_d, pad_h, pad_w = pd.padding
+    str_j, str_d, str_h, str_w = pd.strides
+    cols = np.arange(N)
+    for k in range(pd.K):
+        for m in range(M):
+            for p in range(P):
+                for q in range(Q):
+                    rows = np.array(_pool_pixel_rows(pd, k * str_j - pad_j, m * str_d - pad_d,
+                                                     p * str_h - pad_h, q * str_w - pad_w))
+                    window = I2[rows, :]
+                    O[k, m, p, q, :] = np.max(window, axis=0)
+                    if E is not None:
+                        hit = rows[np.argmax(window, axis=0)]
+                        B[hit, cols] += E[k, m, p, q, :]
+    gradI = B[:-1, :].reshape(pd.dimI) if E is not None else None
+    return O, gradI
+
+
+# ---------------------------------------------------------------------------------------------
+# element-wise
+# ---------------------------------------------------------------------------------------------
+def cast_result(x, dtype):
+    """Final store of an element-wise kernel as the reference test models it
+    (tests/test_tensor.py:50-53): integers round to nearest (ties to even) and saturate."""
+    dtype = np.dtype(dtype)
+    x = np.asarray(x, dtype=np.float32)
+    if dtype.kind in "iu":
+        info = np.iinfo(dtype)
+        x = np.around(x).clip(info.min, info.max)
+    return x.astype(dtype)
+
+
+def batch_norm(A, eps=1e-3, axis=1):
+    """(A - mean(A,axis)) / sqrt(var(A,axis) + eps) with population variance, the README
+    expression built from NervanaGPU.mean / var (nervanagpu/nervanagpu.py:1191-1208)."""
+    a = np.asarray(A, dtype=np.float32)
+    mean = a.sum(axis=axis, keepdims=True, dtype=np.float32) * np.float32(1.0 / a.shape[axis])
+    d = a - mean
+    var = (d * d).sum(axis=axis, keepdims=True, dtype=np.float32) * np.float32(1.0 / a.shape[axis])
+    return (d / np.sqrt(var + np.float32(eps))).astype(np.float32)
+
+
+# ---------------------------------------------------------------------------------------------
+# stochastic rounding
+# ---------------------------------------------------------------------------------------------
+def fp16_neighbours(x, mantissa_bits=10):
+    """The two values a stochastic rounding of fp32 `x` to fp16 with `mantissa_bits` kept may
+    return: truncation toward zero and the next value away from zero (equal when x is exact)."""
+    x = np.asarray(x, dtype=np.float32)
+    bits = x.view(np.uint32)
+    drop = np.uint32(23 - mantissa_bits)
+    mask = np.uint32((1 << int(drop)) - 1)
+    lo_bits = bits & ~mask
+    exact = (bits & mask) == 0
+    hi_bits = np.where(exact, lo_bits, lo_bits + (mask + np.uint32(1)))
+    lo = lo_bits.view(np.float32)
+    hi = hi_bits.view(np.float32)
+    # below the fp16 normal range the spacing is fixed at 2^-24 (times dropped mantissa bits)
+    ulp = np.float32(2.0 ** (-24 + 10 - mantissa_bits))
+    sub = np.abs(x) < np.float32(2.0 ** -14)
+    mag = np.abs(x)
+    lo_s = np.copysign(np.floor(mag / ulp) * ulp, x).astype(np.float32)
+    hi_s = np.copysign(np.where(np.floor(mag / ulp) * ulp == mag, mag, np.floor(mag / ulp) * ulp + ulp), x).astype(np.float32)
+    lo = np.where(sub, lo_s, lo)
+    hi = np.where(sub, hi_s, hi)
+    # truncation never produces infinity from a finite value: clamp at the largest fp16
+    big = np.float32(65504.0)
+    return np.clip(lo, -big, big).astype(np.float16), np.clip(hi, -big, big).astype(np.float16)
