@@ -146,6 +146,8 @@ int ng_pool_bprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, cons
  * source emitted by the float_ew compiler (nervanagpu/float_ew.py:1030-1035,1314). `args` is an
  * array of pointers to the argument values, in kernel-parameter order. */
 int ng_ew_compile(const char* source, const char* kernel_name, int fast_math, void** handle);
+/* Compile only (no device needed): checks that generated source builds for sm_100a. */
+int ng_ew_compile_only(const char* source, int fast_math);
 const char* ng_ew_compile_log(void);
 int ng_ew_launch(void* handle, unsigned gx, unsigned gy, unsigned gz, unsigned bx, unsigned by, unsigned bz,
                  unsigned shared_bytes, void** args, void* stream);

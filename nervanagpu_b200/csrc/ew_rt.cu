@@ -68,13 +68,8 @@ const char* ng_ew_compile_log(void) {
   return g_log.c_str();
 }
 
-int ng_ew_compile(const char* source, const char* kernel_name, int fast_math, void** handle) {
-  if (!source || !kernel_name || !handle) return fail(NG_ERR_INVALID_ARG, "null argument");
-  DeviceCtx* c = current_ctx();
-  if (!c) return NG_ERR_CUDA;
-  DriverApi& api = driver();
-  if (!api.ok) return fail(NG_ERR_CUDA, "driver module entry points not available");
-
+// NVRTC front half: source -> sm_100a cubin. Needs no device.
+static int compile_to_cubin(const char* source, int fast_math, std::vector<char>& cubin) {
   nvrtcProgram prog;
   nvrtcResult r = nvrtcCreateProgram(&prog, source, "ew_kernel.cu", 0, nullptr, nullptr);
   if (r != NVRTC_SUCCESS) return fail(NG_ERR_NVRTC, "nvrtcCreateProgram: %s", nvrtcGetErrorString(r));
@@ -100,9 +95,27 @@ int ng_ew_compile(const char* source, const char* kernel_name, int fast_math, vo
     nvrtcDestroyProgram(&prog);
     return fail(NG_ERR_NVRTC, "nvrtcGetCUBINSize: %s", nvrtcGetErrorString(r));
   }
-  std::vector<char> cubin(cubin_size);
+  cubin.resize(cubin_size);
   nvrtcGetCUBIN(prog, cubin.data());
   nvrtcDestroyProgram(&prog);
+  return NG_OK;
+}
+
+int ng_ew_compile_only(const char* source, int fast_math) {
+  if (!source) return fail(NG_ERR_INVALID_ARG, "null argument");
+  std::vector<char> cubin;
+  return compile_to_cubin(source, fast_math, cubin);
+}
+
+int ng_ew_compile(const char* source, const char* kernel_name, int fast_math, void** handle) {
+  if (!source || !kernel_name || !handle) return fail(NG_ERR_INVALID_ARG, "null argument");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  DriverApi& api = driver();
+  if (!api.ok) return fail(NG_ERR_CUDA, "driver module entry points not available");
+  std::vector<char> cubin;
+  int crc = compile_to_cubin(source, fast_math, cubin);
+  if (crc != NG_OK) return crc;
 
   EwKernel* k = new EwKernel();
   CUresult cr = api.moduleLoadData(&k->mod, cubin.data());

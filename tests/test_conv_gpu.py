@@ -1,0 +1,176 @@
+"""fprop_conv / bprop_conv / update_conv against the reference's numpy path (B200 only)."""
+import numpy as np
+import pytest
+
+from nervanagpu_b200 import _lib
+from oracle import reference_math as rm
+from tests._util import assert_close, f32_tol, golden, golden_names, rn16_tol
+
+pytestmark = pytest.mark.gpu
+
+PATHS = {"auto": _lib.NG_PATH_AUTO, "tensor": _lib.NG_PATH_TENSOR, "simt": _lib.NG_PATH_SIMT,
+         "im2col": _lib.NG_PATH_IM2COL}
+
+
+def _layer(ng, cfg, path="auto"):
+    layer = ng.conv_layer(np.float16, *cfg)
+    layer.path = PATHS[path]
+    return layer
+
+
+def _abs_terms(cd, I, F, E):
+    """sum |a||b| of each output's dot product, for the accumulation-error bound."""
+    aI, aF, aE = np.abs(I.astype(np.float32)), np.abs(F.astype(np.float32)), np.abs(E.astype(np.float32))
+    return rm.conv_fprop_fast(cd, aI, aF), rm.conv_bprop_fast(cd, aF, aE), rm.conv_update_fast(cd, aI, aE)
+
+
+def _run_all(ng, layer, I, F, E, relu=False, alpha=1.0, ops="fbu"):
+    dI, dF, dE = ng.array(I), ng.array(F), ng.array(E)
+    out = {}
+    if "f" in ops:
+        dO = ng.empty(layer.dimO)
+        ng.fprop_conv(layer, dI, dF, dO, alpha=alpha, relu=relu)
+        out["O"] = dO.get()
+    if "b" in ops:
+        dB = ng.empty(layer.dimI)
+        ng.bprop_conv(layer, dF, dE, dB, alpha=alpha)
+        out["gradI"] = dB.get()
+    if "u" in ops:
+        dU = ng.empty(layer.dimF, dtype=np.float32)
+        ng.update_conv(layer, dI, dE, dU, alpha=alpha)
+        out["gradF"] = dU.get()
+    return out
+
+
+def _check(cd, got, I, F, E, ref, what):
+    T, R, S = cd.TRS
+    aO, aB, aU = _abs_terms(cd, I, F, E)
+    M, P, Q = cd.MPQ
+    if "O" in got:
+        assert_close(got["O"], ref["O"], rn16_tol(ref["O"], aO, cd.C * T * R * S), what + " fprop")
+    if "gradI" in got:
+        assert_close(got["gradI"], ref["gradI"], rn16_tol(ref["gradI"], aB, cd.K * T * R * S), what + " bprop")
+    if "gradF" in got:
+        assert_close(got["gradF"], ref["gradF"], f32_tol(aU, M * P * Q * cd.N), what + " update")
+
+
+@pytest.mark.parametrize("name", golden_names("conv_"))
+@pytest.mark.parametrize("path", ["auto", "simt"])
+def test_golden_vectors_of_the_reference_numpy_path(ng, name, path):
+    g = golden(name)
+    cfg = [int(v) for v in g["cfg"]]
+    cd = rm.ConvDims(*cfg)
+    got = _run_all(ng, _layer(ng, cfg, path), g["I"], g["F"], g["E"])
+    _check(cd, got, g["I"], g["F"], g["E"], g, "%s/%s" % (name, path))
+
+
+CASES = {
+    # name: (N, C, K, D, H, W, T, R, S, pad_d, pad_h, pad_w, str_d, str_h, str_w)
+    "c64_3x3_n64": (64, 64, 128, 1, 8, 8, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "c3_3x3_n64_first_layer": (64, 3, 64, 1, 12, 12, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "c16_5x5_stride2_n128": (128, 16, 32, 1, 13, 13, 1, 5, 5, 0, 2, 2, 1, 2, 2),
+    "c96_3x3_n32_flattened": (32, 96, 64, 1, 8, 8, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "c64_3d_n32": (32, 64, 64, 4, 6, 6, 3, 3, 3, 1, 1, 1, 1, 1, 1),
+    "c3_11x11_stride4_n64_alexnet1": (64, 3, 64, 1, 35, 35, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    "c130_k200_ragged_channels": (64, 130, 200, 1, 7, 7, 1, 3, 3, 0, 0, 0, 1, 1, 1),
+    "c32_1x1": (64, 32, 48, 1, 5, 5, 1, 1, 1, 0, 0, 0, 1, 1, 1),
+    "c8_n16_flattened_q8": (16, 8, 16, 1, 8, 8, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "stride_h_only": (64, 16, 16, 1, 9, 8, 1, 3, 3, 0, 1, 1, 1, 2, 1),
+}
+
+
+def _inputs(cd, seed):
+    rng = np.random.default_rng(seed)
+    I = rng.uniform(0, 1, cd.dimI).astype(np.float16)
+    F = rng.normal(0, 0.1, cd.dimF).astype(np.float16)
+    E = (rng.uniform(-1, 1, cd.dimO) * 0.125).astype(np.float16)
+    return I, F, E
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_tensor_core_path_matches_oracle(ng, name):
+    cfg = CASES[name]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 1003)
+    ref = {"O": rm.conv_fprop_fast(cd, I, F, alpha=0.5, relu=True), "gradI": rm.conv_bprop_fast(cd, F, E, alpha=0.5),
+           "gradF": rm.conv_update_fast(cd, I, E, alpha=0.5)}
+    got = _run_all(ng, _layer(ng, cfg, "tensor"), I, F, E, relu=True, alpha=0.5)
+    _check(cd, got, I, F, E, ref, name)
+    assert (got["O"] >= 0).all()
+
+
+@pytest.mark.parametrize("name", ["c3_3x3_n64_first_layer", "c3_11x11_stride4_n64_alexnet1", "c64_3x3_n64"])
+def test_update_im2col_path(ng, name):
+    cfg = CASES[name]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 77)
+    got = _run_all(ng, _layer(ng, cfg, "im2col"), I, F, E, ops="u")
+    _check(cd, got, I, F, E, {"gradF": rm.conv_update_fast(cd, I, E)}, name + "/im2col")
+
+
+def test_shapes_outside_the_tensor_path_run_on_simt(ng):
+    cfg = (8, 24, 16, 1, 5, 5, 1, 3, 3, 0, 1, 1, 1, 2, 2)   # N = 8 with a W stride: no 64-element chunks
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 5)
+    ref = {"O": rm.conv_fprop(cd, I, F), "gradI": rm.conv_bprop(cd, F, E), "gradF": rm.conv_update(cd, I, E)}
+    _check(cd, _run_all(ng, _layer(ng, cfg, "auto"), I, F, E), I, F, E, ref, "auto->simt")
+    with pytest.raises(_lib.NervanaError):
+        _run_all(ng, _layer(ng, cfg, "tensor"), I, F, E, ops="f")
+
+
+def test_update_fp16_output_and_determinism(ng):
+    cfg = CASES["c64_3x3_n64"]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 9)
+    layer = _layer(ng, cfg)
+    dI, dE = ng.array(I), ng.array(E)
+    u16 = ng.empty(layer.dimF, dtype=np.float16)
+    ng.update_conv(layer, dI, dE, u16)
+    ref = rm.conv_update_fast(cd, I, E)
+    assert_close(u16.get(), ref, 2.0 ** -10 * np.abs(ref) + 1e-3, "fp16 dW")
+    a, b = ng.empty(layer.dimF, dtype=np.float32), ng.empty(layer.dimF, dtype=np.float32)
+    ng.update_conv(layer, dI, dE, a)
+    ng.update_conv(layer, dI, dE, b)
+    assert np.array_equal(a.get(), b.get())     # fixed summation order, unlike atomics
+
+
+def test_full_size_alexnet_layer_properties(ng):
+    """AlexNet conv3 at BASELINE size (N=128, 192->384, 13x13): the oracle is too slow for every
+    output, so check (a) linearity in the filter, (b) an exact sample of output pixels."""
+    cfg = (128, 192, 384, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1)
+    cd = rm.ConvDims(*cfg)
+    rng = np.random.default_rng(1003)
+    I = rng.uniform(0, 1, cd.dimI).astype(np.float16)
+    F1 = (rng.integers(-8, 9, cd.dimF) / 256.0).astype(np.float16)
+    F2 = (rng.integers(-8, 9, cd.dimF) / 256.0).astype(np.float16)
+    layer = _layer(ng, cfg)
+    dI = ng.array(I)
+    outs = []
+    for F in (F1, F2, (F1 + F2).astype(np.float16)):
+        dO = ng.empty(layer.dimO)
+        ng.fprop_conv(layer, dI, ng.array(F), dO)
+        outs.append(dO.get().astype(np.float32))
+    s = outs[0] + outs[1]
+    assert (np.abs(outs[2] - s) <= 3 * 2.0 ** -10 * (np.abs(s) + np.abs(outs[0]) + np.abs(outs[1])) + 1e-3).all()
+    # exact sample: 6 output pixels through the per-pixel oracle arithmetic
+    F2d = F1.astype(np.float32).reshape(-1, cd.K)
+    I2 = np.zeros((cd.C * 169 + 1, cd.N), np.float32)
+    I2[:-1] = I.astype(np.float32).reshape(-1, cd.N)
+    for (p, q) in [(0, 0), (0, 12), (6, 6), (12, 0), (12, 12), (3, 9)]:
+        rows = rm._conv_pixel_rows(cd, 0, p - 1, q - 1)
+        ref = np.dot(F2d.T, I2[rows, :])
+        absd = np.dot(np.abs(F2d).T, np.abs(I2[rows, :]))
+        assert_close(outs[0][:, 0, p, q, :], ref, rn16_tol(ref, absd, cd.C * 9), "pixel %d,%d" % (p, q))
+
+
+def test_layer_argument_checks(ng):
+    with pytest.raises(AssertionError):
+        ng.conv_layer(np.float16, 12, 3, 8, 1, 8, 8, 1, 3, 3)       # N % 8
+    with pytest.raises(AssertionError):
+        ng.conv_layer(np.float16, 16, 3, 12, 1, 8, 8, 1, 3, 3)      # K % 8
+    layer = ng.conv_layer(np.float16, 16, 3, 8, 1, 8, 8, 1, 3, 3)
+    with pytest.raises(AssertionError):
+        ng.fprop_conv(layer, ng.empty((3, 1, 8, 8, 8)), ng.empty(layer.dimF), ng.empty(layer.dimO))   # sizeI
+    with pytest.raises(TypeError):
+        ng.fprop_conv(layer, ng.empty(layer.dimI, dtype=np.float32), ng.empty(layer.dimF, dtype=np.float32),
+                      ng.empty(layer.dimO, dtype=np.float32))

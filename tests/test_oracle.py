@@ -1,0 +1,109 @@
+"""The oracle against what the reference itself pins (CPU only).
+
+ * golden vectors: outputs of the reference's own numpy validation code (benchmarks/conv_test.py,
+   benchmarks/pool_test.py) captured by tests/golden/make_golden.py;
+ * known-answer cases of the reference's tests: all-ones GEMM == k, zeros == 0
+   (kernels/C_interface/test.cu:27-55,70; benchmarks/gemm_test2.py:30-43), ones convolution
+   (benchmarks/conv_test.py:58-61);
+ * the unit-test recipe for element-wise results (nervanagpu/tests/test_tensor.py:46-57).
+"""
+import numpy as np
+import pytest
+
+from oracle import reference_math as rm
+from tests._util import golden, golden_names
+
+
+@pytest.mark.parametrize("name", golden_names("conv_"))
+def test_conv_oracle_matches_reference_numpy_path(name):
+    g = golden(name)
+    cd = rm.ConvDims(*[int(v) for v in g["cfg"]])
+    # same loop, same association order: identical fp32 results
+    np.testing.assert_array_equal(rm.conv_fprop(cd, g["I"], g["F"]), g["O"])
+    np.testing.assert_array_equal(rm.conv_update(cd, g["I"], g["E"]), g["gradF"])
+    np.testing.assert_allclose(rm.conv_bprop(cd, g["F"], g["E"]), g["gradI"], rtol=0, atol=1e-4)
+    # vectorised variants: same sums, other order
+    scale = np.abs(g["O"]).max()
+    np.testing.assert_allclose(rm.conv_fprop_fast(cd, g["I"], g["F"]), g["O"], rtol=0, atol=1e-5 * scale)
+    np.testing.assert_allclose(rm.conv_bprop_fast(cd, g["F"], g["E"]), g["gradI"], rtol=0,
+                               atol=1e-5 * np.abs(g["gradI"]).max())
+    np.testing.assert_allclose(rm.conv_update_fast(cd, g["I"], g["E"]), g["gradF"], rtol=0,
+                               atol=1e-5 * np.abs(g["gradF"]).max())
+
+
+@pytest.mark.parametrize("name", golden_names("pool_"))
+def test_pool_oracle_matches_reference_numpy_path(name):
+    g = golden(name)
+    pd = rm.PoolDims(*[int(v) for v in g["cfg"]])
+    O, gradI = rm.pool_max(pd, g["I"], E=g["O"])
+    np.testing.assert_array_equal(O, g["O"])
+    np.testing.assert_array_equal(gradI, g["gradI"])
+
+
+@pytest.mark.parametrize("size", [257, 256, 255, 129, 128, 127, 65, 64, 17, 16, 15])
+@pytest.mark.parametrize("op", ["nn", "nt", "tn"])
+def test_gemm_known_answers(size, op):
+    ones = np.ones((size, size), dtype=np.float16)
+    C = rm.gemm(ones, ones, a_t=op[0] == "t", b_t=op[1] == "t")
+    assert (C == size).all()
+    zeros = np.zeros((size, size), dtype=np.float16)
+    assert (rm.gemm(zeros, zeros, a_t=op[0] == "t", b_t=op[1] == "t") == 0).all()
+
+
+def test_gemm_epilogue_order():
+    A = np.array([[1.0, -2.0]], dtype=np.float16)
+    B = np.array([[3.0], [1.0]], dtype=np.float16)
+    C = np.array([[10.0]], dtype=np.float16)
+    # acc = 1 -> alpha -> relu -> + beta*C : relu acts before the beta term
+    assert rm.gemm(A, B, alpha=-1.0, beta=0.5, relu=True, C=C)[0, 0] == 5.0
+    assert rm.gemm(A, B, alpha=2.0, beta=0.5, relu=True, C=C)[0, 0] == 7.0
+
+
+def test_conv_ones_known_answer():
+    cd = rm.ConvDims(8, 3, 8, 1, 6, 6, 1, 3, 3, 0, 1, 1, 1, 1, 1)
+    O = rm.conv_fprop(cd, np.ones(cd.dimI, np.float32), np.ones(cd.dimF, np.float32))
+    # interior pixels see all 27 taps, corners 12
+    assert O[0, 0, 2, 2, 0] == 27 and O[0, 0, 0, 0, 0] == 12
+    assert cd.MPQ == (1, 6, 6)
+
+
+def test_layer_dims_formula():
+    # AlexNet conv1: (224 - 11 + 1 + 4) / 4 = 54.5 -> 55 (nervanagpu/layers.py:297-301)
+    cd = rm.ConvDims(128, 3, 64, 1, 224, 224, 1, 11, 11, 0, 2, 2, 1, 4, 4)
+    assert cd.MPQ == (1, 55, 55)
+    pd = rm.PoolDims(128, 64, 1, 55, 55, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2)
+    assert (pd.K,) + pd.MPQ == (64, 1, 27, 27)
+
+
+def test_pool_first_maximum_wins():
+    pd = rm.PoolDims(1, 1, 1, 2, 2, 1, 1, 2, 2)
+    I = np.full(pd.dimI, 3.0, dtype=np.float32)
+    O, gradI = rm.pool_max(pd, I, E=np.full(pd.dimO, 7.0, np.float32))
+    assert O.ravel()[0] == 3.0
+    assert gradI.ravel().tolist() == [7.0, 0.0, 0.0, 0.0]
+
+
+def test_cast_recipe_of_reference_unit_test():
+    x = np.array([-300.4, -0.5, 0.5, 1.5, 2.5, 126.6, 300.0], dtype=np.float32)
+    assert rm.cast_result(x, np.int8).tolist() == [-128, 0, 0, 2, 2, 127, 127]
+    assert rm.cast_result(x, np.uint8).tolist() == [0, 0, 0, 2, 2, 127, 255]
+    assert rm.cast_result(np.float32(0.1) + np.float32(0.2), np.float16) == np.float16(np.float32(0.1) + np.float32(0.2))
+
+
+def test_batch_norm_expression():
+    rng = np.random.default_rng(1005)
+    A = rng.uniform(0, 1, (64, 128)).astype(np.float16)
+    out = rm.batch_norm(A)
+    assert abs(out.mean(axis=1)).max() < 1e-5
+    assert abs(out.var(axis=1) - 1).max() < 0.02   # eps = 1e-3 on a variance of ~1/12
+
+
+def test_fp16_neighbours():
+    x = np.array([1.0, 1.0 + 2.0 ** -11, -(1.0 + 2.0 ** -11), 3e-6, 70000.0, 0.0], dtype=np.float32)
+    lo, hi = rm.fp16_neighbours(x)
+    assert lo[0] == hi[0] == np.float16(1.0)
+    assert lo[1] == np.float16(1.0) and hi[1] == np.float16(1.0 + 2.0 ** -10)
+    assert lo[2] == np.float16(-1.0) and hi[2] == np.float16(-(1.0 + 2.0 ** -10))
+    assert float(lo[3]) <= 3e-6 <= float(hi[3]) and float(hi[3]) - float(lo[3]) == 2.0 ** -24
+    assert lo[4] == hi[4] == np.float16(65504.0)
+    assert lo[5] == hi[5] == 0

@@ -1,0 +1,87 @@
+"""fprop_pool / bprop_pool: bit-exact against the reference's numpy path (B200 only)."""
+import numpy as np
+import pytest
+
+from oracle import reference_math as rm
+from tests._util import golden, golden_names
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(ng, cfg, I, E, dtype=np.float16):
+    layer = ng.pool_layer(dtype, "max", *cfg)
+    dI, dE = ng.array(I, dtype=dtype), ng.array(E, dtype=dtype)
+    dO, dB = ng.empty(layer.dimO, dtype=dtype), ng.empty(layer.dimI, dtype=dtype)
+    ng.fprop_pool(layer, dI, dO)
+    ng.bprop_pool(layer, dI, dE, dB)
+    return layer, dO.get(), dB.get()
+
+
+@pytest.mark.parametrize("name", golden_names("pool_"))
+def test_golden_vectors_of_the_reference_numpy_path(ng, name):
+    g = golden(name)
+    cfg = [int(v) for v in g["cfg"]]
+    # the reference script back-propagates its own output
+    layer, O, B = _run(ng, cfg, g["I"], g["O"].astype(np.float16))
+    assert np.array_equal(O.astype(np.float32), g["O"])
+    assert np.array_equal(B, g["gradI"].astype(np.float16))
+
+
+CASES = {
+    # (N, C, D, H, W, J, T, R, S, pad_j, pad_d, pad_h, pad_w, str_j, str_d, str_h, str_w)
+    "alexnet_3x3_s2_n64": (64, 8, 1, 13, 13, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
+    "vgg_2x2_n32": (32, 8, 1, 8, 8, 1, 1, 2, 2, 0, 0, 0, 0, 1, 1, 2, 2),
+    "config5_jtrs_2222": (32, 8, 4, 6, 6, 2, 2, 2, 2, 0, 0, 0, 0, 2, 2, 2, 2),
+    "padded_overlapping": (16, 5, 1, 9, 9, 2, 1, 3, 3, 1, 0, 1, 1, 1, 1, 2, 2),
+    "n4_scalar_lanes": (4, 3, 1, 7, 7, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
+    "stride_larger_than_window": (8, 2, 1, 9, 9, 1, 1, 2, 2, 0, 0, 0, 0, 1, 1, 3, 3),
+    "maxout_over_feature_maps": (64, 16, 1, 1, 1, 4, 1, 1, 1, 0, 0, 0, 0, 4, 1, 1, 1),
+}
+
+
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_bit_exact_against_oracle(ng, name):
+    cfg = CASES[name]
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(1005)
+    # few distinct values: plenty of ties, so the first-maximum rule is exercised
+    I = (rng.integers(0, 12, pd.dimI) / 8.0).astype(np.float16)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float16)
+    refO, refB = rm.pool_max(pd, I, E)
+    layer, O, B = _run(ng, cfg, I, E)
+    assert layer.dimO == pd.dimO
+    assert np.array_equal(O, refO.astype(np.float16))
+    assert np.array_equal(B, refB.astype(np.float16))
+
+
+def test_fp32_pooling(ng):
+    cfg = CASES["alexnet_3x3_s2_n64"]
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(2)
+    I = rng.uniform(0, 1, pd.dimI).astype(np.float32)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float32)
+    refO, refB = rm.pool_max(pd, I, E)
+    _, O, B = _run(ng, cfg, I, E, dtype=np.float32)
+    assert np.array_equal(O, refO)
+    assert np.array_equal(B, refB)
+
+
+def test_full_size_alexnet_pool1_properties(ng):
+    """pool1 at BASELINE size (N=128, C=64, 55x55 -> 27x27, 3x3 stride 2): size-independent checks.
+    Every output is >= each tap of its window and equals one of them; bprop conserves the sum of E
+    (each error lands on exactly one input) and puts nothing where the input is not a window max."""
+    cfg = (128, 64, 1, 55, 55, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2)
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(1003)
+    I = rng.uniform(0, 1, pd.dimI).astype(np.float16)
+    E = (rng.integers(1, 5, pd.dimO) / 4.0).astype(np.float16)
+    _, O, B = _run(ng, cfg, I, E)
+    taps = np.stack([I[:, :, r:r + 53:2, s:s + 53:2, :] for r in range(3) for s in range(3)])
+    assert np.array_equal(O, taps.max(axis=0))
+    assert abs(float(B.astype(np.float64).sum()) - float(E.astype(np.float64).sum())) <= 1e-6 * E.size
+    assert (B >= 0).all() and (B[:, :, 55 - 0:, :, :] == 0).all()
+    # sampled channels against the oracle, bit for bit
+    sub = rm.PoolDims(128, 2, 1, 55, 55, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2)
+    refO, refB = rm.pool_max(sub, I[5:7], E[5:7])
+    assert np.array_equal(O[5:7], refO.astype(np.float16))
+    assert np.array_equal(B[5:7], refB.astype(np.float16))
