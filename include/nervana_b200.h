@@ -63,6 +63,9 @@ int ng_event_elapsed_ms(void* start, void* end, float* ms);
  * kernel abandoned one of its bounded waits. */
 int ng_sync(void);
 int ng_device_status(int* code);
+/* Number of kernels this library has launched so far in this process (its own kernels and the
+ * generated element-wise ones; memcpy / memset / NCCL calls are not counted). */
+int ng_launch_count(unsigned long long* count);
 
 /* ---- GEMM --------------------------------------------------------------------------------
  * C[m x n] = relu?(alpha * op(A) * op(B)) + beta * C, row-major, fp16 storage, fp32 accumulate.

@@ -1,0 +1,168 @@
+"""Conv + pool stacks of the benchmark networks and the loop that times them.
+
+Follows the reference's benchmark driver (benchmarks/convnet-benchmarks.py:250-403) for the
+convolutional part of its networks: forward chain with the ReLU fused into each convolution,
+backward chain in reverse with, per convolution, the ReLU mask on the incoming deltas
+(Layer.bprop_relu), bprop_conv (skipped for the first layer, which needs no input gradient),
+update_conv, and the SGD step (nervanagpu/layers.py:87-96,483-502). Weights and weight gradients
+of all layers live in two flat buffers so that one all-reduce and one fused SGD kernel serve the
+whole stack when the minibatch is split over several GPUs.
+"""
+import ctypes
+
+import numpy as np
+
+from . import _lib
+from .layers import ConvLayer
+
+# (kind, params): conv = (K, R, S, pad, stride), pool = (R, S, stride)
+ALEXNET = {
+    "name": "alexnet_conv_stack", "N": 128, "C": 3, "H": 224, "W": 224,
+    "layers": [("conv", (64, 11, 11, 2, 4)), ("pool", (3, 3, 2)),
+               ("conv", (192, 5, 5, 2, 1)), ("pool", (3, 3, 2)),
+               ("conv", (384, 3, 3, 1, 1)), ("conv", (256, 3, 3, 1, 1)), ("conv", (256, 3, 3, 1, 1)),
+               ("pool", (3, 3, 2))],
+}
+VGG_A = {
+    "name": "vgg_a_conv_stack", "N": 64, "C": 3, "H": 224, "W": 224,
+    "layers": [("conv", (64, 3, 3, 1, 1)), ("pool", (2, 2, 2)),
+               ("conv", (128, 3, 3, 1, 1)), ("pool", (2, 2, 2)),
+               ("conv", (256, 3, 3, 1, 1)), ("conv", (256, 3, 3, 1, 1)), ("pool", (2, 2, 2)),
+               ("conv", (512, 3, 3, 1, 1)), ("conv", (512, 3, 3, 1, 1)), ("pool", (2, 2, 2)),
+               ("conv", (512, 3, 3, 1, 1)), ("conv", (512, 3, 3, 1, 1)), ("pool", (2, 2, 2))],
+}
+NETWORKS = {"alexnet": ALEXNET, "vgg_a": VGG_A}
+
+
+class ConvStack(object):
+    """A chain of ConvLayer / PoolLayer objects with their activations, deltas and weights."""
+
+    def __init__(self, ng, net, N=None, seed=1003, learning_rate=-1e-4, comm=None):
+        self.ng = ng
+        self.net = net
+        self.N = N = net["N"] if N is None else N
+        self.comm = comm                      # ng_comm handle or None (single GPU)
+        self.lr = learning_rate
+        rng = np.random.default_rng(seed)
+        C, H, W = net["C"], net["H"], net["W"]
+        self.layers = []
+        for kind, prm in net["layers"]:
+            if kind == "conv":
+                K, R, S, pad, stride = prm
+                layer = ng.conv_layer(np.float16, N, C, K, 1, H, W, 1, R, S, 0, pad, pad, 1, stride, stride)
+                C, H, W = K, layer.P, layer.Q
+            else:
+                R, S, stride = prm
+                layer = ng.pool_layer(np.float16, "max", N, C, 1, H, W, 1, 1, R, S, 0, 0, 0, 0, 1, 1, stride, stride)
+                H, W = layer.P, layer.Q
+            self.layers.append(layer)
+        self.convs = [l for l in self.layers if isinstance(l, ConvLayer)]
+
+        # flat weight / gradient buffers with per-layer views
+        total_f = sum(l.sizeF for l in self.convs)
+        self.weights_flat = ng.empty((total_f,), dtype=np.float16)
+        self.grads_flat = ng.empty((total_f,), dtype=np.float32)
+        w_host = np.empty(total_f, dtype=np.float16)
+        off = 0
+        for l in self.convs:
+            w_host[off:off + l.sizeF] = rng.normal(0.0, 0.01, l.sizeF).astype(np.float16)
+            l.weights = self.weights_flat[off:off + l.sizeF].reshape(l.dimF)
+            l.updat_out = self.grads_flat[off:off + l.sizeF].reshape(l.dimF)
+            off += l.sizeF
+        self.weights_flat.set(w_host)
+
+        # activations and deltas
+        self.input = ng.empty(self.layers[0].dimI, dtype=np.float16)
+        self.acts = [ng.empty(l.dimO, dtype=np.float16) for l in self.layers]
+        self.deltas = [None] + [ng.empty(l.dimI, dtype=np.float16) for l in self.layers[1:]]
+        self.top_delta = ng.empty(self.layers[-1].dimO, dtype=np.float16)
+        self.host_input = rng.uniform(0.0, 1.0, self.layers[0].dimI).astype(np.float16)
+        self.input.set(self.host_input)
+        top = (rng.uniform(-1.0, 1.0, self.layers[-1].dimO) * 0.125).astype(np.float16)
+        self.top_delta.set(top)
+        self.probe = None    # optional callable(name, layer, launch) used to time single launches
+
+        # work per step on this GPU: fprop + update for every conv, bprop for all but the first
+        self.flops_fprop = sum(l.flops for l in self.convs)
+        self.flops_bprop = sum(l.flops for l in self.convs[1:]) + sum(l.flops for l in self.convs)
+        self.flops = self.flops_fprop + self.flops_bprop
+
+    # ------------------------------------------------------------------------------------
+    def _run(self, name, layer, launch):
+        if self.probe is not None:
+            self.probe(name, layer, launch)
+        else:
+            launch()
+
+    def fprop(self):
+        ng = self.ng
+        x = self.input
+        for i, l in enumerate(self.layers):
+            y = self.acts[i]
+            if isinstance(l, ConvLayer):
+                self._run("fprop_conv", l, lambda l=l, x=x, y=y: ng.fprop_conv(l, x, l.weights, y, relu=True))
+            else:
+                self._run("fprop_pool", l, lambda l=l, x=x, y=y: ng.fprop_pool(l, x, y))
+            x = y
+        return x
+
+    def bprop(self):
+        ng = self.ng
+        grad = self.top_delta
+        for i in range(len(self.layers) - 1, -1, -1):
+            l = self.layers[i]
+            x = self.input if i == 0 else self.acts[i - 1]
+            dx = self.deltas[i]
+            if isinstance(l, ConvLayer):
+                y = self.acts[i]
+                self._run("bprop_relu", l, lambda grad=grad, y=y: _relu_mask(grad, y))
+                if dx is not None:
+                    self._run("bprop_conv", l, lambda l=l, grad=grad, dx=dx: ng.bprop_conv(l, l.weights, grad, dx))
+                self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
+            else:
+                self._run("bprop_pool", l, lambda l=l, x=x, grad=grad, dx=dx: ng.bprop_pool(l, x, grad, dx))
+            grad = dx
+        if self.comm is not None:
+            self._run("allreduce_dW", None, self.allreduce_grads)
+        self._run("grad_descent", None, self.grad_descent)
+
+    def allreduce_grads(self):
+        _lib.check(self.ng.lib.ng_comm_allreduce_f32(self.comm, self.grads_flat.ptr, self.grads_flat.size,
+                                                     self.ng.stream))
+
+    def grad_descent(self):
+        # one fused kernel over the flat buffers: weights += grads * learning_rate
+        w, g = self.weights_flat, self.grads_flat
+        w[:] = w + g * self.lr
+
+    def step(self):
+        self.fprop()
+        self.bprop()
+
+    def set_input(self, host_array):
+        self.input.set(host_array)
+
+
+def _relu_mask(grad, act):
+    grad[:] = grad * (act > 0)
+
+
+class StepTimer(object):
+    """CUDA-event timing of a callable on the backend's stream."""
+
+    def __init__(self, ng):
+        self.ng = ng
+        self.start, self.end = ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.check(ng.lib.ng_event_create(ctypes.byref(self.start)))
+        _lib.check(ng.lib.ng_event_create(ctypes.byref(self.end)))
+
+    def time_ms(self, fn, repeat):
+        lib, stream = self.ng.lib, self.ng.stream
+        _lib.check(lib.ng_event_record(self.start, stream))
+        for _ in range(repeat):
+            fn()
+        _lib.check(lib.ng_event_record(self.end, stream))
+        _lib.check(lib.ng_event_sync(self.end))
+        ms = ctypes.c_float()
+        _lib.check(lib.ng_event_elapsed_ms(self.start, self.end, ctypes.byref(ms)))
+        return ms.value

@@ -289,7 +289,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   if (!tc) {
     conv_fprop_simt<<<launch_1d(g.sizeO(), 256, c), 256, 0, stream>>>(
         g, static_cast<const __half*>(I), static_cast<const __half*>(F), static_cast<__half*>(O), alpha, relu);
-    NG_CUDA(cudaGetLastError());
+    NG_CHECK_LAUNCH();
     return NG_OK;
   }
   const int RST = g.T * g.R * g.S;
@@ -334,7 +334,7 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   if (!tc) {
     conv_bprop_simt<<<launch_1d(g.sizeI(), 256, c), 256, 0, stream>>>(
         g, static_cast<const __half*>(F), static_cast<const __half*>(E), static_cast<__half*>(gradI), alpha);
-    NG_CUDA(cudaGetLastError());
+    NG_CHECK_LAUNCH();
     return NG_OK;
   }
   const int RST = g.T * g.R * g.S;
@@ -415,7 +415,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     __half* col = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(c->ws) + col_off);
     const long long total = 1ll * g.C * RST * span / 8;
     im2col_kernel<<<launch_1d(total, 256, c), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
-    NG_CUDA(cudaGetLastError());
+    NG_CHECK_LAUNCH();
     GemmCall gc = {};
     gc.A = col; gc.B = E; gc.C = gradF; gc.a_t = 0; gc.b_t = 1;
     gc.m = g.C * RST; gc.n = g.K;
@@ -428,7 +428,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   const long long warps = g.sizeF();
   conv_update_simt<<<launch_1d(warps * 32, 256, c), 256, 0, stream>>>(
       g, static_cast<const __half*>(I), static_cast<const __half*>(E), gradF, out_f32, alpha);
-  NG_CUDA(cudaGetLastError());
+  NG_CHECK_LAUNCH();
   return NG_OK;
 }
 

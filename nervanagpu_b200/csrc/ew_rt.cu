@@ -76,7 +76,10 @@ static int compile_to_cubin(const char* source, int fast_math, std::vector<char>
   const char* cuda_home = getenv("CUDA_HOME");
   std::string inc = std::string("--include-path=") + (cuda_home ? cuda_home : "/usr/local/cuda") + "/include";
   std::vector<const char*> opts = {"--gpu-architecture=sm_100a", "--std=c++17", "-default-device", inc.c_str()};
+  // Without fast math every operation rounds once, in source order, like the numpy fp32 oracle:
+  // no contraction of a*b+c into an fma.
   if (fast_math) opts.push_back("--use_fast_math");
+  else opts.push_back("--fmad=false");
   r = nvrtcCompileProgram(prog, static_cast<int>(opts.size()), opts.data());
   size_t log_size = 0;
   nvrtcGetProgramLogSize(prog, &log_size);
@@ -142,6 +145,7 @@ int ng_ew_launch(void* handle, unsigned gx, unsigned gy, unsigned gz, unsigned b
   CUresult cr = api.launchKernel(k->fn, gx, gy, gz, bx, by, bz, shared_bytes, static_cast<CUstream>(stream), args,
                                  nullptr);
   if (cr != CUDA_SUCCESS) return fail(NG_ERR_CUDA, "cuLaunchKernel failed (%d)", static_cast<int>(cr));
+  count_launch();
   return NG_OK;
 }
 

@@ -141,7 +141,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     s.out_f32 = g.out_f32; s.ea = ea;
     dim3 grid((g.n + 63) / 64, (g.m + 63) / 64, g.batch);
     gemm_simt_kernel<<<grid, 256, 0, stream>>>(s);
-    NG_CUDA(cudaGetLastError());
+    NG_CHECK_LAUNCH();
     return NG_OK;
   }
 

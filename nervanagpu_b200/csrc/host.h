@@ -30,6 +30,14 @@ int cuda_fail(cudaError_t e, const char* what);
     if (_e != cudaSuccess) return ::ngb::cuda_fail(_e, #expr); \
   } while (0)
 
+// Count of kernels this library has launched (all devices, all streams); read by ng_launch_count.
+void count_launch();
+#define NG_CHECK_LAUNCH()            \
+  do {                               \
+    NG_CUDA(cudaGetLastError());     \
+    ::ngb::count_launch();           \
+  } while (0)
+
 // Context of the current device (initialised on first use). Null + error set on failure.
 DeviceCtx* current_ctx();
 // Ensure the workspace holds at least `bytes`; may synchronise the device when it has to grow.

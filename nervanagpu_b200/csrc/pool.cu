@@ -199,7 +199,7 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
       pool_bprop_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(
           g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out));
   }
-  NG_CUDA(cudaGetLastError());
+  NG_CHECK_LAUNCH();
   return NG_OK;
 }
 

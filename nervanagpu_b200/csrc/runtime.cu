@@ -1,6 +1,7 @@
 // Runtime services of the C-ABI: device selection, memory, copies, memsets, streams, events,
 // error strings. They stand in for the PyCUDA calls the reference's host code makes
 // (nervanagpu/nervanagpu.py:133,145,298-311,712-729,1333-1350; nervanagpu/layers.py:775-778).
+#include <atomic>
 #include <cstdarg>
 #include <cstdio>
 #include <cstring>
@@ -27,6 +28,9 @@ int fail(int code, const char* fmt, ...) {
 int cuda_fail(cudaError_t e, const char* what) {
   return fail(NG_ERR_CUDA, "CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
 }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static std::mutex g_ctx_mutex;
 static DeviceCtx g_ctx[64];
@@ -152,7 +156,7 @@ int fill(void* dst, T value, size_t count, void* stream) {
   if (blocks > cap) blocks = cap;
   fill_kernel<T><<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<T*>(dst), value, count);
-  NG_CUDA(cudaGetLastError());
+  NG_CHECK_LAUNCH();
   return NG_OK;
 }
 }  // namespace
@@ -297,6 +301,12 @@ int ng_device_status(int* code) {
     cudaMemset(c->status, 0, sizeof(int));
     return fail(NG_ERR_TIMEOUT, "a kernel gave up a bounded wait (site %d)", v);
   }
+  return NG_OK;
+}
+
+int ng_launch_count(unsigned long long* count) {
+  if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
+  *count = g_launches.load(std::memory_order_relaxed);
   return NG_OK;
 }
 

@@ -113,7 +113,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     return fail(NG_ERR_INVALID_ARG, "internal: stage layout is not a whole number of boxes");
   }
   igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, launch);
-  NG_CUDA(cudaGetLastError());
+  NG_CHECK_LAUNCH();
   if (p.splits > 1) {
     EpiArgs ea;
     ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
@@ -123,7 +123,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     const int blocks = static_cast<int>(std::min<long long>((groups + threads - 1) / threads, c->sm_count * 8ll));
     splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p.ws, p.splits, p.nz, p.M, p.N, p.C, p.Cold, p.ldc,
                                                          p.c_zstride, p.out_f32, p.vec_ok, ea);
-    NG_CUDA(cudaGetLastError());
+    NG_CHECK_LAUNCH();
   }
   return NG_OK;
 }

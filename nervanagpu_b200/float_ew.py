@@ -271,6 +271,8 @@ def _analyse(args):
     contiguous = True
     size = None
     same_size = True
+    shape0 = None
+    same_shape = True
     for arg in args:
         if type(arg) is dict:
             op_name = arg["op"]
@@ -286,20 +288,27 @@ def _analyse(args):
         elif isinstance(arg, GPUTensor):
             if out is None:
                 out = arg
-            if _is_2d_special(arg):
-                broadcast = True
-            elif arg.is_trans:
+            if arg.is_trans and len(arg.shape) > 1 and min(arg.shape) > 1:
                 transpose = True
             elif arg.take_array:
                 takeop = True
+            elif _is_2d_special(arg):
+                broadcast = True
             elif not arg.is_contiguous:
                 contiguous = False
+            if not arg.is_contiguous:
+                contiguous = False
             if size is None:
-                size = arg.size
-            elif arg.size != size:
-                same_size = False
+                size, shape0 = arg.size, tuple(arg.shape)
+            else:
+                same_size = same_size and arg.size == size
+                same_shape = same_shape and tuple(arg.shape) == shape0
     if out is None:
         raise TypeError("the first operand of an assignment must be a GPUTensor")
+    # Vectors and single rows/columns only broadcast when they meet a tensor of another shape;
+    # operands that all share one shape (any rank) are walked in memory order.
+    if same_shape:
+        broadcast = False
     flat = not (broadcast or reduction or transpose or takeop) and contiguous and same_size
 
     tensors = []       # slot -> dict(tensor, shape, strides, take)
