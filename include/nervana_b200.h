@@ -88,6 +88,24 @@ int ng_hgemm_batched(const void* A, const void* B, void* C, int a_t, int b_t, in
                      unsigned int rng_offset, int batch_grid, int batch_loops, long long ldaz, long long ldbz,
                      long long ldcz, void* stream);
 
+/* ng_hgemm for callers that must not allocate device memory. It has no counterpart in the
+ * reference. Same arguments and result contract as ng_hgemm, restricted to operands TMA can
+ * address (16-byte aligned, leading dimensions multiples of 8), always computed as a split-K
+ * product whose fp32 partial tiles live in a fixed device array inside the library instead of
+ * the cudaMalloc'ed workspace ng_hgemm grows on demand. The call makes no cudaMalloc / cudaFree
+ * and calls no allocating routine.
+ *   - limit: 2 * m * n * 4 bytes must fit in NG_STATIC_SCRATCH_BYTES, else NG_ERR_TOO_LARGE;
+ *   - the array costs NG_STATIC_SCRATCH_BYTES of memory on every GPU that loads the library;
+ *   - the first call on each device looks up the array's device address (and sets a function
+ *     attribute); make that first call outside any stream capture;
+ *   - all calls share the one array: calls that can overlap on the GPU (different streams or
+ *     threads) race on it; issue them on one stream or serialise them yourself. Nothing in the
+ *     array has to start at zero: every call overwrites the part it later reads. */
+#define NG_STATIC_SCRATCH_BYTES (16u << 20)
+int ng_hgemm_static_scratch(const void* A, const void* B, void* C, int a_t, int b_t, int m, int n, int k, int lda,
+                            int ldb, int ldc, float alpha, float beta, int relu, int sr_bits,
+                            unsigned long long seed, unsigned int rng_offset, void* stream);
+
 /* ---- convolution ---------------------------------------------------------------------------
  * Activations are (C,D,H,W,N), filters (C,T,R,S,K), outputs (K,M,P,Q,N), all fp16, N innermost.
  * The descriptor carries what ConvLayer stores (nervanagpu/layers.py:281-313); output

@@ -70,6 +70,9 @@ SIGNATURES = {
                          c_float, c_float, c_int, c_int, c_ulonglong, c_uint, c_void_p]),
     "ng_hgemm_simt": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                               c_float, c_float, c_int, c_int, c_ulonglong, c_uint, c_void_p]),
+    "ng_hgemm_static_scratch": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_int, c_float, c_float, c_int, c_int, c_ulonglong, c_uint,
+                                        c_void_p]),
     "ng_hgemm_batched": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                  c_int, c_float, c_float, c_int, c_int, c_ulonglong, c_uint, c_int, c_int,
                                  c_longlong, c_longlong, c_longlong, c_void_p]),

@@ -1,7 +1,9 @@
 // Host side of the tensor-core engine: UMMA descriptor construction, ring sizing, split-K
 // choice and the launch itself.
 #include <algorithm>
+#include <mutex>
 
+#include "../../include/nervana_b200.h"
 #include "epilogue.cuh"
 #include "host.h"
 #include "igemm_tc_kernel.cuh"
@@ -129,3 +131,150 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
 }
 
 }  // namespace ngb
+
+// ------------------------------------------------------------------------------------------
+// Split-K GEMM that allocates nothing.
+//
+// Some hosts of this library may not allocate device memory at the point where they call it: a
+// process that has handed its whole memory budget to its own pool or arena, a real-time loop
+// that must not take the allocator's lock or risk an implicit synchronisation, a plugin whose
+// embedding application forbids cudaMalloc after start-up. ng_hgemm cannot serve them, because
+// its split-K path keeps the fp32 partial tiles in a workspace that the library grows with
+// cudaMalloc on demand (and its device status word is allocated on first use). This entry point
+// keeps both in file-scope device arrays of fixed size, which every GPU that loads the library
+// carries until the process exits.
+// ------------------------------------------------------------------------------------------
+namespace ngb {
+namespace {
+
+constexpr size_t kStaticScratchBytes = NG_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) float g_static_scratch[kStaticScratchBytes / sizeof(float)];
+static __device__ __align__(256) int g_static_status[64];
+
+// Device addresses of the two arrays, looked up once per device. In host code the array names
+// are only handles for cudaGetSymbolAddress; a kernel must be given the looked-up pointers.
+struct StaticSlots {
+  float* scratch = nullptr;
+  int* status = nullptr;
+  int sm_count = 0;
+  bool ready = false;
+};
+StaticSlots g_static_slots[64];
+std::mutex g_static_mutex;
+
+int static_setup(int dev, StaticSlots** out) {
+  if (dev < 0 || dev >= 64) return fail(NG_ERR_INVALID_ARG, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  StaticSlots& s = g_static_slots[dev];
+  if (!s.ready) {
+    int major = 0;
+    NG_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+    if (major != 10) return fail(NG_ERR_UNSUPPORTED, "device %d is not sm_100", dev);
+    NG_CUDA(cudaDeviceGetAttribute(&s.sm_count, cudaDevAttrMultiProcessorCount, dev));
+    void* p = nullptr;
+    NG_CUDA(cudaGetSymbolAddress(&p, g_static_scratch));
+    s.scratch = static_cast<float*>(p);
+    NG_CUDA(cudaGetSymbolAddress(&p, g_static_status));
+    s.status = static_cast<int*>(p);
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    s.ready = true;
+  }
+  *out = &s;
+  return NG_OK;
+}
+
+}  // namespace
+}  // namespace ngb
+
+using namespace ngb;
+
+extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, int a_t, int b_t, int m, int n, int k,
+                                       int lda, int ldb, int ldc, float alpha, float beta, int relu, int sr_bits,
+                                       unsigned long long seed, unsigned int rng_offset, void* stream_) {
+  if (!A || !B || !C) return fail(NG_ERR_INVALID_ARG, "null operand");
+  if (m <= 0 || n <= 0 || k <= 0) return fail(NG_ERR_INVALID_ARG, "m, n, k must be positive");
+  if (a_t && b_t) return fail(NG_ERR_UNSUPPORTED, "op 'tt' is not supported");
+  if (sr_bits < 0 || sr_bits > 10) return fail(NG_ERR_INVALID_ARG, "stochastic rounding keeps 1..10 mantissa bits");
+  if (lda < (a_t ? m : k) || ldb < (b_t ? k : n) || ldc < n) return fail(NG_ERR_INVALID_ARG, "leading dimension too small");
+  auto tma_ok = [](const void* p, long long ld) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0 && (ld & 7) == 0; };
+  if (!tma_ok(A, lda) || !tma_ok(B, ldb))
+    return fail(NG_ERR_UNSUPPORTED, "operands must be 16-byte aligned with leading dimensions that are multiples of 8");
+  // two partitions of fp32 partials is the least this variant uses
+  const size_t tile_bytes = static_cast<size_t>(m) * n * sizeof(float);
+  if (2 * tile_bytes > kStaticScratchBytes)
+    return fail(NG_ERR_TOO_LARGE, "m*n = %lld exceeds the static scratch: 2 * m * n * 4 bytes must fit in %zu bytes",
+                static_cast<long long>(m) * n, kStaticScratchBytes);
+  int dev = -1;
+  NG_CUDA(cudaGetDevice(&dev));
+  StaticSlots* slots = nullptr;
+  int rc = static_setup(dev, &slots);
+  if (rc != NG_OK) return rc;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+
+  TcParams p = {};
+  p.mode = TC_GEMM;
+  p.block_n = n <= 64 ? 64 : (n <= 128 ? 128 : 256);
+  p.M = m; p.N = n;
+  p.tiles_m = (m + kTileM - 1) / kTileM;
+  p.tiles_n = (n + p.block_n - 1) / p.block_n;
+  p.nz = 1;
+  p.num_kb = (k + kChunk - 1) / kChunk;
+  TcOperandLayout lay;
+  lay.a_mn_major = a_t ? 1 : 0;
+  lay.b_mn_major = b_t ? 0 : 1;
+  lay.kb_rows = kChunk;
+  tc_fill_mma(p, lay);
+  p.C = C; p.Cold = beta != 0.0f ? C : nullptr;
+  p.ldc = ldc; p.c_zstride = 0;
+  p.alpha = alpha; p.beta = beta; p.relu = relu; p.sr_bits = sr_bits; p.out_f32 = 0;
+  p.vec_ok = (reinterpret_cast<uintptr_t>(C) & 15u) == 0 && ldc % 8 == 0;
+  p.seed_lo = static_cast<uint32_t>(seed); p.seed_hi = static_cast<uint32_t>(seed >> 32); p.rng_offset = rng_offset;
+
+  // partitions: enough to occupy the SMs, never more than the scratch holds, at least two
+  long long want = (slots->sm_count + static_cast<long long>(p.tiles_m) * p.tiles_n - 1) /
+                   (static_cast<long long>(p.tiles_m) * p.tiles_n);
+  want = std::min<long long>(want, static_cast<long long>(kStaticScratchBytes / tile_bytes));
+  want = std::min<long long>(want, 32);
+  want = std::max<long long>(want, 2);
+  p.splits = static_cast<int>(std::min<long long>(want, p.num_kb));
+  p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
+  p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;
+  p.status = slots->status;
+  p.ws = slots->scratch;     // device address from cudaGetSymbolAddress, never the symbol itself
+
+  CUtensorMap mapA, mapB;
+  {
+    uint64_t dims[5] = {1, 1, 1, 1, 1};
+    uint64_t str[4];
+    uint32_t box[5] = {kChunk, 1, 1, 1, 1};
+    if (a_t) { dims[0] = m; dims[1] = k; box[1] = kChunk; } else { dims[0] = k; dims[1] = m; box[1] = kTileM; }
+    str[0] = static_cast<uint64_t>(lda) * 2; str[1] = str[0] * dims[1]; str[2] = str[1]; str[3] = str[1];
+    rc = make_tensor_map(&mapA, A, dims, str, box);
+    if (rc != NG_OK) return rc;
+  }
+  {
+    uint64_t dims[5] = {1, 1, 1, 1, 1};
+    uint64_t str[4];
+    uint32_t box[5] = {kChunk, 1, 1, 1, 1};
+    if (b_t) { dims[0] = k; dims[1] = n; box[1] = p.block_n; } else { dims[0] = n; dims[1] = k; box[1] = kChunk; }
+    str[0] = static_cast<uint64_t>(ldb) * 2; str[1] = str[0] * dims[1]; str[2] = str[1]; str[3] = str[1];
+    rc = make_tensor_map(&mapB, B, dims, str, box);
+    if (rc != NG_OK) return rc;
+  }
+
+  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.splits;
+  const int grid = static_cast<int>(std::min<long long>(total, slots->sm_count));
+  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
+  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, p);
+  NG_CHECK_LAUNCH();
+  EpiArgs ea;
+  ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;
+  ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = rng_offset;
+  if (p.splits > 1) {
+    const long long groups = static_cast<long long>(m) * ((n + 7) / 8);
+    const int blocks = static_cast<int>(std::min<long long>((groups + 255) / 256, slots->sm_count * 8ll));
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.ws, p.splits, 1, m, n, C, p.Cold, ldc, 0, 0, p.vec_ok, ea);
+    NG_CHECK_LAUNCH();
+  }
+  return NG_OK;
+}
