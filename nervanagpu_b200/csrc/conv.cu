@@ -284,8 +284,35 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   if (!c) return NG_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
   const ChunkMode mode = pick_chunk_mode(g.N, g.Q, g.str_w);
-  const bool tc = path != NG_PATH_SIMT && mode != CH_NONE && aligned16(I) && aligned16(F) && aligned16(O);
+  const bool al = aligned16(I) && aligned16(F) && aligned16(O);
+  const bool tc = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al;
   if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
+  {
+    // Few input channels (first layers): one tap per k-block would feed the tensor core 3 useful
+    // rows out of 16, so gather the patches once and run a dense GEMM over all C*T*R*S rows:
+    //   O[K x span] = F2d[crst][k]^T * col[crst][span]
+    const int RST = g.T * g.R * g.S;
+    const long long span = 1ll * g.M * g.P * g.Q * g.N;
+    const bool small_c = g.C < 16 && path == NG_PATH_AUTO;
+    const bool im2col = (small_c || path == NG_PATH_IM2COL) && al && span <= 0x7fffffffll &&
+                        1ll * g.C * RST * span * 2 <= (6ll << 30);
+    if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
+    if (im2col) {
+      const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
+      rc = ensure_workspace(c, col_bytes);
+      if (rc != NG_OK) return rc;
+      __half* col = reinterpret_cast<__half*>(c->ws);
+      im2col_kernel<<<launch_1d(1ll * g.C * RST * span / 8, 256, c), 256, 0, stream>>>(
+          g, static_cast<const __half*>(I), col);
+      NG_CHECK_LAUNCH();
+      GemmCall gc = {};
+      gc.A = F; gc.B = col; gc.C = O; gc.a_t = 1; gc.b_t = 0;
+      gc.m = g.K; gc.n = static_cast<int>(span); gc.k = g.C * RST;
+      gc.lda = g.K; gc.ldb = span; gc.ldc = span;
+      gc.alpha = alpha; gc.beta = 0.0f; gc.relu = relu; gc.batch = 1; gc.loops = 1;
+      return run_gemm(gc, stream);
+    }
+  }
   if (!tc) {
     conv_fprop_simt<<<launch_1d(g.sizeO(), 256, c), 256, 0, stream>>>(
         g, static_cast<const __half*>(I), static_cast<const __half*>(F), static_cast<__half*>(O), alpha, relu);

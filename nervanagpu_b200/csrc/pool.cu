@@ -175,6 +175,166 @@ __global__ void pool_bprop_kernel(PoolGeo g, const T* __restrict__ I, const T* _
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Specialised 2-D windows (J = T = 1, no padding, fp16, N % 8 == 0): compile-time R,S and strides,
+// grid (x: q|block column and image lane, y: p|block row, z: channel) so no index division.
+// ------------------------------------------------------------------------------------------
+struct Lanes8 {
+  float v[8];
+};
+__device__ __forceinline__ Lanes8 load8(const __half* p) {
+  const uint4 r = *reinterpret_cast<const uint4*>(p);
+  const __half2* h = reinterpret_cast<const __half2*>(&r);
+  Lanes8 o;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const float2 f = __half22float2(h[i]);
+    o.v[2 * i] = f.x;
+    o.v[2 * i + 1] = f.y;
+  }
+  return o;
+}
+__device__ __forceinline__ void store8(__half* p, const float (&v)[8]) {
+  uint4 r;
+  __half2* h = reinterpret_cast<__half2*>(&r);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) h[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  *reinterpret_cast<uint4*>(p) = r;
+}
+
+// max and first-argmax (tap id r*S+s) of window (p,q) of channel plane `plane` for 8 images
+template <int R, int S, int SH, int SW>
+__device__ __forceinline__ void window2d(const __half* __restrict__ plane, int H, int W, int N, int p, int q, int n0,
+                                         float (&best)[8], int (&arg)[8]) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) { best[i] = -FLT_MAX; arg[i] = 0; }
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    const int y = p * SH + r;
+    if (y >= H) break;
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int x = q * SW + s;
+      if (x >= W) break;
+      const Lanes8 t = load8(plane + (static_cast<long long>(y) * W + x) * N + n0);
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (t.v[i] > best[i]) { best[i] = t.v[i]; arg[i] = r * S + s; }
+    }
+  }
+}
+
+template <int R, int S, int SH, int SW>
+__global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O, int H,
+                                                          int W, int N, int P, int Q) {
+  const int nvec = N >> 3;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int q = t / nvec;
+  if (q >= Q) return;
+  const int n0 = (t - q * nvec) << 3;
+  const int p = blockIdx.y, c = blockIdx.z;
+  float best[8];
+  int arg[8];
+  window2d<R, S, SH, SW>(I + static_cast<long long>(c) * H * W * N, H, W, N, p, q, n0, best, arg);
+  store8(O + ((static_cast<long long>(c) * P + p) * Q + q) * N + n0, best);
+}
+
+// Each thread owns the SH x SW block of inputs at block coordinates (a, b). The windows that
+// overlap the block are visited in increasing (p, q) order; a window's error goes to the block
+// input that is its first maximum. Same sums in the same order as the per-element gather.
+template <int R, int S, int SH, int SW>
+__global__ void __launch_bounds__(256) pool2d_bprop_kernel(const __half* __restrict__ I, const __half* __restrict__ E,
+                                                          __half* __restrict__ dI, int H, int W, int N, int P, int Q,
+                                                          int BW) {
+  constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
+  const int nvec = N >> 3;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = t / nvec;
+  if (b >= BW) return;
+  const int n0 = (t - b * nvec) << 3;
+  const int a = blockIdx.y, c = blockIdx.z;
+  const __half* plane = I + static_cast<long long>(c) * H * W * N;
+  float acc[SH][SW][8];
+#pragma unroll
+  for (int dy = 0; dy < SH; ++dy)
+#pragma unroll
+    for (int dx = 0; dx < SW; ++dx)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[dy][dx][i] = 0.0f;
+#pragma unroll
+  for (int wp = 0; wp < WP; ++wp) {
+    const int p = a - (WP - 1) + wp;
+    if (p < 0 || p >= P) continue;
+#pragma unroll
+    for (int wq = 0; wq < WQ; ++wq) {
+      const int q = b - (WQ - 1) + wq;
+      if (q < 0 || q >= Q) continue;
+      float best[8];
+      int arg[8];
+      window2d<R, S, SH, SW>(plane, H, W, N, p, q, n0, best, arg);
+      const Lanes8 e = load8(E + ((static_cast<long long>(c) * P + p) * Q + q) * N + n0);
+#pragma unroll
+      for (int dy = 0; dy < SH; ++dy) {
+        constexpr int dummy = 0;
+        (void)dummy;
+        const int r = (WP - 1 - wp) * SH + dy;   // tap row of block input dy inside window p
+        if (r >= R) continue;
+#pragma unroll
+        for (int dx = 0; dx < SW; ++dx) {
+          const int s = (WQ - 1 - wq) * SW + dx;
+          if (s >= S) continue;
+          const int tap = r * S + s;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (arg[i] == tap) acc[dy][dx][i] += e.v[i];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int dy = 0; dy < SH; ++dy) {
+    const int y = a * SH + dy;
+    if (y >= H) break;
+#pragma unroll
+    for (int dx = 0; dx < SW; ++dx) {
+      const int x = b * SW + dx;
+      if (x >= W) break;
+      store8(dI + ((static_cast<long long>(c) * H + y) * W + x) * N + n0, acc[dy][dx]);
+    }
+  }
+}
+
+template <int R, int S, int SH, int SW>
+int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, cudaStream_t stream) {
+  const int nvec = g.N / 8;
+  if (mode == 0) {
+    dim3 grid((g.Q * nvec + 255) / 256, g.P, g.C);
+    pool2d_fprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
+        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), g.H, g.W, g.N, g.P, g.Q);
+  } else {
+    const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
+    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    pool2d_bprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
+        static_cast<const __half*>(I), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W, g.N, g.P,
+        g.Q, BW);
+  }
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
+
+// returns NG_OK when a specialised kernel ran, 1 when the generic path must be used
+int try_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, cudaStream_t stream) {
+  const bool plain = g.J == 1 && g.T == 1 && g.D == 1 && g.str_j == 1 && g.str_d == 1 && g.pad_j == 0 &&
+                     g.pad_d == 0 && g.pad_h == 0 && g.pad_w == 0 && g.N % 8 == 0 && g.C <= 65535 && g.H <= 65535 &&
+                     (reinterpret_cast<uintptr_t>(I) & 15u) == 0 && (reinterpret_cast<uintptr_t>(EO) & 15u) == 0 &&
+                     (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+  if (!plain) return 1;
+  if (g.R == 3 && g.S == 3 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<3, 3, 2, 2>(g, I, EO, out, mode, stream);
+  if (g.R == 2 && g.S == 2 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<2, 2, 2, 2>(g, I, EO, out, mode, stream);
+  if (g.R == 3 && g.S == 3 && g.str_h == 3 && g.str_w == 3) return launch_pool2d<3, 3, 3, 3>(g, I, EO, out, mode, stream);
+  return 1;
+}
+
 int grid_for(long long total, const DeviceCtx* c) {
   const long long blocks = (total + 255) / 256;
   return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, c->sm_count * 32ll)));
@@ -187,6 +347,10 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
                    (reinterpret_cast<uintptr_t>(EO) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
   const long long out_elems = 1ll * g.K * g.M * g.P * g.Q * g.N;
   const long long in_elems = 1ll * g.C * g.D * g.H * g.W * g.N;
+  if (sizeof(T) == 2) {
+    const int rc = try_pool2d(g, I, EO, out, mode, stream);
+    if (rc <= 0) return rc;
+  }
   if (mode == 0) {
     T* O = static_cast<T*>(const_cast<void*>(EO));
     if (vec) pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O);
