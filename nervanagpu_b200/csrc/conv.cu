@@ -91,7 +91,7 @@ int filter_map(CUtensorMap* m, const void* base, const Geo& g, uint32_t box_c) {
 }
 
 void fill_taps(TcParams& p, const Geo& g, ChunkMode mode) {
-  p.RS = g.R * g.S; p.S = g.S;
+  p.RS = g.R * g.S; p.S = g.S; p.R = g.R;
   p.pad_d = g.pad_d; p.pad_h = g.pad_h; p.pad_w = g.pad_w;
   p.str_d = g.str_d; p.str_h = g.str_h; p.str_w = g.str_w;
   p.inner_tap = mode == CH_FLAT ? g.N : 0;
@@ -229,26 +229,30 @@ __global__ void conv_update_simt(Geo g, const __half* __restrict__ I, const __ha
 // ------------------------------------------------------------------------------------------
 // im2col: col[crst][pixel * N + n] = I[c, z, y, x, n] (zero outside the image); 8 images per thread
 // ------------------------------------------------------------------------------------------
-__global__ void im2col_kernel(Geo g, const __half* __restrict__ I, __half* __restrict__ col) {
+// grid: x covers (q, 8-image lane) of one output row, y = (m, p) row, z = (c, t, r, s) patch row,
+// so the only per-thread division is by the lane count.
+__global__ void __launch_bounds__(256) im2col_kernel(Geo g, const __half* __restrict__ I, __half* __restrict__ col) {
   const int n8 = g.N / 8;
-  const long long mpq = 1ll * g.M * g.P * g.Q;
-  const long long total = 1ll * g.C * g.T * g.R * g.S * mpq * n8;
-  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
-    long long r = i;
-    const int nv = r % n8; r /= n8;
-    const int q = r % g.Q; r /= g.Q;
-    const int p = r % g.P; r /= g.P;
-    const int m = r % g.M; r /= g.M;
-    const int s = r % g.S; r /= g.S;
-    const int rr = r % g.R; r /= g.R;
-    const int t = r % g.T; r /= g.T;
-    const int c = static_cast<int>(r);
-    const int z = m * g.str_d - g.pad_d + t, y = p * g.str_h - g.pad_h + rr, x = q * g.str_w - g.pad_w + s;
-    uint4 v = make_uint4(0, 0, 0, 0);
-    if (z >= 0 && z < g.D && y >= 0 && y < g.H && x >= 0 && x < g.W)
-      v = *reinterpret_cast<const uint4*>(I + (((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + nv * 8);
-    reinterpret_cast<uint4*>(col)[i] = v;
-  }
+  const int t0 = blockIdx.x * blockDim.x + threadIdx.x;
+  const int q = t0 / n8;
+  if (q >= g.Q) return;
+  const int nv = t0 - q * n8;
+  const int p = blockIdx.y % g.P, m = blockIdx.y / g.P;
+  int r = blockIdx.z;
+  const int s = r % g.S; r /= g.S;
+  const int rr = r % g.R; r /= g.R;
+  const int t = r % g.T;
+  const int c = r / g.T;
+  const int z = m * g.str_d - g.pad_d + t, y = p * g.str_h - g.pad_h + rr, x = q * g.str_w - g.pad_w + s;
+  uint4 v = make_uint4(0, 0, 0, 0);
+  if (z >= 0 && z < g.D && y >= 0 && y < g.H && x >= 0 && x < g.W)
+    v = *reinterpret_cast<const uint4*>(I + (((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + nv * 8);
+  const long long row = blockIdx.z, pix = (1ll * m * g.P + p) * g.Q + q;
+  reinterpret_cast<uint4*>(col)[(row * g.M * g.P * g.Q + pix) * n8 + nv] = v;
+}
+
+dim3 im2col_grid(const Geo& g) {
+  return dim3((g.Q * (g.N / 8) + 255) / 256, g.M * g.P, g.C * g.T * g.R * g.S);
 }
 
 int launch_1d(long long total, int threads, const DeviceCtx* c) {
@@ -295,15 +299,14 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
     const long long span = 1ll * g.M * g.P * g.Q * g.N;
     const bool small_c = g.C < 16 && path == NG_PATH_AUTO;
     const bool im2col = (small_c || path == NG_PATH_IM2COL) && al && span <= 0x7fffffffll &&
-                        1ll * g.C * RST * span * 2 <= (6ll << 30);
+                        1ll * g.C * RST * span * 2 <= (6ll << 30) && g.M * g.P <= 65535 && g.C * RST <= 65535;
     if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
     if (im2col) {
       const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
       rc = ensure_workspace(c, col_bytes);
       if (rc != NG_OK) return rc;
       __half* col = reinterpret_cast<__half*>(c->ws);
-      im2col_kernel<<<launch_1d(1ll * g.C * RST * span / 8, 256, c), 256, 0, stream>>>(
-          g, static_cast<const __half*>(I), col);
+      im2col_kernel<<<im2col_grid(g), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
       NG_CHECK_LAUNCH();
       GemmCall gc = {};
       gc.A = F; gc.B = col; gc.C = O; gc.a_t = 1; gc.b_t = 0;
@@ -406,7 +409,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   const bool direct = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al &&
                       (g.C >= 16 || path == NG_PATH_TENSOR);
   const bool im2col = !direct && path != NG_PATH_SIMT && path != NG_PATH_TENSOR && al &&
-                      1ll * g.C * RST * span * 2 <= (6ll << 30);
+                      1ll * g.C * RST * span * 2 <= (6ll << 30) && g.M * g.P <= 65535 && g.C * RST <= 65535;
   if (path == NG_PATH_TENSOR && !direct) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
   if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
   if (direct) {
@@ -441,7 +444,8 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     if (rc != NG_OK) return rc;
     __half* col = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(c->ws) + col_off);
     const long long total = 1ll * g.C * RST * span / 8;
-    im2col_kernel<<<launch_1d(total, 256, c), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
+    (void)total;
+    im2col_kernel<<<im2col_grid(g), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
     NG_CHECK_LAUNCH();
     GemmCall gc = {};
     gc.A = col; gc.B = E; gc.C = gradF; gc.a_t = 0; gc.b_t = 1;

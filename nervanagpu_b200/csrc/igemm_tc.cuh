@@ -42,7 +42,7 @@ struct TcParams {
   int a_zmul, b_zmul;              // batched GEMM: coordinate in dim 2 = z * zmul
   // conv geometry (unused by TC_GEMM)
   int red_chunks;                  // fprop: ceil(C/kb_rows); bprop: ceil(K/64)
-  int RS, S;                       // filter taps
+  int RS, S, R;                    // filter taps
   int pad_d, pad_h, pad_w;
   int str_d, str_h, str_w;
   int inner_tap;                   // N in flattened-(W,N) mode else 0

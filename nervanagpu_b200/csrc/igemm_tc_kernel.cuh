@@ -153,13 +153,20 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const WorkItem it = decode_work(p, w);
       const int m0 = it.tile_m * kTileM;
       const int n0 = it.tile_n * p.block_n;
-      // per-tile state of this lane's box
-      ChunkPos cp = {0, 0, 0, 0, true};
-      Tap ztap = {0, 0, 0};
+      // Per-tile state of this lane's box. Everything that changes from one k-block to the next
+      // is kept as counters that are stepped, not re-derived: integer division by run-time
+      // values costs this single warp more than the MMAs of a k-block take.
+      ChunkPos cp = {0, 0, 0, 0, true};   // fprop/bprop: pixel chunk of this B box; update: walks
+      Tap tap = {0, 0, 0};                // fprop/bprop: walks the filter taps; update: fixed (z)
+      int trs = 0, rc = 0;                // tap number and reduction-chunk number inside the tap
       if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
         if (!is_a) cp = decode_chunk(p, n0 / kChunk + bi);
+        trs = it.kb0 / p.red_chunks;
+        rc = it.kb0 - trs * p.red_chunks;
+        tap = decode_tap(p, trs);
       } else if (p.mode == TC_UPDATE) {
-        ztap = decode_tap(p, it.z);
+        tap = decode_tap(p, it.z);
+        cp = decode_chunk(p, it.kb0);
       }
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER)) {
@@ -180,50 +187,63 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               c2 = it.z * p.b_zmul;
             }
           } else if (p.mode == TC_FPROP) {
-            const int trs = kb / p.red_chunks;
-            const int cc = kb - trs * p.red_chunks;
             if (is_a) {  // filter rows c of tap trs, 64 output channels wide
-              c0 = m0 + kChunk * bi; c1 = trs; c2 = cc * p.kb_rows;
+              c0 = m0 + kChunk * bi; c1 = trs; c2 = rc * p.kb_rows;
             } else {     // input pixels of this chunk shifted by the tap
-              const Tap tp = decode_tap(p, trs);
-              c0 = cp.inner0 + (tp.s - p.pad_w) * p.inner_tap;
-              c1 = (cp.q * p.str_w - p.pad_w + tp.s) * p.x_tap;
-              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tp.r : p.oob_y;
-              c3 = cp.m * p.str_d - p.pad_d + tp.t;
-              c4 = cc * p.kb_rows;
+              c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
+              c1 = (cp.q * p.str_w - p.pad_w + tap.s) * p.x_tap;
+              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tap.r : p.oob_y;
+              c3 = cp.m * p.str_d - p.pad_d + tap.t;
+              c4 = rc * p.kb_rows;
             }
           } else if (p.mode == TC_BPROP) {
-            const int trs = kb / p.red_chunks;
-            const int kc = kb - trs * p.red_chunks;
             if (is_a) {  // filter rows c0.., 64 output channels k of tap trs
-              c0 = kc * kChunk; c1 = trs; c2 = m0;
+              c0 = rc * kChunk; c1 = trs; c2 = m0;
             } else {     // error pixels that reach this input pixel through tap trs
-              const Tap tp = decode_tap(p, trs);
               bool v = cp.valid;
               int q = 0, pp = 0, mm = 0;
               if (p.x_tap) {
-                v &= div_exact(cp.q + p.pad_w - tp.s, p.str_w, q);
+                v &= div_exact(cp.q + p.pad_w - tap.s, p.str_w, q);
                 c0 = cp.inner0;
               } else {
-                c0 = cp.inner0 + (p.pad_w - tp.s) * p.inner_tap;
+                c0 = cp.inner0 + (p.pad_w - tap.s) * p.inner_tap;
               }
-              v &= div_exact(cp.p + p.pad_h - tp.r, p.str_h, pp);
-              v &= div_exact(cp.m + p.pad_d - tp.t, p.str_d, mm);
-              c1 = q; c2 = v ? pp : p.oob_y; c3 = mm; c4 = kc * kChunk;
+              v &= div_exact(cp.p + p.pad_h - tap.r, p.str_h, pp);
+              v &= div_exact(cp.m + p.pad_d - tap.t, p.str_d, mm);
+              c1 = q; c2 = v ? pp : p.oob_y; c3 = mm; c4 = rc * kChunk;
             }
           } else {  // TC_UPDATE: k-block = one 64-element chunk of the (m,p,q,n) space
-            const ChunkPos ep = decode_chunk(p, kb);
             if (is_a) {  // input pixels under tap z, 128 channels c
-              c0 = ep.inner0 + (ztap.s - p.pad_w) * p.inner_tap;
-              c1 = (ep.q * p.str_w - p.pad_w + ztap.s) * p.x_tap;
-              c2 = ep.p * p.str_h - p.pad_h + ztap.r;
-              c3 = ep.m * p.str_d - p.pad_d + ztap.t;
+              c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
+              c1 = (cp.q * p.str_w - p.pad_w + tap.s) * p.x_tap;
+              c2 = cp.p * p.str_h - p.pad_h + tap.r;
+              c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = m0;
             } else {     // error pixels, block_n output channels k
-              c0 = ep.inner0; c1 = ep.q * p.x_tap; c2 = ep.p; c3 = ep.m; c4 = n0;
+              c0 = cp.inner0; c1 = cp.q * p.x_tap; c2 = cp.p; c3 = cp.m; c4 = n0;
             }
           }
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
+        }
+        // step the walkers to the next k-block
+        if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
+          if (++rc == p.red_chunks) {
+            rc = 0;
+            ++trs;
+            if (++tap.s == p.S) {
+              tap.s = 0;
+              if (++tap.r == p.R) { tap.r = 0; ++tap.t; }
+            }
+          }
+        } else if (p.mode == TC_UPDATE) {
+          cp.inner0 += kChunk;
+          if (cp.inner0 == p.dec_cpi * kChunk) {
+            cp.inner0 = 0;
+            if (++cp.q == p.dec_q) {
+              cp.q = 0;
+              if (++cp.p == p.dec_p) { cp.p = 0; ++cp.m; }
+            }
+          }
         }
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }

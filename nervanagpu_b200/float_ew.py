@@ -719,17 +719,43 @@ def _launch_shape(plan):
     return False, threads, sr
 
 
-def call_compound_kernel(rand_state, *args):
-    """Run the expression given as a postfix stack, e.g. for C[:] = 2.5 * A * B + 1:
-    (C, 2.5, A, {"op":"mul"}, B, {"op":"mul"}, 1, {"op":"add"}, {"op":"assign"})."""
+class _Launch(object):
+    """A prepared launch: compiled kernel, marshalled arguments, grid. Reused while the same
+    expression is applied to tensors with the same device layout (the common case in a training
+    loop), so that the per-call host cost is a dictionary lookup and one C call."""
+    __slots__ = ("kernel", "holders", "argv", "grid", "block", "offset_holder", "keepalive")
+
+
+_launch_cache = {}
+_LAUNCH_CACHE_LIMIT = 4096
+
+
+def _tensor_key(t):
+    take = t.take_array
+    return (t.ptr, t.shape, t.strides, t.dtype.str, t.is_trans, t.rounding,
+            None if not take else (take[0].ptr, take[0].shape, take[1]))
+
+
+def _stack_key(args):
+    key = []
+    for a in args:
+        if type(a) is dict:
+            if "idx" in a:
+                key.append(tuple(sorted((k, (_tensor_key(v) if k == "idx" else v)) for k, v in a.items())))
+            else:
+                key.append(tuple(sorted(a.items())))
+        elif hasattr(a, "gpudata"):
+            key.append(_tensor_key(a))
+        else:
+            key.append(("c", float(a)))
+    return tuple(key)
+
+
+def _prepare(args):
     plan = _analyse(args)
     out = plan.out
-    if out.size == 0:
-        return out
     vec, threads, sr = _launch_shape(plan)
     kernel = _get_kernel(plan, vec, threads, sr)
-    lib = _lib.init()
-
     holders = []
 
     def push(ctype, value):
@@ -766,18 +792,52 @@ def call_compound_kernel(rand_state, *args):
             grid, block = ((n_rows + rows_per_block - 1) // rows_per_block, 1, 1), (32 * rows_per_block, 1, 1)
         else:
             grid, block = (n_rows, 1, 1), (threads, 1, 1)
-    seed = rand_state.seed if rand_state is not None else 0
-    offset = rand_state.next_offset() if rand_state is not None else 0
-    push(ctypes.c_uint, seed & 0xFFFFFFFF)
-    push(ctypes.c_uint, (seed >> 32) & 0xFFFFFFFF)
-    push(ctypes.c_uint, offset)
+    launch = _Launch()
+    push(ctypes.c_uint, 0)          # seed lo (filled per call)
+    push(ctypes.c_uint, 0)          # seed hi
+    push(ctypes.c_uint, 0)          # rng offset
     push(ctypes.c_int, sr)
+    launch.kernel = kernel
+    launch.holders = holders
+    launch.argv = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
+    launch.grid, launch.block = grid, block
+    # The entry holds raw addresses, not tensors: it is found again only through a key made of the
+    # same addresses and layouts, so it never outlives the meaning of its arguments.
+    launch.keepalive = None
+    return launch
 
-    argv = (ctypes.c_void_p * len(holders))(*[ctypes.cast(ctypes.pointer(h), ctypes.c_void_p) for h in holders])
+
+def call_compound_kernel(rand_state, *args):
+    """Run the expression given as a postfix stack, e.g. for C[:] = 2.5 * A * B + 1:
+    (C, 2.5, A, {"op":"mul"}, B, {"op":"mul"}, 1, {"op":"add"}, {"op":"assign"})."""
+    out = None
+    for a in args:
+        if hasattr(a, "gpudata"):
+            out = a
+            break
+    if out is None:
+        raise TypeError("the first operand of an assignment must be a GPUTensor")
+    key = _stack_key(args)
+    launch = _launch_cache.get(key)
+    if launch is None:
+        if out.size == 0:
+            _analyse(args)          # still validate the expression
+            return out
+        launch = _prepare(args)
+        if len(_launch_cache) >= _LAUNCH_CACHE_LIMIT:
+            _launch_cache.clear()
+        _launch_cache[key] = launch
+    h = launch.holders
+    seed = rand_state.seed if rand_state is not None else 0
+    h[-4].value = seed & 0xFFFFFFFF
+    h[-3].value = (seed >> 32) & 0xFFFFFFFF
+    h[-2].value = rand_state.next_offset() if rand_state is not None else 0
     backend = out.backend
     repeat = backend.bench if (backend is not None and type(backend.bench) is int and backend.bench > 1) else 1
+    lib = _lib.init()
+    g, b = launch.grid, launch.block
     for _ in range(repeat):
-        _lib.check(lib.ng_ew_launch(kernel, grid[0], grid[1], grid[2], block[0], block[1], block[2], 0, argv,
+        _lib.check(lib.ng_ew_launch(launch.kernel, g[0], g[1], g[2], b[0], b[1], b[2], 0, launch.argv,
                                     backend.stream if backend is not None else None))
     return out
 
