@@ -214,6 +214,8 @@ def main():
         run_reference_arm(args, rank)
         return
 
+    # keep stdout to the one JSON line: NCCL's version banner goes to stderr
+    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
     dist = None
     if world > 1:
         import torch.distributed as dist   # plumbing only: rendezvous, barrier, max over ranks

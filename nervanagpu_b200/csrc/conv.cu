@@ -328,13 +328,13 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   p.mode = TC_FPROP;
   p.block_n = 256;
   p.M = g.K; p.N = static_cast<int>(cols);
-  p.tiles_m = (g.K + kTileM - 1) / kTileM;
   p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {1, 1, pick_kb_rows(g.C)};
-  tc_fill_mma(p, lay);
   p.red_chunks = (g.C + lay.kb_rows - 1) / lay.kb_rows;
   p.num_kb = RST * p.red_chunks;
+  tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.Q, g.P, g.M, mode);
   p.oob_y = g.H;
@@ -373,20 +373,20 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   p.mode = TC_BPROP;
   p.block_n = 256;
   p.M = g.C; p.N = static_cast<int>(cols);
-  p.tiles_m = (g.C + kTileM - 1) / kTileM;
   p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {0, 1, kChunk};
-  tc_fill_mma(p, lay);
   p.red_chunks = (g.K + kChunk - 1) / kChunk;
   p.num_kb = RST * p.red_chunks;
+  tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.W, g.H, g.D, mode);
   p.oob_y = g.P;
   p.C = gradI; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
   CUtensorMap mapA, mapB;
-  rc = filter_map(&mapA, F, g, kTileM);
+  rc = filter_map(&mapA, F, g, kTileM * p.m_halves);
   if (rc != NG_OK) return rc;
   rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk);
   if (rc != NG_OK) return rc;
@@ -417,12 +417,14 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     p.mode = TC_UPDATE;
     p.block_n = g.K <= 64 ? 64 : (g.K <= 128 ? 128 : 256);
     p.M = g.C; p.N = g.K;
-    p.tiles_m = (g.C + kTileM - 1) / kTileM;
     p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
     p.nz = RST;
     TcOperandLayout lay = {0, 0, kChunk};
-    tc_fill_mma(p, lay);
     p.num_kb = static_cast<int>(span / kChunk);
+    // the reduction is split to fill the SMs whatever the tile count, so only the operand
+    // traffic argues: assume many column tiles
+    tc_pick_tile_rows(c, p, 64ll * p.tiles_n * p.nz, p.num_kb);
+    tc_fill_mma(p, lay);
     fill_taps(p, g, mode);
     fill_decode(p, g.N, g.Q, g.P, g.M, mode);
     p.oob_y = g.H;
@@ -430,7 +432,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = out_f32; p.vec_ok = 1;
     p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n * p.nz, p.num_kb, 1ll * g.C * g.K * RST);
     CUtensorMap mapA, mapB;
-    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, kTileM);
+    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, kTileM * p.m_halves);
     if (rc != NG_OK) return rc;
     rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, p.block_n);
     if (rc != NG_OK) return rc;

@@ -122,4 +122,47 @@ __device__ __forceinline__ void epi_store8(const EpiArgs& e, float (&v)[8], void
   }
 }
 
+// Same arithmetic as epi_store8 for 8 consecutive, fully valid, 16-byte aligned outputs, but the
+// result is returned in registers (one 16-byte vector of fp16, or two of fp32) so the caller can
+// stage it in shared memory for a bulk tensor store. `oldp` points at the 8 old values or is null.
+template <bool F32OUT>
+__device__ __forceinline__ void epi_pack8(const EpiArgs& e, float (&v)[8], const void* oldp, unsigned long long lin,
+                                          uint4& lo, uint4& hi) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = epi_scale(e, v[i]);
+  if (F32OUT) {
+    if (e.beta != 0.0f && oldp) {
+      const float4 a = reinterpret_cast<const float4*>(oldp)[0], b = reinterpret_cast<const float4*>(oldp)[1];
+      v[0] = fmaf(e.beta, a.x, v[0]); v[1] = fmaf(e.beta, a.y, v[1]); v[2] = fmaf(e.beta, a.z, v[2]);
+      v[3] = fmaf(e.beta, a.w, v[3]); v[4] = fmaf(e.beta, b.x, v[4]); v[5] = fmaf(e.beta, b.y, v[5]);
+      v[6] = fmaf(e.beta, b.z, v[6]); v[7] = fmaf(e.beta, b.w, v[7]);
+    }
+    lo = make_uint4(__float_as_uint(v[0]), __float_as_uint(v[1]), __float_as_uint(v[2]), __float_as_uint(v[3]));
+    hi = make_uint4(__float_as_uint(v[4]), __float_as_uint(v[5]), __float_as_uint(v[6]), __float_as_uint(v[7]));
+    return;
+  }
+  if (e.beta != 0.0f && oldp) {
+    const uint4 o = *reinterpret_cast<const uint4*>(oldp);
+    const __half2* oh = reinterpret_cast<const __half2*>(&o);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(oh[i]);
+      v[2 * i] = fmaf(e.beta, f.x, v[2 * i]);
+      v[2 * i + 1] = fmaf(e.beta, f.y, v[2 * i + 1]);
+    }
+  }
+  __half2* oh = reinterpret_cast<__half2*>(&lo);
+  if (e.sr_bits) {
+    uint32_t rnd[8];
+    sr_bits8(e, lin >> 3, rnd);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      oh[i] = __halves2half2(f2h_sr(v[2 * i], rnd[2 * i], e.sr_bits), f2h_sr(v[2 * i + 1], rnd[2 * i + 1], e.sr_bits));
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);
+  }
+  hi = lo;
+}
+
 }  // namespace ngb

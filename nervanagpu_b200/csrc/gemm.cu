@@ -149,10 +149,10 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.mode = TC_GEMM;
   p.block_n = g.n <= 64 ? 64 : (g.n <= 128 ? 128 : 256);
   p.M = g.m; p.N = g.n;
-  p.tiles_m = (g.m + kTileM - 1) / kTileM;
   p.tiles_n = (g.n + p.block_n - 1) / p.block_n;
   p.nz = g.batch;
   p.num_kb = (g.k + kChunk - 1) / kChunk;
+  tc_pick_tile_rows(c, p, static_cast<long long>(p.tiles_n) * p.nz, p.num_kb);
   TcOperandLayout lay;
   lay.a_mn_major = g.a_t ? 1 : 0;   // stored k x m: m contiguous
   lay.b_mn_major = g.b_t ? 0 : 1;   // stored k x n: n contiguous
@@ -176,7 +176,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     uint64_t str[4] = {16, 16, 16, 16};
     uint32_t box[5] = {kChunk, 1, 1, 1, 1};
     if (g.a_t) { dims[0] = g.m; dims[1] = g.k; box[1] = kChunk; }
-    else       { dims[0] = g.k; dims[1] = g.m; box[1] = kTileM; }
+    else       { dims[0] = g.k; dims[1] = g.m; box[1] = kTileM * p.m_halves; }
     dims[2] = g.az != 0 ? g.batch : 1;
     str[0] = static_cast<uint64_t>(g.lda) * 2;
     str[1] = g.az != 0 ? static_cast<uint64_t>(g.az) * 2 : str[0] * dims[1];

@@ -56,6 +56,11 @@ struct TcOperandLayout {
 void tc_fill_mma(TcParams& p, const TcOperandLayout& lay);
 int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream);
 
+// 1 = 128-row tiles, 2 = 256-row tiles (two accumulators sharing each B operand: a third less
+// L2 -> SM traffic per flop, but no overlap of the epilogue with the next tile and coarser waves).
+// `col_tiles` = column tiles x z x splits. Sets p.m_halves and p.tiles_m.
+void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int num_kb);
+
 // Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems);
 

@@ -11,7 +11,9 @@ enum TcMode : int { TC_GEMM = 0, TC_FPROP = 1, TC_BPROP = 2, TC_UPDATE = 3 };
 constexpr int kTileM = 128;        // UMMA M (TMEM lanes)
 constexpr int kChunk = 64;         // fp16 elements per 128-byte swizzle row
 constexpr int kMaxStages = 8;
-constexpr int kTcThreads = 192;    // warp 0 TMA, warp 1 MMA, warps 2-5 epilogue
+constexpr int kEpiWarps = 8;       // two per group of 32 TMEM lanes, each takes half of the columns
+constexpr int kTcThreads = 64 + 32 * kEpiWarps;    // warp 0 TMA, warp 1 MMA, then the epilogue warps
+constexpr uint32_t kEpiStageBytes = kEpiWarps * 4096;  // one [32 rows][128 B] staging box per epilogue warp
 
 struct TcParams {
   // ---- work decomposition: item = ((split * nz + z) * tiles_n + tile_n) * tiles_m + tile_m
@@ -19,6 +21,8 @@ struct TcParams {
   int num_kb;          // k-blocks in the whole reduction
   int kb_per_split;    // ceil(num_kb / splits)
   int block_n;         // UMMA N: 64, 128 or 256
+  int m_halves;        // 1: 128-row tiles, accumulator double-buffered across tiles
+                       // 2: 256-row tiles, two accumulators that share every B operand
   int M, N;            // logical output extent (rows, cols)
 
   // ---- MMA descriptors (host-built)
@@ -26,6 +30,7 @@ struct TcParams {
   uint32_t a_desc_lo, a_desc_hi;   // lo: LBO field only; start address is or-ed in per stage
   uint32_t b_desc_lo, b_desc_hi;
   uint32_t a_kstep, b_kstep;       // start-address increment (16-byte units) per K=16 MMA
+  uint32_t a_half_step;            // start-address increment (16-byte units) to the second 128 rows of A
   int mma_per_kb;                  // kb_rows / 16
 
   // ---- shared-memory ring
@@ -60,6 +65,8 @@ struct TcParams {
   int sr_bits;                     // 0 = round to nearest even, else mantissa bits kept
   int out_f32;
   int vec_ok;                      // rows are 16-byte aligned for vector access
+  int tma_store;                   // 1: tiles leave through shared memory + bulk tensor stores
+  int c_box_cols;                  // columns per store box (128 bytes worth: 64 fp16 / 32 fp32)
   uint32_t seed_lo, seed_hi, rng_offset;
   float* ws;                       // split-K partials [split][z][M][N] when splits > 1
   int* status;                     // device status word

@@ -91,16 +91,18 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                const __grid_constant__ TcParams p) {
+                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // ring buffer must be 1024-byte aligned for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t ring_bytes = static_cast<uint32_t>(p.stages) * p.stage_bytes;
+  // output staging (bulk-store epilogue only), then the control block
+  const uint32_t epi_base = smem_base + ring_bytes;
+  const uint32_t epi_bytes = p.tma_store ? kEpiStageBytes : 0u;
 
-  // control block after the ring
-  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + ring_bytes);
-  const uint32_t bar_base = smem_base + ring_bytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + ring_bytes + epi_bytes);
+  const uint32_t bar_base = smem_base + ring_bytes + epi_bytes;
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (kMaxStages + s); };
   auto accf_bar = [&](int a) { return bar_base + 8u * (2 * kMaxStages + a); };
@@ -120,7 +122,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(accf_bar(a), 1);
-      mbar_init(acce_bar(a), 4);
+      mbar_init(acce_bar(a), kEpiWarps);
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -128,6 +130,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
+    if (p.tma_store) tma_prefetch_desc(&mapC);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), tmem_cols);
@@ -151,7 +154,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     bool ok = true;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const WorkItem it = decode_work(p, w);
-      const int m0 = it.tile_m * kTileM;
+      const int m0 = it.tile_m * kTileM * p.m_halves;
       const int n0 = it.tile_n * p.block_n;
       // Per-tile state of this lane's box. Everything that changes from one k-block to the next
       // is kept as counters that are stepped, not re-derived: integer division by run-time
@@ -250,19 +253,26 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
+    // m_halves == 1: accumulator `local & 1` (double-buffered across tiles), barriers accf/acce[acc].
+    // m_halves == 2: both accumulators belong to one 256-row tile; acce[h] says half h was drained,
+    //                accf[0] says both halves are complete.
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
       bool ok = true;
+      const bool wide = p.m_halves == 2;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++local) {
         const WorkItem it = decode_work(p, w);
-        const int acc = local & 1;
-        const uint32_t acc_phase = (local >> 1) & 1u;
-        if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * p.block_n);
-        for (int kb = it.kb0; kb < it.kb1; ++kb) {
+        const int acc = wide ? 0 : (local & 1);
+        const uint32_t acc_phase = wide ? (local & 1u) : ((local >> 1) & 1u);
+        // rows of the second half that lie beyond M need no MMAs
+        const int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
+        if (!wide) {
+          if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
+          tc_fence_after();
+        }
+        for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA)) {
             ok = false;
             break;
@@ -270,17 +280,29 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tc_fence_after();
           const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
           const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
-          for (int k = 0; k < p.mma_per_kb; ++k) {
-            const uint64_t adesc = (static_cast<uint64_t>(p.a_desc_hi) << 32) |
-                                   (p.a_desc_lo | ((sa + k * p.a_kstep) & 0x3fffu));
-            const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
-                                   (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
-            tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, (kb > it.kb0 || k > 0) ? 1u : 0u);
+          for (int h = 0; h < halves; ++h) {
+            if (wide && kb == it.kb0) {
+              if (!mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) {
+                ok = false;
+                break;
+              }
+              tc_fence_after();
+            }
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((wide ? h : acc) * p.block_n);
+            const uint32_t sah = sa + h * p.a_half_step;
+            for (int k = 0; k < p.mma_per_kb; ++k) {
+              const uint64_t adesc = (static_cast<uint64_t>(p.a_desc_hi) << 32) |
+                                     (p.a_desc_lo | ((sah + k * p.a_kstep) & 0x3fffu));
+              const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
+                                     (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
+              tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, (kb > it.kb0 || k > 0) ? 1u : 0u);
+            }
           }
+          if (!ok) break;
           tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(accf_bar(acc));  // accumulator complete
+        if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
       }
     }
     __syncwarp();
@@ -292,61 +314,143 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
     EpiArgs raw = ea;  // split-K partials: untouched accumulators
     raw.alpha = 1.0f; raw.beta = 0.0f; raw.relu = 0; raw.sr_bits = 0;
+    const bool wide = p.m_halves == 2;
+    // two warps share each group of 32 TMEM lanes and split the columns between them
+    const int col_group = (warp - 2) >> 2;
     int local = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++local) {
       const WorkItem it = decode_work(p, w);
-      const int acc = local & 1;
-      const uint32_t acc_phase = (local >> 1) & 1u;
+      const int acc = wide ? 0 : (local & 1);
+      const uint32_t acc_phase = wide ? (local & 1u) : ((local >> 1) & 1u);
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
-      const int row = it.tile_m * kTileM + lane_group * 32 + lane;
       const int n0 = it.tile_n * p.block_n;
-      const bool row_ok = row < p.M;
-      const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
-                             static_cast<uint32_t>(acc * p.block_n);
       const bool partial = p.splits > 1;
-      // row base pointers
-      uint8_t* crow = nullptr;
-      const uint8_t* oldrow = nullptr;
-      unsigned long long lin_row = 0;
-      if (partial) {
-        const long long off = ((static_cast<long long>(it.split) * p.nz + it.z) * p.M + row) * p.N;
-        crow = reinterpret_cast<uint8_t*>(p.ws + off);
-      } else {
-        const long long off = it.z * p.c_zstride + static_cast<long long>(row) * p.ldc;
-        const int esz = p.out_f32 ? 4 : 2;
-        crow = static_cast<uint8_t*>(p.C) + off * esz;
-        oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
-        lin_row = (static_cast<unsigned long long>(it.z) * p.M + row) * static_cast<unsigned long long>(p.N);
-      }
-      for (int c = 0; c < p.block_n / 32; ++c) {
-        uint32_t r[32];
-        tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
-        tc_wait_ld();
-        const int col0 = n0 + c * 32;
-        if (row_ok && col0 < p.N) {
+      for (int h = 0; h < p.m_halves; ++h) {
+        const int row = (it.tile_m * p.m_halves + h) * kTileM + lane_group * 32 + lane;
+        const bool row_ok = row < p.M;
+        // whole half beyond M: nothing was accumulated there, nothing to store
+        const bool half_live = (it.tile_m * p.m_halves + h) * kTileM < p.M;
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
+                               static_cast<uint32_t>((wide ? h : acc) * p.block_n);
+        // row base pointers
+        uint8_t* crow = nullptr;
+        const uint8_t* oldrow = nullptr;
+        unsigned long long lin_row = 0;
+        if (partial) {
+          const long long off = ((static_cast<long long>(it.split) * p.nz + it.z) * p.M + row) * p.N;
+          crow = reinterpret_cast<uint8_t*>(p.ws + off);
+        } else {
+          const long long off = it.z * p.c_zstride + static_cast<long long>(row) * p.ldc;
+          const int esz = p.out_f32 ? 4 : 2;
+          crow = static_cast<uint8_t*>(p.C) + off * esz;
+          oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
+          lin_row = (static_cast<unsigned long long>(it.z) * p.M + row) * static_cast<unsigned long long>(p.N);
+        }
+        if (p.tma_store) {
+          // Staged path: 32 rows x 128 bytes per box, written to shared memory in the 128-byte
+          // swizzle pattern (16-byte chunk j of row t lands at chunk j ^ (t & 7): conflict-free
+          // for the per-row writes below), then one bulk tensor store per box. The store clips
+          // rows >= M and columns >= N itself.
+          const int epi_warp = warp - 2;
+          const int row0 = (it.tile_m * p.m_halves + h) * kTileM + lane_group * 32;
+          const int zc = partial ? it.split * p.nz + it.z : it.z;
+          const int subs = p.c_box_cols / 32;            // tcgen05.ld groups per box: 2 (fp16) or 1 (fp32)
+          const int n_boxes = p.block_n / p.c_box_cols;
+          const int cb0 = col_group == 0 ? 0 : (n_boxes + 1) / 2;
+          const int cb1 = col_group == 0 ? (n_boxes + 1) / 2 : n_boxes;
+          const uint32_t buf = epi_base + static_cast<uint32_t>(epi_warp * 4096);
+          for (int cb = cb0; half_live && cb < cb1; ++cb) {
+            const int colb = n0 + cb * p.c_box_cols;
+            for (int sub = 0; sub < subs; ++sub) {
+              uint32_t r[32];
+              tc_ld_32x32(taddr + static_cast<uint32_t>(cb * p.c_box_cols + sub * 32), r);
+              tc_wait_ld();
+              if (sub == 0) {
+                // the previous store from this warp's buffer must have read it before we overwrite
+                if (lane == 0) tma_store_wait_read<0>();
+                __syncwarp();
+              }
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const int col = col0 + g * 8;
-            const int nvalid = min(8, p.N - col);
-            if (nvalid <= 0) break;
-            float v[8];
+              for (int g = 0; g < 4; ++g) {
+                const int col = colb + sub * 32 + g * 8;
+                float v[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-            if (partial) {
-              epi_store8<true>(raw, v, crow, nullptr, col, 0ull, nvalid, (p.N & 3) == 0);
-            } else if (p.out_f32) {
-              epi_store8<true>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
-            } else {
-              epi_store8<false>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+                for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+                uint4 lo, hi;
+                const bool live = row_ok && col < p.N;
+                if (partial) {
+                  epi_pack8<true>(raw, v, nullptr, 0ull, lo, hi);
+                } else if (p.out_f32) {
+                  epi_pack8<true>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 4 : nullptr,
+                                  lin_row + col, lo, hi);
+                } else {
+                  epi_pack8<false>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 2 : nullptr,
+                                   lin_row + col, lo, hi);
+                }
+                const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
+                if (partial || p.out_f32) {   // 8 fp32 = two chunks
+                  const int j = g * 2;
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + (((j) ^ (lane & 7)) << 4)),
+                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + (((j + 1) ^ (lane & 7)) << 4)),
+                               "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                } else {                       // 8 fp16 = one chunk
+                  const int j = sub * 4 + g;
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + ((j ^ (lane & 7)) << 4)),
+                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                }
+              }
+            }
+            fence_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (colb < p.N && row0 < p.M) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
+              tma_store_commit();
             }
           }
         }
+        const int n_chunks = p.block_n / 32;
+        const int c_begin = col_group == 0 ? 0 : (n_chunks + 1) / 2;
+        const int c_end = col_group == 0 ? (n_chunks + 1) / 2 : n_chunks;
+        for (int c = c_begin; !p.tma_store && half_live && c < c_end; ++c) {
+          uint32_t r[32];
+          tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
+          tc_wait_ld();
+          const int col0 = n0 + c * 32;
+          if (row_ok && col0 < p.N) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              const int col = col0 + g * 8;
+              const int nvalid = min(8, p.N - col);
+              if (nvalid <= 0) break;
+              float v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
+              if (partial) {
+                epi_store8<true>(raw, v, crow, nullptr, col, 0ull, nvalid, (p.N & 3) == 0);
+              } else if (p.out_f32) {
+                epi_store8<true>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+              } else {
+                epi_store8<false>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+              }
+            }
+          }
+        }
+        if (wide) {   // hand this half back as soon as it is drained
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acce_bar(h));
+        }
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acce_bar(acc));
+      if (!wide) {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acce_bar(acc));
+      }
     }
+    // outstanding bulk stores must be complete before the CTA (and its shared memory) goes away
+    if (p.tma_store && lane == 0) tma_store_wait_all();
   }
 
   // =========================== teardown ===========================

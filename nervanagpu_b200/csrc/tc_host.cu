@@ -39,16 +39,20 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   // MN-major operand: boxes of [kb_rows][64 mn]; 8 reduction rows = 1024 B (stride offset),
   // next 64-wide MN chunk = next box (leading offset); a K=16 step moves 16 rows = 2048 B.
   const uint32_t mn_box = static_cast<uint32_t>(lay.kb_rows) * 128u;
+  if (p.m_halves != 2) p.m_halves = 1;
+  const uint32_t tile_rows = kTileM * p.m_halves;
   if (lay.a_mn_major) {
-    p.a_boxes = kTileM / kChunk;
+    p.a_boxes = tile_rows / kChunk;
     p.a_box_bytes = mn_box;
     p.a_desc_lo = desc_lo(mn_box);
     p.a_kstep = 2048u >> 4;
+    p.a_half_step = (2u * mn_box) >> 4;
   } else {
     p.a_boxes = 1;
-    p.a_box_bytes = kTileM * 128u;
+    p.a_box_bytes = tile_rows * 128u;
     p.a_desc_lo = desc_lo(16);
     p.a_kstep = 32u >> 4;
+    p.a_half_step = (kTileM * 128u) >> 4;
   }
   p.a_desc_hi = desc_hi(1024);
   p.a_bytes = p.a_boxes * p.a_box_bytes;
@@ -68,7 +72,61 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   p.a_bytes = (p.a_bytes + 1023u) & ~1023u;
   const uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
   p.stage_bytes = p.a_bytes + b_bytes;
-  p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes) / p.stage_bytes);
+  p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes) / p.stage_bytes);
+}
+
+// Output tensor map for the bulk-store epilogue: (columns, rows, z) over C, or over the split-K
+// workspace. Returns false when the output cannot be addressed that way (the kernel then stores
+// straight from registers).
+static bool make_store_map(CUtensorMap* map, TcParams& p) {
+  static const char* off = getenv("NG_TMA_STORE");
+  if (off && off[0] == '0') return false;
+  if ((p.N & 7) != 0) return false;
+  const bool partial = p.splits > 1;
+  const int esz = (partial || p.out_f32) ? 4 : 2;
+  uint64_t dims[5] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), 1, 1, 1};
+  uint64_t str[4];
+  const void* base;
+  if (partial) {
+    base = p.ws;
+    dims[2] = static_cast<uint64_t>(p.nz) * p.splits;
+    str[0] = static_cast<uint64_t>(p.N) * 4;
+    str[1] = str[0] * p.M;
+  } else {
+    if (!p.vec_ok) return false;
+    base = p.C;
+    dims[2] = p.nz;
+    str[0] = static_cast<uint64_t>(p.ldc) * esz;
+    str[1] = p.nz > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : str[0] * p.M;
+    if (str[1] == 0) return false;
+  }
+  str[2] = str[3] = std::max(str[1] * dims[2], str[0] * dims[1]);
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (str[0] & 15u) || (str[1] & 15u)) return false;
+  p.c_box_cols = 128 / esz;
+  const uint32_t box[5] = {static_cast<uint32_t>(p.c_box_cols), 32, 1, 1, 1};
+  if (make_tensor_map(map, base, dims, str, box, esz) != NG_OK) return false;
+  return true;
+}
+
+void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int num_kb) {
+  p.m_halves = 1;
+  p.tiles_m = (p.M + kTileM - 1) / kTileM;
+  if (p.M <= kTileM) return;
+  const long long sm = c->sm_count;
+  // cost model in "operand bytes per SM": waves x k-blocks x (rows + columns) of a k-block,
+  // plus an un-overlapped epilogue worth about four k-blocks for the wide tile
+  const long long t1 = p.tiles_m * col_tiles;
+  const long long cost1 = ((t1 + sm - 1) / sm) * num_kb * (kTileM + p.block_n);
+  const long long tm2 = (p.M + 2 * kTileM - 1) / (2 * kTileM);
+  const long long t2 = tm2 * col_tiles;
+  const long long cost2 = ((t2 + sm - 1) / sm) * (num_kb + 4ll) * (2 * kTileM + p.block_n);
+  // NG_TILE_ROWS=128|256 overrides the choice (tuning aid)
+  static const char* force = getenv("NG_TILE_ROWS");
+  const bool wide = force ? (force[0] == '2') : (cost2 < cost1);
+  if (wide) {
+    p.m_halves = 2;
+    p.tiles_m = static_cast<int>(tm2);
+  }
 }
 
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems) {
@@ -106,7 +164,9 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
   if (total > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many work items");
   const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
-  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
+  CUtensorMap mapC = mapA;   // placeholder when the bulk-store epilogue is off
+  p.tma_store = make_store_map(&mapC, p) ? 1 : 0;
+  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u);
   TcParams launch = p;
   launch.stage_bytes = p.stage_bytes;
   // expect_tx must equal the bytes the boxes deliver; regions are box multiples already
@@ -114,7 +174,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     // padded regions: the kernel's expect_tx uses stage_bytes, so keep them identical
     return fail(NG_ERR_INVALID_ARG, "internal: stage layout is not a whole number of boxes");
   }
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, launch);
+  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, launch);
   NG_CHECK_LAUNCH();
   if (p.splits > 1) {
     EpiArgs ea;
@@ -265,7 +325,8 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.splits;
   const int grid = static_cast<int>(std::min<long long>(total, slots->sm_count));
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, p);
+  p.tma_store = 0;   // this variant stores straight from registers
+  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;
   ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;
