@@ -92,6 +92,7 @@ int filter_map(CUtensorMap* m, const void* base, const Geo& g, uint32_t box_c) {
 
 void fill_taps(TcParams& p, const Geo& g, ChunkMode mode) {
   p.RS = g.R * g.S; p.S = g.S; p.R = g.R;
+  p.tap_w = 1; p.tap_h = 1;
   p.pad_d = g.pad_d; p.pad_h = g.pad_h; p.pad_w = g.pad_w;
   p.str_d = g.str_d; p.str_h = g.str_h; p.str_w = g.str_w;
   p.inner_tap = mode == CH_FLAT ? g.N : 0;
@@ -260,6 +261,168 @@ int launch_1d(long long total, int threads, const DeviceCtx* c) {
   return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, c->sm_count * 32ll)));
 }
 
+// ------------------------------------------------------------------------------------------
+// Few input channels (first layers): tap blocks.
+// One TMA box (64 n, bw x, bh y, 1, C) of the input carries the C*bh*bw rows that a block of
+// bh x bw filter taps needs for one output pixel, already in the order (c, dy, dx). With
+// rows = C*bh*bw a multiple of 16 this is one k-block of `rows` reduction rows, so a 3-channel
+// 11x11 stride-4 layer runs as 9 k-blocks of 48 rows (bh = bw = 4) instead of 121 k-blocks of
+// 16 rows holding 3 useful ones. The filter is re-packed (zero padded) to the same row order:
+//   Fp[row = (c*bh + dy)*bw + dx][tb = (t*nr + r')*ns + s'][k] = F[c][t][r'*bh+dy][s'*bw+dx][k].
+// ------------------------------------------------------------------------------------------
+struct TapBlock {
+  int bw = 0, bh = 0, rows = 0, nr = 0, ns = 0;
+  bool ok = false;
+};
+
+TapBlock pick_tap_block(const Geo& g) {
+  TapBlock best;
+  long long best_cost = 0;
+  for (int bh = 1; bh <= 16; ++bh)
+    for (int bw = 1; bw <= 16; ++bw) {
+      const int rows = g.C * bh * bw;
+      if (rows % 16 != 0 || rows > 64) continue;
+      const int nr = (g.R + bh - 1) / bh, ns = (g.S + bw - 1) / bw;
+      // padded reduction length, plus a fixed charge per k-block
+      const long long cost = 1ll * nr * ns * (rows + 8);
+      if (!best.ok || cost < best_cost) {
+        best.bw = bw; best.bh = bh; best.rows = rows; best.nr = nr; best.ns = ns; best.ok = true;
+        best_cost = cost;
+      }
+    }
+  return best;
+}
+
+__global__ void filter_repack_kernel(Geo g, TapBlock tb, const __half* __restrict__ F, __half* __restrict__ Fp) {
+  const int k8 = g.K / 8;
+  const int ntb = g.T * tb.nr * tb.ns;
+  const long long total = 1ll * tb.rows * ntb * k8;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int kv = r % k8; r /= k8;
+    const int b = r % ntb;
+    const int row = static_cast<int>(r / ntb);
+    const int dx = row % tb.bw, dy = (row / tb.bw) % tb.bh, c = row / (tb.bw * tb.bh);
+    const int sp = b % tb.ns, rp = (b / tb.ns) % tb.nr, t = b / (tb.ns * tb.nr);
+    const int rr = rp * tb.bh + dy, s = sp * tb.bw + dx;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (rr < g.R && s < g.S)
+      v = *reinterpret_cast<const uint4*>(F + ((((1ll * c * g.T + t) * g.R + rr) * g.S + s) * g.K + kv * 8));
+    reinterpret_cast<uint4*>(Fp)[i] = v;
+  }
+}
+
+// gradient in tap-block order Dp[tb][row][k] (fp32) -> gradF[c][t][r][s][k]
+__global__ void filter_unpack_kernel(Geo g, TapBlock tb, const float* __restrict__ Dp, void* gradF, int out_f32) {
+  const long long total = g.sizeF();
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int k = r % g.K; r /= g.K;
+    const int s = r % g.S; r /= g.S;
+    const int rr = r % g.R; r /= g.R;
+    const int t = r % g.T;
+    const int c = static_cast<int>(r / g.T);
+    const int b = (t * tb.nr + rr / tb.bh) * tb.ns + s / tb.bw;
+    const int row = (c * tb.bh + rr % tb.bh) * tb.bw + s % tb.bw;
+    const float v = Dp[(1ll * b * tb.rows + row) * g.K + k];
+    if (out_f32) static_cast<float*>(gradF)[i] = v;
+    else static_cast<__half*>(gradF)[i] = __float2half_rn(v);
+  }
+}
+
+// input map whose box carries one tap block: (64 n, bw, bh, 1, C)
+int act_map_tapblock(CUtensorMap* m, const void* base, const Geo& g, const TapBlock& tb) {
+  const uint64_t xn = 1ull * g.W * g.N * 2;
+  uint64_t dims[5] = {static_cast<uint64_t>(g.N), static_cast<uint64_t>(g.W), static_cast<uint64_t>(g.H),
+                      static_cast<uint64_t>(g.D), static_cast<uint64_t>(g.C)};
+  uint64_t str[4] = {1ull * g.N * 2, xn, xn * g.H, xn * g.H * g.D};
+  const uint32_t box[5] = {kChunk, static_cast<uint32_t>(tb.bw), static_cast<uint32_t>(tb.bh), 1,
+                           static_cast<uint32_t>(g.C)};
+  return make_tensor_map(m, base, dims, str, box);
+}
+
+int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I, const void* F, void* O, float alpha,
+                   int relu, cudaStream_t stream) {
+  const int ntb = g.T * tb.nr * tb.ns;
+  const long long cols = 1ll * g.M * g.P * g.Q * g.N;
+  const size_t fp_bytes = static_cast<size_t>(tb.rows) * ntb * g.K * 2;
+  int rc = ensure_workspace(c, fp_bytes);
+  if (rc != NG_OK) return rc;
+  __half* Fp = reinterpret_cast<__half*>(c->ws);
+  filter_repack_kernel<<<launch_1d(1ll * tb.rows * ntb * g.K / 8, 256, c), 256, 0, stream>>>(
+      g, tb, static_cast<const __half*>(F), Fp);
+  NG_CHECK_LAUNCH();
+  TcParams p = {};
+  p.mode = TC_FPROP;
+  p.block_n = 256;
+  p.M = g.K; p.N = static_cast<int>(cols);
+  p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
+  p.nz = 1; p.splits = 1;
+  TcOperandLayout lay = {1, 1, tb.rows};
+  p.red_chunks = 1;
+  p.num_kb = ntb;
+  tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  tc_fill_mma(p, lay);
+  fill_taps(p, g, CH_PIXEL);
+  p.R = tb.nr; p.S = tb.ns; p.RS = tb.nr * tb.ns; p.tap_w = tb.bw; p.tap_h = tb.bh;
+  fill_decode(p, g.N, g.Q, g.P, g.M, CH_PIXEL);
+  p.oob_y = g.H;
+  p.C = O; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
+  p.alpha = alpha; p.beta = 0.0f; p.relu = relu; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
+  CUtensorMap mapA, mapB;
+  {  // packed filter seen as (k, tap block, row)
+    uint64_t dims[5] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(ntb), static_cast<uint64_t>(tb.rows), 1, 1};
+    uint64_t str[4];
+    str[0] = 1ull * g.K * 2; str[1] = str[0] * ntb; str[2] = str[1] * tb.rows; str[3] = str[2];
+    const uint32_t box[5] = {kChunk, 1, static_cast<uint32_t>(tb.rows), 1, 1};
+    rc = make_tensor_map(&mapA, Fp, dims, str, box);
+    if (rc != NG_OK) return rc;
+  }
+  rc = act_map_tapblock(&mapB, I, g, tb);
+  if (rc != NG_OK) return rc;
+  return tc_launch(c, mapA, mapB, p, stream);
+}
+
+int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I, const void* E, void* gradF,
+                    int out_f32, float alpha, cudaStream_t stream) {
+  const int ntb = g.T * tb.nr * tb.ns;
+  const long long span = 1ll * g.M * g.P * g.Q * g.N;
+  // workspace: [split-K partials of the engine, at most 32 splits][Dp]
+  const size_t dp_bytes = static_cast<size_t>(ntb) * tb.rows * g.K * 4;
+  const size_t dp_off = (32 * dp_bytes + 255) & ~size_t(255);
+  int rc = ensure_workspace(c, dp_off + dp_bytes);
+  if (rc != NG_OK) return rc;
+  float* Dp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c->ws) + dp_off);
+  TcParams p = {};
+  p.mode = TC_UPDATE;
+  p.block_n = g.K <= 64 ? 64 : (g.K <= 128 ? 128 : 256);
+  p.M = tb.rows; p.N = g.K;
+  p.m_halves = 1; p.tiles_m = 1;
+  p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
+  p.nz = ntb;
+  TcOperandLayout lay = {0, 0, kChunk};
+  lay.a_box_rows = tb.rows;
+  p.num_kb = static_cast<int>(span / kChunk);
+  tc_fill_mma(p, lay);
+  fill_taps(p, g, CH_PIXEL);
+  p.R = tb.nr; p.S = tb.ns; p.RS = tb.nr * tb.ns; p.tap_w = tb.bw; p.tap_h = tb.bh;
+  fill_decode(p, g.N, g.Q, g.P, g.M, CH_PIXEL);
+  p.oob_y = g.H;
+  p.C = Dp; p.Cold = nullptr; p.ldc = g.K; p.c_zstride = 1ll * tb.rows * g.K;
+  p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 1; p.vec_ok = 1;
+  p.splits = choose_splits(c, 1ll * p.tiles_n * p.nz, p.num_kb, 1ll * ntb * tb.rows * g.K);
+  CUtensorMap mapA, mapB;
+  rc = act_map_tapblock(&mapA, I, g, tb);
+  if (rc != NG_OK) return rc;
+  rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, CH_PIXEL, p.block_n);
+  if (rc != NG_OK) return rc;
+  rc = tc_launch(c, mapA, mapB, p, stream);
+  if (rc != NG_OK) return rc;
+  filter_unpack_kernel<<<launch_1d(g.sizeF(), 256, c), 256, 0, stream>>>(g, tb, Dp, gradF, out_f32);
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
+
 }  // namespace
 
 }  // namespace ngb
@@ -291,9 +454,13 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   const bool al = aligned16(I) && aligned16(F) && aligned16(O);
   const bool tc = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al;
   if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
+  if ((path == NG_PATH_AUTO || path == NG_PATH_TENSOR) && g.C < 16 && g.N % kChunk == 0 && al) {
+    const TapBlock tb = pick_tap_block(g);
+    if (tb.ok) return fprop_tapblock(c, g, tb, I, F, O, alpha, relu, stream);
+  }
   {
-    // Few input channels (first layers): one tap per k-block would feed the tensor core 3 useful
-    // rows out of 16, so gather the patches once and run a dense GEMM over all C*T*R*S rows:
+    // Few input channels where tap blocks do not apply: one tap per k-block would feed the tensor
+    // core 3 useful rows out of 16, so gather the patches once and run a dense GEMM over all rows:
     //   O[K x span] = F2d[crst][k]^T * col[crst][span]
     const int RST = g.T * g.R * g.S;
     const long long span = 1ll * g.M * g.P * g.Q * g.N;
@@ -412,6 +579,10 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
                       1ll * g.C * RST * span * 2 <= (6ll << 30) && g.M * g.P <= 65535 && g.C * RST <= 65535;
   if (path == NG_PATH_TENSOR && !direct) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
   if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
+  if ((path == NG_PATH_AUTO || path == NG_PATH_TENSOR) && g.C < 16 && g.N % kChunk == 0 && al) {
+    const TapBlock tb = pick_tap_block(g);
+    if (tb.ok) return update_tapblock(c, g, tb, I, E, gradF, out_f32, alpha, stream);
+  }
   if (direct) {
     TcParams p = {};
     p.mode = TC_UPDATE;

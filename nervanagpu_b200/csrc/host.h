@@ -52,6 +52,7 @@ int make_tensor_map(CUtensorMap* out, const void* base, const uint64_t dims[5], 
 struct TcOperandLayout {
   int a_mn_major, b_mn_major;
   int kb_rows;   // reduction rows per k-block
+  int a_box_rows = 0;   // K-major A only: rows one box delivers (0 = the whole tile)
 };
 void tc_fill_mma(TcParams& p, const TcOperandLayout& lay);
 int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream);

@@ -35,7 +35,8 @@ struct TcParams {
 
   // ---- shared-memory ring
   int stages;
-  uint32_t stage_bytes;            // bytes landed per stage (= expect_tx)
+  uint32_t stage_bytes;            // distance between ring slots
+  uint32_t tx_bytes;               // bytes the boxes of one k-block deliver (= expect_tx)
   uint32_t a_bytes;                // B region starts at this offset inside a stage
   int a_boxes, b_boxes;            // TMA boxes per stage per operand
   uint32_t a_box_bytes, b_box_bytes;
@@ -47,7 +48,9 @@ struct TcParams {
   int a_zmul, b_zmul;              // batched GEMM: coordinate in dim 2 = z * zmul
   // conv geometry (unused by TC_GEMM)
   int red_chunks;                  // fprop: ceil(C/kb_rows); bprop: ceil(K/64)
-  int RS, S, R;                    // filter taps
+  int RS, S, R;                    // filter taps (tap blocks when tap_w/tap_h > 1)
+  int tap_w, tap_h;                // input pixels per tap step: 1, or the tap-block size of the
+                                   // few-channel modes where one box carries a block of taps
   int pad_d, pad_h, pad_w;
   int str_d, str_h, str_w;
   int inner_tap;                   // N in flattened-(W,N) mode else 0

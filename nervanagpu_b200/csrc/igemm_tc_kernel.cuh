@@ -176,7 +176,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           ok = false;
           break;
         }
-        if (lane == 0) mbar_expect_tx(full_bar(stage), p.stage_bytes);
+        if (lane == 0) mbar_expect_tx(full_bar(stage), p.tx_bytes);
         __syncwarp();
         if (active) {
           int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
@@ -194,8 +194,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               c0 = m0 + kChunk * bi; c1 = trs; c2 = rc * p.kb_rows;
             } else {     // input pixels of this chunk shifted by the tap
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
-              c1 = (cp.q * p.str_w - p.pad_w + tap.s) * p.x_tap;
-              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tap.r : p.oob_y;
+              c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
+              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tap.r * p.tap_h : p.oob_y;
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = rc * p.kb_rows;
             }
@@ -218,8 +218,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           } else {  // TC_UPDATE: k-block = one 64-element chunk of the (m,p,q,n) space
             if (is_a) {  // input pixels under tap z, 128 channels c
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
-              c1 = (cp.q * p.str_w - p.pad_w + tap.s) * p.x_tap;
-              c2 = cp.p * p.str_h - p.pad_h + tap.r;
+              c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
+              c2 = cp.p * p.str_h - p.pad_h + tap.r * p.tap_h;
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = m0;
             } else {     // error pixels, block_n output channels k

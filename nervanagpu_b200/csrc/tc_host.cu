@@ -49,13 +49,15 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
     p.a_half_step = (2u * mn_box) >> 4;
   } else {
     p.a_boxes = 1;
-    p.a_box_bytes = tile_rows * 128u;
+    // a box may deliver fewer rows than the tile has (few-channel update): the rest of the
+    // slot keeps stale data whose products land in rows that are never stored
+    p.a_box_bytes = (lay.a_box_rows ? lay.a_box_rows : tile_rows) * 128u;
     p.a_desc_lo = desc_lo(16);
     p.a_kstep = 32u >> 4;
     p.a_half_step = (kTileM * 128u) >> 4;
   }
   p.a_desc_hi = desc_hi(1024);
-  p.a_bytes = p.a_boxes * p.a_box_bytes;
+  p.a_bytes = lay.a_mn_major ? p.a_boxes * p.a_box_bytes : tile_rows * 128u;
   if (lay.b_mn_major) {
     p.b_boxes = p.block_n / kChunk;
     p.b_box_bytes = mn_box;
@@ -72,6 +74,7 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   p.a_bytes = (p.a_bytes + 1023u) & ~1023u;
   const uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
   p.stage_bytes = p.a_bytes + b_bytes;
+  p.tx_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
   p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes) / p.stage_bytes);
 }
 
@@ -130,14 +133,24 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
 }
 
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems) {
-  if (tiles * 2 > c->sm_count || num_kb < 8) return 1;
-  long long s = (c->sm_count + tiles - 1) / tiles;
-  s = std::min<long long>(s, num_kb / 4);
-  s = std::min<long long>(s, 32);
-  // partials cost 8 bytes of traffic per output element per split; keep them cheap relative
-  // to the operand traffic
-  while (s > 1 && s * out_elems * 4 > (512ll << 20)) --s;
-  return static_cast<int>(std::max<long long>(s, 1));
+  if (tiles >= c->sm_count || num_kb < 8) return 1;
+  // Makespan model: items run in waves of one per SM; an item costs its k-blocks plus a fixed
+  // start-up/drain charge. 17 splits of 9 tiles (153 items on 148 SMs) would take two waves;
+  // 16 splits take one.
+  const long long sm = c->sm_count;
+  long long best = 1, best_cost = -1;
+  for (long long s = 1; s <= 32 && s * 4 <= num_kb; ++s) {
+    // partials cost 8 bytes of traffic per output element per split
+    if (s > 1 && s * out_elems * 4 > (512ll << 20)) break;
+    const long long items = tiles * s;
+    const long long waves = (items + sm - 1) / sm;
+    const long long cost = waves * ((num_kb + s - 1) / s + 6);
+    if (best_cost < 0 || cost < best_cost) {
+      best = s;
+      best_cost = cost;
+    }
+  }
+  return static_cast<int>(best);
 }
 
 int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream) {
@@ -169,10 +182,9 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u);
   TcParams launch = p;
   launch.stage_bytes = p.stage_bytes;
-  // expect_tx must equal the bytes the boxes deliver; regions are box multiples already
-  if (landed != p.stage_bytes) {
-    // padded regions: the kernel's expect_tx uses stage_bytes, so keep them identical
-    return fail(NG_ERR_INVALID_ARG, "internal: stage layout is not a whole number of boxes");
+  // expect_tx must equal the bytes the boxes deliver
+  if (landed != p.tx_bytes || landed > p.stage_bytes) {
+    return fail(NG_ERR_INVALID_ARG, "internal: stage layout and box sizes disagree");
   }
   igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, launch);
   NG_CHECK_LAUNCH();
