@@ -34,6 +34,27 @@ VGG_A = {
 NETWORKS = {"alexnet": ALEXNET, "vgg_a": VGG_A}
 
 
+def shard_minibatch(array, rank, world):
+    """The slice of a (..., N) host array that rank `rank` of `world` works on: images are the
+    innermost dimension of every activation, so a shard is a contiguous copy of N/world columns.
+    N/world must stay a multiple of 8 (the convolution kernels' requirement)."""
+    n = array.shape[-1]
+    if n % world != 0 or (n // world) % 8 != 0:
+        raise ValueError("minibatch of %d cannot be split over %d ranks in multiples of 8" % (n, world))
+    per = n // world
+    return np.ascontiguousarray(array[..., rank * per:(rank + 1) * per])
+
+
+def bucket_layout(sizes, align=8):
+    """Offsets of per-layer slices inside one flat buffer (elements). Every slice starts on an
+    `align`-element boundary so that each view stays 16-byte aligned for fp16 and fp32 alike."""
+    offsets, total = [], 0
+    for s in sizes:
+        offsets.append(total)
+        total += (s + align - 1) // align * align
+    return offsets, total
+
+
 class ConvStack(object):
     """A chain of ConvLayer / PoolLayer objects with their activations, deltas and weights."""
 
@@ -59,16 +80,14 @@ class ConvStack(object):
         self.convs = [l for l in self.layers if isinstance(l, ConvLayer)]
 
         # flat weight / gradient buffers with per-layer views
-        total_f = sum(l.sizeF for l in self.convs)
+        offsets, total_f = bucket_layout([l.sizeF for l in self.convs])
         self.weights_flat = ng.empty((total_f,), dtype=np.float16)
-        self.grads_flat = ng.empty((total_f,), dtype=np.float32)
-        w_host = np.empty(total_f, dtype=np.float16)
-        off = 0
-        for l in self.convs:
+        self.grads_flat = ng.zeros((total_f,), dtype=np.float32)
+        w_host = np.zeros(total_f, dtype=np.float16)
+        for l, off in zip(self.convs, offsets):
             w_host[off:off + l.sizeF] = rng.normal(0.0, 0.01, l.sizeF).astype(np.float16)
             l.weights = self.weights_flat[off:off + l.sizeF].reshape(l.dimF)
             l.updat_out = self.grads_flat[off:off + l.sizeF].reshape(l.dimF)
-            off += l.sizeF
         self.weights_flat.set(w_host)
 
         # activations and deltas

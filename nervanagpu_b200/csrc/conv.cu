@@ -389,7 +389,7 @@ int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* 
   const long long span = 1ll * g.M * g.P * g.Q * g.N;
   // workspace: [split-K partials of the engine, at most 32 splits][Dp]
   const size_t dp_bytes = static_cast<size_t>(ntb) * tb.rows * g.K * 4;
-  const size_t dp_off = (32 * dp_bytes + 255) & ~size_t(255);
+  const size_t dp_off = (kMaxSplits * dp_bytes + 255) & ~size_t(255);
   int rc = ensure_workspace(c, dp_off + dp_bytes);
   if (rc != NG_OK) return rc;
   float* Dp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c->ws) + dp_off);
@@ -612,7 +612,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   if (im2col) {
     // dF[crst][k] = col[crst][span] * E[k][span]^T  (both K-major: an "nt" GEMM with split-K)
     const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
-    const size_t col_off = ((static_cast<size_t>(32) * g.C * RST * g.K * 4) + 255) & ~size_t(255);  // room for partials
+    const size_t col_off = ((static_cast<size_t>(kMaxSplits) * g.C * RST * g.K * 4) + 255) & ~size_t(255);  // room for partials
     rc = ensure_workspace(c, col_off + col_bytes);
     if (rc != NG_OK) return rc;
     __half* col = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(c->ws) + col_off);

@@ -63,6 +63,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
 void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int num_kb);
 
 // Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
+constexpr int kMaxSplits = 160;
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems);
 
 // One GEMM request: C[m x n] = epilogue(op(A) * op(B)); see ng_hgemm for the conventions.

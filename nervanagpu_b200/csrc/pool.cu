@@ -106,8 +106,18 @@ __device__ __forceinline__ void window_max(const PoolGeo& g, const T* __restrict
   }
 }
 
+// first window index along one axis that can contain coordinate x, and the last
+__device__ __forceinline__ void window_range(int x, int pad, int f, int str, int nout, int& lo, int& hi) {
+  // windows w with w*str - pad <= x <= w*str - pad + f - 1
+  const int a = x + pad - f + 1;
+  lo = a <= 0 ? 0 : (a + str - 1) / str;
+  hi = min(nout - 1, (x + pad) / str);
+}
+
+// O and/or arg_out may be null: the forward pass stores the maxima, the first stage of the
+// backward pass stores the flat (c,z,y,x) index of each window's first maximum.
 template <typename T, int V>
-__global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restrict__ O) {
+__global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restrict__ O, int* __restrict__ arg_out) {
   const int nvec = g.N / V;
   const long long total = 1ll * g.K * g.M * g.P * g.Q * nvec;
   for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
@@ -120,19 +130,57 @@ __global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restr
     float best[V];
     int arg[V];
     window_max<T, V>(g, I, k, m, p, q, nv, best, arg);
-    Vec<T, V> out;
+    if (O) {
+      Vec<T, V> out;
 #pragma unroll
-    for (int j = 0; j < V; ++j) out.set(j, best[j]);
-    *reinterpret_cast<Vec<T, V>*>(O + i * V) = out;
+      for (int j = 0; j < V; ++j) out.set(j, best[j]);
+      *reinterpret_cast<Vec<T, V>*>(O + i * V) = out;
+    }
+    if (arg_out) {
+#pragma unroll
+      for (int j = 0; j < V; ++j) arg_out[i * V + j] = arg[j];
+    }
   }
 }
 
-// first window index along one axis that can contain coordinate x, and the last
-__device__ __forceinline__ void window_range(int x, int pad, int f, int str, int nout, int& lo, int& hi) {
-  // windows w with w*str - pad <= x <= w*str - pad + f - 1
-  const int a = x + pad - f + 1;
-  lo = a <= 0 ? 0 : (a + str - 1) / str;
-  hi = min(nout - 1, (x + pad) / str);
+// Second stage of the backward pass: every input element sums the errors of the windows whose
+// recorded argmax it is, visiting them in increasing (k,m,p,q) order.
+template <typename T, int V>
+__global__ void pool_gather_kernel(PoolGeo g, const int* __restrict__ arg, const T* __restrict__ E,
+                                   T* __restrict__ dI) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.C * g.D * g.H * g.W * nvec;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int flat = static_cast<int>(r);
+    const int x = r % g.W; r /= g.W;
+    const int y = r % g.H; r /= g.H;
+    const int z = r % g.D; r /= g.D;
+    const int c = static_cast<int>(r);
+    int k0, k1, m0, m1, p0, p1, q0, q1;
+    window_range(c, g.pad_j, g.J, g.str_j, g.K, k0, k1);
+    window_range(z, g.pad_d, g.T, g.str_d, g.M, m0, m1);
+    window_range(y, g.pad_h, g.R, g.str_h, g.P, p0, p1);
+    window_range(x, g.pad_w, g.S, g.str_w, g.Q, q0, q1);
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+    for (int k = k0; k <= k1; ++k)
+      for (int m = m0; m <= m1; ++m)
+        for (int p = p0; p <= p1; ++p)
+          for (int q = q0; q <= q1; ++q) {
+            const long long o = ((((1ll * k * g.M + m) * g.P + p) * g.Q + q) * g.N) + nv * V;
+            const Vec<T, V> e = *reinterpret_cast<const Vec<T, V>*>(E + o);
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+              if (arg[o + j] == flat) acc[j] += e.get(j);
+          }
+    Vec<T, V> out;
+#pragma unroll
+    for (int j = 0; j < V; ++j) out.set(j, acc[j]);
+    *reinterpret_cast<Vec<T, V>*>(dI + i * V) = out;
+  }
 }
 
 template <typename T, int V>
@@ -225,8 +273,9 @@ __device__ __forceinline__ void window2d(const __half* __restrict__ plane, int H
 }
 
 template <int R, int S, int SH, int SW>
-__global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O, int H,
-                                                          int W, int N, int P, int Q) {
+__global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O,
+                                                          int* __restrict__ arg_out, int H, int W, int N, int P,
+                                                          int Q) {
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int q = t / nvec;
@@ -236,7 +285,74 @@ __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restr
   float best[8];
   int arg[8];
   window2d<R, S, SH, SW>(I + static_cast<long long>(c) * H * W * N, H, W, N, p, q, n0, best, arg);
-  store8(O + ((static_cast<long long>(c) * P + p) * Q + q) * N + n0, best);
+  const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
+  if (O) store8(O + o, best);
+  if (arg_out) {
+    int flat[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) flat[i] = (c * H + p * SH + arg[i] / S) * W + q * SW + arg[i] % S;
+    reinterpret_cast<int4*>(arg_out + o)[0] = make_int4(flat[0], flat[1], flat[2], flat[3]);
+    reinterpret_cast<int4*>(arg_out + o)[1] = make_int4(flat[4], flat[5], flat[6], flat[7]);
+  }
+}
+
+// Backward, second stage: the thread that owns the SH x SW input block (a, b) reads the recorded
+// argmax and the error of each overlapping window once and credits the block input it names.
+template <int R, int S, int SH, int SW>
+__global__ void __launch_bounds__(256) pool2d_gather_kernel(const int* __restrict__ arg, const __half* __restrict__ E,
+                                                           __half* __restrict__ dI, int H, int W, int N, int P, int Q,
+                                                           int BW) {
+  constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
+  const int nvec = N >> 3;
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = t / nvec;
+  if (b >= BW) return;
+  const int n0 = (t - b * nvec) << 3;
+  const int a = blockIdx.y, c = blockIdx.z;
+  float acc[SH][SW][8];
+#pragma unroll
+  for (int dy = 0; dy < SH; ++dy)
+#pragma unroll
+    for (int dx = 0; dx < SW; ++dx)
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[dy][dx][i] = 0.0f;
+#pragma unroll
+  for (int wp = 0; wp < WP; ++wp) {
+    const int p = a - (WP - 1) + wp;
+    if (p < 0 || p >= P) continue;
+#pragma unroll
+    for (int wq = 0; wq < WQ; ++wq) {
+      const int q = b - (WQ - 1) + wq;
+      if (q < 0 || q >= Q) continue;
+      const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
+      const int4 i0 = reinterpret_cast<const int4*>(arg + o)[0], i1 = reinterpret_cast<const int4*>(arg + o)[1];
+      const int idx[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+      const Lanes8 e = load8(E + o);
+#pragma unroll
+      for (int dy = 0; dy < SH; ++dy) {
+        if ((WP - 1 - wp) * SH + dy >= R) continue;
+#pragma unroll
+        for (int dx = 0; dx < SW; ++dx) {
+          if ((WQ - 1 - wq) * SW + dx >= S) continue;
+          const int flat = (c * H + a * SH + dy) * W + b * SW + dx;
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            if (idx[i] == flat) acc[dy][dx][i] += e.v[i];
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int dy = 0; dy < SH; ++dy) {
+    const int y = a * SH + dy;
+    if (y >= H) break;
+#pragma unroll
+    for (int dx = 0; dx < SW; ++dx) {
+      const int x = b * SW + dx;
+      if (x >= W) break;
+      store8(dI + ((static_cast<long long>(c) * H + y) * W + x) * N + n0, acc[dy][dx]);
+    }
+  }
 }
 
 // Each thread owns the SH x SW block of inputs at block coordinates (a, b). The windows that
@@ -305,33 +421,46 @@ __global__ void __launch_bounds__(256) pool2d_bprop_kernel(const __half* __restr
 }
 
 template <int R, int S, int SH, int SW>
-int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, cudaStream_t stream) {
+int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, int* arg_ws,
+                  cudaStream_t stream) {
   const int nvec = g.N / 8;
+  dim3 fgrid((g.Q * nvec + 255) / 256, g.P, g.C);
   if (mode == 0) {
-    dim3 grid((g.Q * nvec + 255) / 256, g.P, g.C);
-    pool2d_fprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
-        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), g.H, g.W, g.N, g.P, g.Q);
-  } else {
+    pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(
+        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), nullptr, g.H, g.W, g.N, g.P, g.Q);
+    NG_CHECK_LAUNCH();
+  } else if (R <= SH && S <= SW) {
+    // windows do not overlap: one pass, each block of inputs sees at most one window
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
     dim3 grid((BW * nvec + 255) / 256, BH, g.C);
     pool2d_bprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
         static_cast<const __half*>(I), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W, g.N, g.P,
         g.Q, BW);
+    NG_CHECK_LAUNCH();
+  } else {
+    pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(static_cast<const __half*>(I), nullptr, arg_ws, g.H,
+                                                                g.W, g.N, g.P, g.Q);
+    NG_CHECK_LAUNCH();
+    const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
+    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(arg_ws, static_cast<const __half*>(EO),
+                                                                 static_cast<__half*>(out), g.H, g.W, g.N, g.P, g.Q, BW);
+    NG_CHECK_LAUNCH();
   }
-  NG_CHECK_LAUNCH();
   return NG_OK;
 }
 
 // returns NG_OK when a specialised kernel ran, 1 when the generic path must be used
-int try_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, cudaStream_t stream) {
+int try_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, int* arg_ws,
+               cudaStream_t stream) {
   const bool plain = g.J == 1 && g.T == 1 && g.D == 1 && g.str_j == 1 && g.str_d == 1 && g.pad_j == 0 &&
                      g.pad_d == 0 && g.pad_h == 0 && g.pad_w == 0 && g.N % 8 == 0 && g.C <= 65535 && g.H <= 65535 &&
                      (reinterpret_cast<uintptr_t>(I) & 15u) == 0 && (reinterpret_cast<uintptr_t>(EO) & 15u) == 0 &&
                      (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
   if (!plain) return 1;
-  if (g.R == 3 && g.S == 3 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<3, 3, 2, 2>(g, I, EO, out, mode, stream);
-  if (g.R == 2 && g.S == 2 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<2, 2, 2, 2>(g, I, EO, out, mode, stream);
-  if (g.R == 3 && g.S == 3 && g.str_h == 3 && g.str_w == 3) return launch_pool2d<3, 3, 3, 3>(g, I, EO, out, mode, stream);
+  if (g.R == 3 && g.S == 3 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<3, 3, 2, 2>(g, I, EO, out, mode, arg_ws, stream);
+  if (g.R == 2 && g.S == 2 && g.str_h == 2 && g.str_w == 2) return launch_pool2d<2, 2, 2, 2>(g, I, EO, out, mode, arg_ws, stream);
+  if (g.R == 3 && g.S == 3 && g.str_h == 3 && g.str_w == 3) return launch_pool2d<3, 3, 3, 3>(g, I, EO, out, mode, arg_ws, stream);
   return 1;
 }
 
@@ -341,29 +470,46 @@ int grid_for(long long total, const DeviceCtx* c) {
 }
 
 template <typename T, int VW>
-int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, const DeviceCtx* c,
+int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, DeviceCtx* c,
              cudaStream_t stream) {
   const bool vec = g.N % VW == 0 && (reinterpret_cast<uintptr_t>(I) & 15u) == 0 &&
                    (reinterpret_cast<uintptr_t>(EO) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
   const long long out_elems = 1ll * g.K * g.M * g.P * g.Q * g.N;
   const long long in_elems = 1ll * g.C * g.D * g.H * g.W * g.N;
+  // backward = record each window's argmax (scratch: one int per output element, in the
+  // library workspace), then gather
+  int* arg_ws = nullptr;
+  if (mode == 1) {
+    int rc = ensure_workspace(c, static_cast<size_t>(out_elems) * sizeof(int));
+    if (rc != NG_OK) return rc;
+    arg_ws = reinterpret_cast<int*>(c->ws);
+  }
   if (sizeof(T) == 2) {
-    const int rc = try_pool2d(g, I, EO, out, mode, stream);
+    const int rc = try_pool2d(g, I, EO, out, mode, arg_ws, stream);
     if (rc <= 0) return rc;
   }
   if (mode == 0) {
     T* O = static_cast<T*>(const_cast<void*>(EO));
-    if (vec) pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O);
-    else pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O);
-  } else {
     if (vec)
-      pool_bprop_kernel<T, VW><<<grid_for(in_elems / VW, c), 256, 0, stream>>>(
-          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out));
+      pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr);
     else
-      pool_bprop_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(
-          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out));
+      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr);
+    NG_CHECK_LAUNCH();
+  } else {
+    if (vec) {
+      pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), nullptr,
+                                                                               arg_ws);
+      NG_CHECK_LAUNCH();
+      pool_gather_kernel<T, VW><<<grid_for(in_elems / VW, c), 256, 0, stream>>>(g, arg_ws, static_cast<const T*>(EO),
+                                                                                static_cast<T*>(out));
+    } else {
+      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), nullptr, arg_ws);
+      NG_CHECK_LAUNCH();
+      pool_gather_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(g, arg_ws, static_cast<const T*>(EO),
+                                                                          static_cast<T*>(out));
+    }
+    NG_CHECK_LAUNCH();
   }
-  NG_CHECK_LAUNCH();
   return NG_OK;
 }
 

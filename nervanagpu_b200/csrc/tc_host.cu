@@ -139,9 +139,11 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
   // 16 splits take one.
   const long long sm = c->sm_count;
   long long best = 1, best_cost = -1;
-  for (long long s = 1; s <= 32 && s * 4 <= num_kb; ++s) {
-    // partials cost 8 bytes of traffic per output element per split
-    if (s > 1 && s * out_elems * 4 > (512ll << 20)) break;
+  for (long long s = 1; s <= kMaxSplits && s * 4 <= num_kb; ++s) {
+    // partials cost 8 bytes of traffic per output element per split: keep them small next to
+    // the operands (and bounded in absolute size)
+    if (s > 1 && s * out_elems * 4 > (256ll << 20)) break;
+    if (s > 32 && s * out_elems * 4 > (16ll << 20)) break;
     const long long items = tiles * s;
     const long long waves = (items + sm - 1) / sm;
     const long long cost = waves * ((num_kb + s - 1) / s + 6);
