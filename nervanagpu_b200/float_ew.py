@@ -451,6 +451,8 @@ class _Emitter(object):
         t = self.plan.tensors[slot]
         if self.plan.flat:
             return "a%d[j]" % slot if self.vec else "IO<%s>::ld(p%d + idx)" % (_CTYPES[t["dtype"]], slot)
+        if isinstance(self.vec, tuple):          # row-vector mode: values are already in registers
+            return "a%d[ch][j]" % slot if self.vec[4][slot] == "v" else "b%d" % slot
         row = "row" if t["take"] != 1 else "take%d[row]" % slot
         col = "col" if t["take"] != 2 else "take%d[col]" % slot
         return "IO<%s>::ld(p%d + (long long)(%s) * s%d_0 + (long long)(%s) * s%d_1)" % (
@@ -586,6 +588,9 @@ def _generate(plan, vec, threads, sr, kernel_name):
         src.append("}")
         return "\n".join(src)
 
+    if isinstance(vec, tuple):
+        return _generate_rowvec(plan, em, vec, sr, src, red_list, out_c)
+
     # ---- 2-D: one row per warp (THREADS == 32) or per CTA ---------------------------------
     if threads == 32:
         src.append("  const int tid = threadIdx.x & 31;")
@@ -659,6 +664,125 @@ def _generate(plan, vec, threads, sr, kernel_name):
     return "\n".join(src)
 
 
+def _generate_rowvec(plan, em, cfg, sr, src, red_list, out_c):
+    _, lpr, nch, cached, kinds = cfg
+    src.append("  const int lane = threadIdx.x & 31, sub = lane / %d, li = lane %% %d;" % (lpr, lpr))
+    src.append("  const long long row_ll = (blockIdx.x * (long long)(blockDim.x >> 5) + (threadIdx.x >> 5)) * %d + sub;"
+               % (32 // lpr))
+    src.append("  const bool row_live = row_ll < n_rows;")
+    src.append("  const int row = row_live ? (int)row_ll : 0;   // idle lanes shadow row 0 so shuffles stay uniform")
+    vslots = [i for i, k in enumerate(kinds) if k == "v"]
+
+    def emit_loads(indent, ch_expr, slots):
+        out = []
+        for sl in slots:
+            ct = _CTYPES[plan.tensors[sl]["dtype"]]
+            out.append("%sIO<%s>::ld8(p%d + (long long)row * s%d_0 + col0, a%d[%s]);" % (indent, ct, sl, sl, sl, ch_expr))
+        return out
+
+    for sl, k in enumerate(kinds):
+        if k == "b":
+            src.append("  const float b%d = IO<%s>::ld(p%d + (long long)row * s%d_0);" %
+                       (sl, _CTYPES[plan.tensors[sl]["dtype"]], sl, sl))
+    arr = nch if cached else 1
+    used_all = set()
+
+    def tensors_used(node, acc):
+        for c in node.children:
+            tensors_used(c, acc)
+        if node.kind == "tensor":
+            acc.add(node.slot)
+        return acc
+
+    tensors_used(plan.value, used_all)
+    in_slots = [sl for sl in vslots if sl in used_all]
+    for sl in in_slots:
+        src.append("  float a%d[%d][8];" % (sl, arr))
+    if cached:
+        src.append("  #pragma unroll")
+        src.append("  for (int ch = 0; ch < %d; ++ch) {" % nch)
+        src.append("    const int col0 = (ch * %d + li) * 8;" % lpr)
+        src.append("    if (col0 < n_cols) {")
+        src += emit_loads("      ", "ch", in_slots)
+        src.append("    } else {")
+        for sl in in_slots:
+            src.append("      for (int j = 0; j < 8; ++j) a%d[ch][j] = 0.0f;" % sl)
+        src.append("    }")
+        src.append("  }")
+
+    def chunk_loop_open():
+        lines = ["  #pragma unroll" if cached else "  // rows too long for registers: re-read per stage",
+                 "  for (int chi = 0; chi < %d; ++chi) {" % nch,
+                 "    const int ch = %s;" % ("chi" if cached else "0"),
+                 "    const int col0 = (chi * %d + li) * 8;" % lpr,
+                 "    if (col0 >= n_cols) continue;"]
+        if not cached:
+            lines += emit_loads("    ", "0", in_slots)
+        return lines
+
+    max_depth = max([r.depth for r in red_list] + [0])
+    for stage in range(1, max_depth + 1):
+        stage_reds = [r for r in red_list if r.depth == stage]
+        loop_names, loop_lines = {}, []
+        mark = len(em.row_lines)
+        updates, inits = [], []
+        for r in stage_reds:
+            i = red_list.index(r)
+            arg = em.emit(r.children[0], loop_names, loop_lines)
+            acc = "r%d" % i
+            if r.name in ("argmax", "argmin"):
+                inits.append("  ArgVal %s; %s.v = 0.0f; %s.i = -1;" % (acc, acc, acc))
+                cmp_ = ">" if r.name == "argmax" else "<"
+                updates.append("if (%s.i < 0 || %s %s %s.v) { %s.v = %s; %s.i = col; }" % (acc, arg, cmp_, acc, acc, arg, acc))
+            else:
+                inits.append("  float %s = %s;" % (acc, _RED_INIT[r.name]))
+                updates.append({"sum": "%s += %s;", "max": "%s = fmaxf(%s, %s);", "min": "%s = fminf(%s, %s);"}[r.name] %
+                               ((acc, arg) if r.name == "sum" else (acc, acc, arg)))
+        src += ["  " + l for l in em.row_lines[mark:]]
+        src += inits
+        src += chunk_loop_open()
+        src.append("    #pragma unroll")
+        src.append("    for (int j = 0; j < 8; ++j) {")
+        src.append("      const int col = col0 + j; const long long lin = (long long)row * n_cols + col; (void)lin; (void)col;")
+        src += ["      " + l for l in loop_lines]
+        src += ["      " + u for u in updates]
+        src.append("    }")
+        src.append("  }")
+        for r in stage_reds:
+            i = red_list.index(r)
+            if r.name in ("argmax", "argmin"):
+                want = "true" if r.name == "argmax" else "false"
+                src.append("  for (int o = %d; o; o >>= 1) { ArgVal t_; t_.v = __shfl_xor_sync(FULL, r%d.v, o); "
+                           "t_.i = __shfl_xor_sync(FULL, r%d.i, o); r%d = arg_better(r%d, t_, %s); }" %
+                           (lpr // 2, i, i, i, i, want))
+                src.append("  const float rr%d = (float)r%d.i;" % (i, i))
+            else:
+                op = {"sum": "r%d += t_;", "max": "r%d = fmaxf(r%d, t_);", "min": "r%d = fminf(r%d, t_);"}[r.name]
+                op = op % ((i,) if r.name == "sum" else (i, i))
+                src.append("  for (int o = %d; o; o >>= 1) { const float t_ = __shfl_xor_sync(FULL, r%d, o); %s }" %
+                           (lpr // 2, i, op))
+                src.append("  const float rr%d = r%d;" % (i, i))
+            em.red_names[r.key] = "rr%d" % i
+
+    loop_names, loop_lines = {}, []
+    mark = len(em.row_lines)
+    value = em.emit(plan.value, loop_names, loop_lines)
+    src += ["  " + l for l in em.row_lines[mark:]]
+    src += chunk_loop_open()
+    src.append("    float o[8]; u32 rnd[8];")
+    src.append("    #pragma unroll")
+    src.append("    for (int j = 0; j < 8; ++j) {")
+    src.append("      const int col = col0 + j; const long long lin = (long long)row * n_cols + col; (void)lin; (void)col;")
+    src += ["      " + l for l in loop_lines]
+    src.append("      o[j] = %s;" % value)
+    src.append("      rnd[j] = %s;" % ("sr_bits ? rng_u32(rng, (u64)lin, 0u) : 0u" if sr else "0u"))
+    src.append("    }")
+    src.append("    if (row_live) IO<%s>::st8(p0 + (long long)row * s0_0 + col0, o, rnd, sr_bits);" % out_c)
+    src.append("  }")
+    src.append("}")
+    return "\n".join(src)
+
+
 # ---------------------------------------------------------------------------------------------
 # compile cache and launch
 # ---------------------------------------------------------------------------------------------
@@ -710,6 +834,9 @@ def _launch_shape(plan):
         vec = size % 8 == 0 and aligned and size > 0
         return vec, 256, sr
     depth = max(list(plan.red_len.values()) + [plan.max_shape[plan.axis]])
+    rowvec = _rowvec_config(plan, depth)
+    if rowvec is not None:
+        return rowvec, 32, sr
     if depth <= 1024:
         threads = 32
     elif depth <= 4096:
@@ -717,6 +844,39 @@ def _launch_shape(plan):
     else:
         threads = 1024
     return False, threads, sr
+
+
+def _rowvec_config(plan, depth):
+    """Row-vector mode for 2-D expressions over short rows with unit inner stride: every lane
+    holds 8 consecutive elements per 16-byte access, 32/LPR rows share a warp, each tensor is read
+    from memory once and kept in registers across the reduction stages.
+    Returns ("row", lanes_per_row, chunks_per_lane, cached, kinds) or None."""
+    n_cols = plan.max_shape[plan.axis]
+    if n_cols % 8 != 0 or n_cols > 4096 or n_cols < 8:
+        return None
+    if any(v != n_cols for v in plan.red_len.values()):
+        return None
+    kinds = []
+    for i, t in enumerate(plan.tensors):
+        if t["take"] or t.get("raw_index"):
+            return None
+        s0, s1 = t["strides"]
+        item = int(t["dtype"][1:])
+        if s1 == 1:
+            if t["tensor"].ptr % 16 != 0 or (s0 * item) % 16 != 0:
+                return None
+            kinds.append("v")
+        elif s1 == 0 and i != 0:
+            kinds.append("b")
+        else:
+            return None
+    chunks = n_cols // 8
+    lpr = 32
+    for cand in (1, 2, 4, 8, 16):
+        if chunks == cand:
+            lpr = cand
+    ch = (chunks + lpr - 1) // lpr
+    return ("row", lpr, ch, ch <= 4, "".join(kinds))
 
 
 class _Launch(object):
@@ -787,7 +947,10 @@ def _prepare(args):
         n_cols = plan.max_shape[axis]
         push(ctypes.c_longlong, n_rows)
         push(ctypes.c_int, n_cols)
-        if threads == 32:
+        if isinstance(vec, tuple):
+            rows_per_block = 8 * (32 // vec[1])
+            grid, block = ((n_rows + rows_per_block - 1) // rows_per_block, 1, 1), (256, 1, 1)
+        elif threads == 32:
             rows_per_block = 8
             grid, block = ((n_rows + rows_per_block - 1) // rows_per_block, 1, 1), (32 * rows_per_block, 1, 1)
         else:

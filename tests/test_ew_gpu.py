@@ -118,7 +118,9 @@ def test_config5_batch_norm_expression(ng):
     ref = rm.batch_norm(a, eps=1e-3, axis=1)
     got = A.get().astype(np.float32)
     ulp = np.maximum(2.0 ** (np.floor(np.log2(np.maximum(np.abs(ref), 2.0 ** -14))) - 10), 2.0 ** -24)
-    assert (np.abs(got - ref) <= ulp).all()
+    # one fp16 ulp, plus the fp32 summation-order slack of a 128-term mean/variance (matters only
+    # for outputs next to zero, whose fp16 ulp is smaller than fp32 rounding of the inputs' mean)
+    assert (np.abs(got - ref) <= ulp + 4e-6).all()
     # axis 0 variant into a separate output
     B = ng.array(a)
     O = ng.empty(a.shape, dtype=np.float32)

@@ -52,7 +52,8 @@ def test_batch_norm_shares_the_mean(lib, ops, fake_tensor):
     src, info = _source(A, expr)
     assert not info["flat"] and info["threads"] == 32
     # two reductions only: sum(A) (shared by both means) and sum((A-mean)^2)
-    assert src.count("row_reduce<32>(r") == 2
+    assert src.count("const float rr") == 2
+    assert "a0[ch][j]" in src and src.count("ld8(p0") == 1     # row read once, kept in registers
     _compiles(lib, src)
 
 
