@@ -287,17 +287,22 @@ def main():
     _lib.check(lib.ng_host_alloc(ctypes.byref(pin_out), out_bytes))
     ctypes.memmove(pin_in.value, stack.host_input.ctypes.data, in_bytes)
 
+    # Every step copies its own minibatch from pinned host memory and returns its last activation
+    # to the host. The copy of minibatch i+1 runs on a second stream while step i computes
+    # (ConvStack.prefetch_input / step_prefetched); the read-back is waited for every step.
     def e2e_step():
-        _lib.check(lib.ng_memcpy_h2d_async(stack.input.ptr, pin_in, in_bytes, ng.stream))
-        stack.step()
+        stack.step_prefetched()                      # waits (on the device) for its minibatch
+        stack.prefetch_input(pin_in)                 # next minibatch, overlapped with this step
         _lib.check(lib.ng_memcpy_d2h_async(pin_out, out_t.ptr, out_bytes, ng.stream))
         _lib.check(lib.ng_stream_sync(ng.stream))
 
+    stack.prefetch_input(pin_in)
     for _ in range(3):
         e2e_step()
     barrier()
     w0 = time.perf_counter()
     e2e_ms_dev = timer.time_ms(e2e_step, args.steps)
+    ng.synchronize()                                 # includes the last prefetch: K steps, K copies
     e2e_wall = (time.perf_counter() - w0) * 1e3
     barrier()
     e2e_ms = max_over_ranks(max(e2e_ms_dev, e2e_wall)) / args.steps

@@ -161,6 +161,46 @@ class ConvStack(object):
     def set_input(self, host_array):
         self.input.set(host_array)
 
+    # ---- pipelined input: the next minibatch is copied while the current step computes -------
+    def _init_prefetch(self):
+        lib = self.ng.lib
+        self._copy_stream = ctypes.c_void_p()
+        _lib.check(lib.ng_stream_create(ctypes.byref(self._copy_stream)))
+        self._next_input = self.ng.empty(self.layers[0].dimI, dtype=np.float16)
+        self._copied, self._consumed = ctypes.c_void_p(), ctypes.c_void_p()
+        _lib.check(lib.ng_event_create(ctypes.byref(self._copied)))
+        _lib.check(lib.ng_event_create(ctypes.byref(self._consumed)))
+        self._prefetch_pending = False
+        self._consumed_recorded = False
+
+    def prefetch_input(self, pinned_host_ptr):
+        """Start the host-to-device copy of the next minibatch (pinned host memory) on a separate
+        stream into the spare input buffer. It overlaps whatever the compute stream is doing."""
+        if not hasattr(self, "_copy_stream"):
+            self._init_prefetch()
+        lib = self.ng.lib
+        if self._consumed_recorded:
+            # the spare buffer was the live input until the step that recorded this event finished
+            _lib.check(lib.ng_stream_wait_event(self._copy_stream, self._consumed))
+        _lib.check(lib.ng_memcpy_h2d_async(self._next_input.ptr, pinned_host_ptr, self._next_input.nbytes,
+                                           self._copy_stream))
+        _lib.check(lib.ng_event_record(self._copied, self._copy_stream))
+        self._prefetch_pending = True
+
+    def step_prefetched(self):
+        """Swap in the prefetched minibatch (waiting for its copy on the device, not on the host)
+        and run one step."""
+        lib = self.ng.lib
+        if self._prefetch_pending:
+            _lib.check(lib.ng_stream_wait_event(self.ng.stream, self._copied))
+            self.input, self._next_input = self._next_input, self.input
+            self._prefetch_pending = False
+            # everything queued so far (the previous step, which read what is now the spare
+            # buffer) is done when this event fires; the next copy waits for it, not for this step
+            _lib.check(lib.ng_event_record(self._consumed, self.ng.stream))
+            self._consumed_recorded = True
+        self.step()
+
 
 def _relu_mask(grad, act):
     grad[:] = grad * (act > 0)

@@ -275,6 +275,21 @@ struct TapBlock {
   bool ok = false;
 };
 
+// Weight update with few input rows per tap: one work item accumulates `acc_groups` taps at once
+// (one TMEM accumulator each), so every chunk of the error tensor is fetched once per group of
+// taps instead of once per tap. The group is limited by tensor memory (512 columns), by the
+// shared-memory ring (at least four stages must remain) and balanced over the slices.
+void set_update_groups(TcParams& p, int taps, int a_rows) {
+  static const char* cap = getenv("NG_UPDATE_GROUPS");
+  int g = std::min(std::min(8, 512 / p.block_n), taps);
+  if (cap) g = std::max(1, std::min(g, atoi(cap)));
+  const int ring = 232448 - 1024 - 512 - static_cast<int>(kEpiStageBytes) - kTileM * 128;
+  while (g > 1 && (g * a_rows * 128 + p.block_n * 128) * 4 > ring) --g;
+  p.nz = (taps + g - 1) / g;
+  p.acc_groups = (taps + p.nz - 1) / p.nz;
+  p.nz_out = taps;
+}
+
 TapBlock pick_tap_block(const Geo& g) {
   TapBlock best;
   long long best_cost = 0;
@@ -399,7 +414,7 @@ int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* 
   p.M = tb.rows; p.N = g.K;
   p.m_halves = 1; p.tiles_m = 1;
   p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
-  p.nz = ntb;
+  set_update_groups(p, ntb, tb.rows);
   TcOperandLayout lay = {0, 0, kChunk};
   lay.a_box_rows = tb.rows;
   p.num_kb = static_cast<int>(span / kChunk);
@@ -595,6 +610,13 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     // the reduction is split to fill the SMs whatever the tile count, so only the operand
     // traffic argues: assume many column tiles
     tc_pick_tile_rows(c, p, 64ll * p.tiles_n * p.nz, p.num_kb);
+    int a_rows = kTileM * p.m_halves;
+    if (g.C <= 64) {
+      // short A boxes leave room in the ring for several taps per work item
+      a_rows = (g.C + 7) / 8 * 8;
+      lay.a_box_rows = a_rows;
+      set_update_groups(p, RST, a_rows);
+    }
     tc_fill_mma(p, lay);
     fill_taps(p, g, mode);
     fill_decode(p, g.N, g.Q, g.P, g.M, mode);
@@ -603,7 +625,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = out_f32; p.vec_ok = 1;
     p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n * p.nz, p.num_kb, 1ll * g.C * g.K * RST);
     CUtensorMap mapA, mapB;
-    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, kTileM * p.m_halves);
+    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, a_rows);
     if (rc != NG_OK) return rc;
     rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, p.block_n);
     if (rc != NG_OK) return rc;

@@ -10,7 +10,7 @@ enum TcMode : int { TC_GEMM = 0, TC_FPROP = 1, TC_BPROP = 2, TC_UPDATE = 3 };
 
 constexpr int kTileM = 128;        // UMMA M (TMEM lanes)
 constexpr int kChunk = 64;         // fp16 elements per 128-byte swizzle row
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 16;
 constexpr int kEpiWarps = 8;       // two per group of 32 TMEM lanes, each takes half of the columns
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;    // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr uint32_t kEpiStageBytes = kEpiWarps * 4096;  // one [32 rows][128 B] staging box per epilogue warp
@@ -23,6 +23,9 @@ struct TcParams {
   int block_n;         // UMMA N: 64, 128 or 256
   int m_halves;        // 1: 128-row tiles, accumulator double-buffered across tiles
                        // 2: 256-row tiles, two accumulators that share every B operand
+  int acc_groups;      // weight update only: accumulators per work item (taps z*g .. z*g+g-1 share
+                       // every B operand); 1 otherwise. Needs m_halves == 1, g * block_n <= 512.
+  int nz_out;          // number of output slices (= nz unless acc_groups > 1, then nz = ceil(nz_out / g))
   int M, N;            // logical output extent (rows, cols)
 
   // ---- MMA descriptors (host-built)

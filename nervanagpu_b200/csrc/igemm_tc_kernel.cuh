@@ -162,13 +162,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       ChunkPos cp = {0, 0, 0, 0, true};   // fprop/bprop: pixel chunk of this B box; update: walks
       Tap tap = {0, 0, 0};                // fprop/bprop: walks the filter taps; update: fixed (z)
       int trs = 0, rc = 0;                // tap number and reduction-chunk number inside the tap
+      bool tap_live = true;               // update: this A box's tap exists (last group may be short)
       if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
         if (!is_a) cp = decode_chunk(p, n0 / kChunk + bi);
         trs = it.kb0 / p.red_chunks;
         rc = it.kb0 - trs * p.red_chunks;
         tap = decode_tap(p, trs);
       } else if (p.mode == TC_UPDATE) {
-        tap = decode_tap(p, it.z);
+        // with several accumulators per item, A box `bi` belongs to tap it.z * groups + bi
+        const int zt = it.z * p.acc_groups + (is_a ? bi : 0);
+        tap = decode_tap(p, zt);
+        tap_live = zt < p.nz_out;
         cp = decode_chunk(p, it.kb0);
       }
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
@@ -219,7 +223,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             if (is_a) {  // input pixels under tap z, 128 channels c
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
               c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
-              c2 = cp.p * p.str_h - p.pad_h + tap.r * p.tap_h;
+              c2 = tap_live ? cp.p * p.str_h - p.pad_h + tap.r * p.tap_h : p.oob_y;
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = m0;
             } else {     // error pixels, block_n output channels k
@@ -262,12 +266,16 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       int local = 0;
       bool ok = true;
       const bool wide = p.m_halves == 2;
+      // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
+      // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
+      const bool grouped = p.acc_groups > 1;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++local) {
         const WorkItem it = decode_work(p, w);
-        const int acc = wide ? 0 : (local & 1);
-        const uint32_t acc_phase = wide ? (local & 1u) : ((local >> 1) & 1u);
-        // rows of the second half that lie beyond M need no MMAs
-        const int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
+        const int acc = (wide || grouped) ? 0 : (local & 1);
+        const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
+        // rows of the second half that lie beyond M need no MMAs; taps beyond the last need none
+        int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
+        if (grouped) halves = min(p.acc_groups, p.nz_out - it.z * p.acc_groups);
         if (!wide) {
           if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
           tc_fence_after();
@@ -288,7 +296,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               }
               tc_fence_after();
             }
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>((wide ? h : acc) * p.block_n);
+            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
             const uint32_t sah = sa + h * p.a_half_step;
             for (int k = 0; k < p.mma_per_kb; ++k) {
               const uint64_t adesc = (static_cast<uint64_t>(p.a_desc_hi) << 32) |
@@ -317,35 +325,40 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
+    const bool grouped = p.acc_groups > 1;
+    const int n_acc = wide ? 2 : p.acc_groups;   // accumulators of one work item
     int local = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++local) {
       const WorkItem it = decode_work(p, w);
-      const int acc = wide ? 0 : (local & 1);
-      const uint32_t acc_phase = wide ? (local & 1u) : ((local >> 1) & 1u);
+      const int acc = (wide || grouped) ? 0 : (local & 1);
+      const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
       tc_fence_after();
       const int n0 = it.tile_n * p.block_n;
       const bool partial = p.splits > 1;
-      for (int h = 0; h < p.m_halves; ++h) {
-        const int row = (it.tile_m * p.m_halves + h) * kTileM + lane_group * 32 + lane;
+      for (int h = 0; h < n_acc; ++h) {
+        // accumulator h holds rows of row-tile `rt` of output slice `zt`
+        const int rt = wide ? it.tile_m * 2 + h : it.tile_m;
+        const int zt = grouped ? it.z * p.acc_groups + h : it.z;
+        const int row = rt * kTileM + lane_group * 32 + lane;
         const bool row_ok = row < p.M;
-        // whole half beyond M: nothing was accumulated there, nothing to store
-        const bool half_live = (it.tile_m * p.m_halves + h) * kTileM < p.M;
+        // whole accumulator beyond M (or beyond the last tap): nothing accumulated, nothing to store
+        const bool half_live = rt * kTileM < p.M && zt < p.nz_out;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
-                               static_cast<uint32_t>((wide ? h : acc) * p.block_n);
+                               static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
         // row base pointers
         uint8_t* crow = nullptr;
         const uint8_t* oldrow = nullptr;
         unsigned long long lin_row = 0;
         if (partial) {
-          const long long off = ((static_cast<long long>(it.split) * p.nz + it.z) * p.M + row) * p.N;
+          const long long off = ((static_cast<long long>(it.split) * p.nz_out + zt) * p.M + row) * p.N;
           crow = reinterpret_cast<uint8_t*>(p.ws + off);
         } else {
-          const long long off = it.z * p.c_zstride + static_cast<long long>(row) * p.ldc;
+          const long long off = zt * p.c_zstride + static_cast<long long>(row) * p.ldc;
           const int esz = p.out_f32 ? 4 : 2;
           crow = static_cast<uint8_t*>(p.C) + off * esz;
           oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
-          lin_row = (static_cast<unsigned long long>(it.z) * p.M + row) * static_cast<unsigned long long>(p.N);
+          lin_row = (static_cast<unsigned long long>(zt) * p.M + row) * static_cast<unsigned long long>(p.N);
         }
         if (p.tma_store) {
           // Staged path: 32 rows x 128 bytes per box, written to shared memory in the 128-byte
@@ -353,8 +366,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           // for the per-row writes below), then one bulk tensor store per box. The store clips
           // rows >= M and columns >= N itself.
           const int epi_warp = warp - 2;
-          const int row0 = (it.tile_m * p.m_halves + h) * kTileM + lane_group * 32;
-          const int zc = partial ? it.split * p.nz + it.z : it.z;
+          const int row0 = rt * kTileM + lane_group * 32;
+          const int zc = partial ? it.split * p.nz_out + zt : zt;
           const int subs = p.c_box_cols / 32;            // tcgen05.ld groups per box: 2 (fp16) or 1 (fp32)
           const int n_boxes = p.block_n / p.c_box_cols;
           const int cb0 = col_group == 0 ? 0 : (n_boxes + 1) / 2;

@@ -12,7 +12,7 @@ namespace ngb {
 
 namespace {
 constexpr uint32_t kSmemLimit = 232448;  // 227 KB opt-in dynamic shared memory per CTA
-constexpr uint32_t kCtrlBytes = 256;     // barriers + TMEM slot + abort flag
+constexpr uint32_t kCtrlBytes = 512;     // barriers + TMEM slot + abort flag
 constexpr uint32_t kLayoutSw128 = 2;     // UMMA shared-memory descriptor layout type
 
 // Upper 32 bits of a shared-memory matrix descriptor: stride byte offset [32,46), descriptor
@@ -23,6 +23,14 @@ uint32_t desc_hi(uint32_t sbo_bytes) {
 // Lower 32 bits without the start address: leading byte offset in [16,30).
 uint32_t desc_lo(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3fffu) << 16; }
 }  // namespace
+
+// Bytes a K-major A descriptor may read past its (short) slot; kept inside the allocation.
+static uint32_t a_overread(const TcParams& p) {
+  if (p.a_mn_major) return 0u;
+  const uint32_t full = kTileM * p.m_halves * 128u;
+  const uint32_t last_end = (p.a_boxes > 1 ? (p.a_boxes - 1) * p.a_box_bytes : 0u) + full;
+  return last_end > p.a_bytes ? last_end - p.a_bytes : 0u;
+}
 
 void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   p.a_mn_major = lay.a_mn_major;
@@ -48,16 +56,21 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
     p.a_kstep = 2048u >> 4;
     p.a_half_step = (2u * mn_box) >> 4;
   } else {
-    p.a_boxes = 1;
+    if (p.acc_groups < 1) p.acc_groups = 1;
+    p.a_boxes = p.acc_groups;   // grouped update: one A box per accumulator
     // a box may deliver fewer rows than the tile has (few-channel update): the rest of the
     // slot keeps stale data whose products land in rows that are never stored
     p.a_box_bytes = (lay.a_box_rows ? lay.a_box_rows : tile_rows) * 128u;
     p.a_desc_lo = desc_lo(16);
     p.a_kstep = 32u >> 4;
-    p.a_half_step = (kTileM * 128u) >> 4;
+    p.a_half_step = (p.acc_groups > 1 ? p.a_box_bytes : kTileM * 128u) >> 4;
   }
+  if (p.acc_groups < 1) p.acc_groups = 1;
   p.a_desc_hi = desc_hi(1024);
-  p.a_bytes = lay.a_mn_major ? p.a_boxes * p.a_box_bytes : tile_rows * 128u;
+  // A slot: the rows the box delivers. When that is fewer than the MMA's 128 rows the instruction
+  // also reads what follows (the B slot, the next stage, the staging area: all inside this CTA's
+  // allocation); those products fall in accumulator rows that are never stored.
+  p.a_bytes = p.a_boxes * p.a_box_bytes;
   if (lay.b_mn_major) {
     p.b_boxes = p.block_n / kChunk;
     p.b_box_bytes = mn_box;
@@ -75,7 +88,8 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   const uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
   p.stage_bytes = p.a_bytes + b_bytes;
   p.tx_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
-  p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes) / p.stage_bytes);
+  p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes - a_overread(p)) /
+                                               p.stage_bytes);
 }
 
 // Output tensor map for the bulk-store epilogue: (columns, rows, z) over C, or over the split-K
@@ -92,15 +106,15 @@ static bool make_store_map(CUtensorMap* map, TcParams& p) {
   const void* base;
   if (partial) {
     base = p.ws;
-    dims[2] = static_cast<uint64_t>(p.nz) * p.splits;
+    dims[2] = static_cast<uint64_t>(p.nz_out) * p.splits;
     str[0] = static_cast<uint64_t>(p.N) * 4;
     str[1] = str[0] * p.M;
   } else {
     if (!p.vec_ok) return false;
     base = p.C;
-    dims[2] = p.nz;
+    dims[2] = p.nz_out;
     str[0] = static_cast<uint64_t>(p.ldc) * esz;
-    str[1] = p.nz > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : str[0] * p.M;
+    str[1] = p.nz_out > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : str[0] * p.M;
     if (str[1] == 0) return false;
   }
   str[2] = str[3] = std::max(str[1] * dims[2], str[0] * dims[1]);
@@ -158,6 +172,11 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
 int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream) {
   if (p.num_kb < 1) return fail(NG_ERR_INVALID_ARG, "empty reduction");
   if (p.splits < 1) p.splits = 1;
+  if (p.acc_groups < 1) p.acc_groups = 1;
+  if (p.nz_out < 1) p.nz_out = p.nz;
+  if (p.acc_groups > 1 && (p.m_halves != 1 || p.acc_groups * p.block_n > 512)) {
+    return fail(NG_ERR_INVALID_ARG, "internal: grouped accumulators do not fit tensor memory");
+  }
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty partitions
   p.status = c->status;
@@ -165,7 +184,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   // stage_bytes was sized from padded regions; the bytes that actually land are:
   const uint32_t landed = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
   if (p.splits > 1) {
-    const size_t need = static_cast<size_t>(p.splits) * p.nz * p.M * p.N * sizeof(float);
+    const size_t need = static_cast<size_t>(p.splits) * p.nz_out * p.M * p.N * sizeof(float);
     int rc = ensure_workspace(c, need);
     if (rc != NG_OK) return rc;
     p.ws = c->ws;
@@ -181,7 +200,8 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
   CUtensorMap mapC = mapA;   // placeholder when the bulk-store epilogue is off
   p.tma_store = make_store_map(&mapC, p) ? 1 : 0;
-  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u);
+  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u) +
+                        a_overread(p);
   TcParams launch = p;
   launch.stage_bytes = p.stage_bytes;
   // expect_tx must equal the bytes the boxes deliver
@@ -194,10 +214,10 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     EpiArgs ea;
     ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
-    const long long groups = static_cast<long long>(p.nz) * p.M * ((p.N + 7) / 8);
+    const long long groups = static_cast<long long>(p.nz_out) * p.M * ((p.N + 7) / 8);
     const int threads = 256;
     const int blocks = static_cast<int>(std::min<long long>((groups + threads - 1) / threads, c->sm_count * 8ll));
-    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p.ws, p.splits, p.nz, p.M, p.N, p.C, p.Cold, p.ldc,
+    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p.ws, p.splits, p.nz_out, p.M, p.N, p.C, p.Cold, p.ldc,
                                                          p.c_zstride, p.out_f32, p.vec_ok, ea);
     NG_CHECK_LAUNCH();
   }
@@ -292,6 +312,8 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   p.tiles_m = (m + kTileM - 1) / kTileM;
   p.tiles_n = (n + p.block_n - 1) / p.block_n;
   p.nz = 1;
+  p.nz_out = 1;
+  p.acc_groups = 1;
   p.num_kb = (k + kChunk - 1) / kChunk;
   TcOperandLayout lay;
   lay.a_mn_major = a_t ? 1 : 0;
