@@ -60,6 +60,8 @@ struct TcParams {
   int x_tap;                       // 0 in flattened mode else 1
   int dec_cpi, dec_q, dec_p, dec_m;  // chunk decode of the pixel space the chunks walk
   int oob_y;                       // a y/p coordinate that is out of range (forces zero fill)
+  int l2_prefetch;                 // bit 0: A boxes, bit 1: B boxes are requested into L2 ahead of the loads
+  int l2_ahead;                    // how many k-blocks ahead
 
   // ---- epilogue
   void* C;                         // fp16 or fp32 output

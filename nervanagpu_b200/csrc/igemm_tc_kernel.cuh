@@ -56,6 +56,13 @@ __device__ __forceinline__ Tap decode_tap(const TcParams& p, int trs) {
   return tp;
 }
 
+// Producer state that is stepped from one k-block to the next.
+struct Walk {
+  ChunkPos cp;
+  Tap tap;
+  int trs, rc, kb;
+};
+
 // Exact division for the strided gather of the backward pass: returns false when `num` is not
 // a multiple of `den` (that tap does not touch this pixel).
 __device__ __forceinline__ bool div_exact(int num, int den, int& out) {
@@ -159,31 +166,31 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // Per-tile state of this lane's box. Everything that changes from one k-block to the next
       // is kept as counters that are stepped, not re-derived: integer division by run-time
       // values costs this single warp more than the MMAs of a k-block take.
-      ChunkPos cp = {0, 0, 0, 0, true};   // fprop/bprop: pixel chunk of this B box; update: walks
-      Tap tap = {0, 0, 0};                // fprop/bprop: walks the filter taps; update: fixed (z)
-      int trs = 0, rc = 0;                // tap number and reduction-chunk number inside the tap
-      bool tap_live = true;               // update: this A box's tap exists (last group may be short)
+      Walk wk;
+      wk.cp = {0, 0, 0, 0, true};   // fprop/bprop: pixel chunk of this B box; update: walks
+      wk.tap = {0, 0, 0};           // fprop/bprop: walks the filter taps; update: fixed (z)
+      wk.trs = 0; wk.rc = 0;        // tap number and reduction-chunk number inside the tap
+      wk.kb = it.kb0;
+      bool tap_live = true;         // update: this A box's tap exists (last group may be short)
       if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
-        if (!is_a) cp = decode_chunk(p, n0 / kChunk + bi);
-        trs = it.kb0 / p.red_chunks;
-        rc = it.kb0 - trs * p.red_chunks;
-        tap = decode_tap(p, trs);
+        if (!is_a) wk.cp = decode_chunk(p, n0 / kChunk + bi);
+        wk.trs = it.kb0 / p.red_chunks;
+        wk.rc = it.kb0 - wk.trs * p.red_chunks;
+        wk.tap = decode_tap(p, wk.trs);
       } else if (p.mode == TC_UPDATE) {
         // with several accumulators per item, A box `bi` belongs to tap it.z * groups + bi
         const int zt = it.z * p.acc_groups + (is_a ? bi : 0);
-        tap = decode_tap(p, zt);
+        wk.tap = decode_tap(p, zt);
         tap_live = zt < p.nz_out;
-        cp = decode_chunk(p, it.kb0);
+        wk.cp = decode_chunk(p, it.kb0);
       }
-      for (int kb = it.kb0; kb < it.kb1; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER)) {
-          ok = false;
-          break;
-        }
-        if (lane == 0) mbar_expect_tx(full_bar(stage), p.tx_bytes);
-        __syncwarp();
-        if (active) {
-          int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
+      // box coordinates of this lane's box at walker position `s`
+      auto coords = [&](const Walk& s, int& c0, int& c1, int& c2, int& c3, int& c4) {
+        const ChunkPos& cp = s.cp;
+        const Tap& tap = s.tap;
+        const int trs = s.trs, rc = s.rc, kb = s.kb;
+        c0 = c1 = c2 = c3 = c4 = 0;
+        {
           if (p.mode == TC_GEMM) {
             const int k0 = kb * kChunk;
             if (is_a) {
@@ -230,27 +237,66 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               c0 = cp.inner0; c1 = cp.q * p.x_tap; c2 = cp.p; c3 = cp.m; c4 = n0;
             }
           }
-          tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
-        // step the walkers to the next k-block
+      };
+      // step a walker to the next k-block
+      auto advance = [&](Walk& s) {
+        ++s.kb;
         if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
-          if (++rc == p.red_chunks) {
-            rc = 0;
-            ++trs;
-            if (++tap.s == p.S) {
-              tap.s = 0;
-              if (++tap.r == p.R) { tap.r = 0; ++tap.t; }
+          if (++s.rc == p.red_chunks) {
+            s.rc = 0;
+            ++s.trs;
+            if (++s.tap.s == p.S) {
+              s.tap.s = 0;
+              if (++s.tap.r == p.R) { s.tap.r = 0; ++s.tap.t; }
             }
           }
         } else if (p.mode == TC_UPDATE) {
-          cp.inner0 += kChunk;
-          if (cp.inner0 == p.dec_cpi * kChunk) {
-            cp.inner0 = 0;
-            if (++cp.q == p.dec_q) {
-              cp.q = 0;
-              if (++cp.p == p.dec_p) { cp.p = 0; ++cp.m; }
+          s.cp.inner0 += kChunk;
+          if (s.cp.inner0 == p.dec_cpi * kChunk) {
+            s.cp.inner0 = 0;
+            if (++s.cp.q == p.dec_q) {
+              s.cp.q = 0;
+              if (++s.cp.p == p.dec_p) { s.cp.p = 0; ++s.cp.m; }
             }
           }
+        }
+      };
+      // A second walker runs `l2_ahead` k-blocks in front and asks the L2 for those boxes, so that
+      // the loads proper find their lines there: a load that waits for DRAM holds up the copy
+      // engine's queue behind it.
+      Walk pre = wk;
+      const bool pf_lane = active && tap_live && ((is_a ? p.l2_prefetch & 1 : p.l2_prefetch & 2) != 0);
+      if (p.l2_prefetch) {
+        for (int i = 0; i < p.l2_ahead && pre.kb < it.kb1; ++i) {
+          if (pf_lane) {
+            int c0, c1, c2, c3, c4;
+            coords(pre, c0, c1, c2, c3, c4);
+            tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
+          }
+          advance(pre);
+        }
+      }
+      for (int kb = it.kb0; kb < it.kb1; ++kb) {
+        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER)) {
+          ok = false;
+          break;
+        }
+        if (lane == 0) mbar_expect_tx(full_bar(stage), p.tx_bytes);
+        __syncwarp();
+        if (active) {
+          int c0, c1, c2, c3, c4;
+          coords(wk, c0, c1, c2, c3, c4);
+          tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
+        }
+        advance(wk);
+        if (p.l2_prefetch && pre.kb < it.kb1) {
+          if (pf_lane) {
+            int c0, c1, c2, c3, c4;
+            coords(pre, c0, c1, c2, c3, c4);
+            tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
+          }
+          advance(pre);
         }
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }

@@ -180,6 +180,13 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty partitions
   p.status = c->status;
+  {
+    // NG_L2_PREFETCH=<bits> / NG_L2_AHEAD=<k-blocks> override the policy (tuning aid)
+    static const char* pf = getenv("NG_L2_PREFETCH");
+    static const char* ahead = getenv("NG_L2_AHEAD");
+    p.l2_prefetch = pf ? atoi(pf) : (p.mode == TC_UPDATE ? 3 : 0);
+    p.l2_ahead = ahead ? std::max(1, atoi(ahead)) : 8;
+  }
   // TMA counts the whole box (including zero-filled parts) against the barrier
   // stage_bytes was sized from padded regions; the bytes that actually land are:
   const uint32_t landed = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
