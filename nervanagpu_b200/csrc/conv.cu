@@ -279,15 +279,31 @@ struct TapBlock {
 // (one TMEM accumulator each), so every chunk of the error tensor is fetched once per group of
 // taps instead of once per tap. The group is limited by tensor memory (512 columns), by the
 // shared-memory ring (at least four stages must remain) and balanced over the slices.
+// Taps with at most 64 rows are also stacked along the 128 rows of one accumulator (`acc_taps`
+// boxes of a_rows rows each), which halves (or better) the MMAs a tap costs.
 void set_update_groups(TcParams& p, int taps, int a_rows) {
-  static const char* cap = getenv("NG_UPDATE_GROUPS");
-  int g = std::min(std::min(8, 512 / p.block_n), taps);
+  static const char* cap = getenv("NG_UPDATE_GROUPS");   // tuning aid: limits on groups / stacking
+  static const char* cap_t = getenv("NG_UPDATE_STACK");
+  int t = std::max(1, std::min(std::min(kTileM / a_rows, 8), taps));
+  if (cap_t) t = std::max(1, std::min(t, atoi(cap_t)));
+  const int accs = (taps + t - 1) / t;                    // accumulators the whole filter needs
+  int g = std::min(std::min(8, 512 / p.block_n), accs);
   if (cap) g = std::max(1, std::min(g, atoi(cap)));
   const int ring = 232448 - 1024 - 512 - static_cast<int>(kEpiStageBytes) - kTileM * 128;
-  while (g > 1 && (g * a_rows * 128 + p.block_n * 128) * 4 > ring) --g;
-  p.nz = (taps + g - 1) / g;
-  p.acc_groups = (taps + p.nz - 1) / p.nz;
+  while (g > 1 && ((g * t * a_rows * 128 + p.block_n * 128) * 4 > ring || g * t > 24)) --g;
+  p.nz = (accs + g - 1) / g;
+  p.acc_groups = (accs + p.nz - 1) / p.nz;
+  p.acc_taps = t;
+  p.pack_rows = a_rows;
   p.nz_out = taps;
+}
+
+// Column tile of the weight update (output channels): the smallest multiple of 64 that covers K
+// in the fewest tiles, so that K = 192 or 384 does not pay for 256-wide MMAs.
+int update_block_n(int K) {
+  const int tiles = (K + 255) / 256;
+  const int per = (K + tiles - 1) / tiles;
+  return (per + 63) / 64 * 64;
 }
 
 TapBlock pick_tap_block(const Geo& g) {
@@ -410,7 +426,7 @@ int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* 
   float* Dp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c->ws) + dp_off);
   TcParams p = {};
   p.mode = TC_UPDATE;
-  p.block_n = g.K <= 64 ? 64 : (g.K <= 128 ? 128 : 256);
+  p.block_n = update_block_n(g.K);
   p.M = tb.rows; p.N = g.K;
   p.m_halves = 1; p.tiles_m = 1;
   p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
@@ -601,7 +617,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   if (direct) {
     TcParams p = {};
     p.mode = TC_UPDATE;
-    p.block_n = g.K <= 64 ? 64 : (g.K <= 128 ? 128 : 256);
+    p.block_n = update_block_n(g.K);
     p.M = g.C; p.N = g.K;
     p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
     p.nz = RST;

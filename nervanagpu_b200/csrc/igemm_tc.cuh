@@ -25,7 +25,12 @@ struct TcParams {
                        // 2: 256-row tiles, two accumulators that share every B operand
   int acc_groups;      // weight update only: accumulators per work item (taps z*g .. z*g+g-1 share
                        // every B operand); 1 otherwise. Needs m_halves == 1, g * block_n <= 512.
-  int nz_out;          // number of output slices (= nz unless acc_groups > 1, then nz = ceil(nz_out / g))
+  int acc_taps;        // weight update only: taps stacked along the rows of one accumulator (each
+                       // `pack_rows` rows: t * pack_rows <= 128), so that a tap with few rows does
+                       // not cost a whole 128-row MMA; 1 otherwise
+  int pack_rows;       // rows per stacked tap (= rows of one A box)
+  int nz_out;          // number of output slices (= nz unless taps are grouped or stacked, then
+                       // nz = ceil(nz_out / (acc_groups * acc_taps)))
   int M, N;            // logical output extent (rows, cols)
 
   // ---- MMA descriptors (host-built)

@@ -5,12 +5,19 @@
 // and a fused epilogue (alpha, ReLU, beta*C, round-to-nearest or stochastic rounding, fp16 or
 // fp32 store, or raw fp32 split-K partials).
 //
-//   warp 0      TMA producer: up to six lanes each issue one box per k-block
+//   warp 0      TMA producer: one lane per box of a k-block issues the load
 //   warp 1      allocates TMEM, one lane issues tcgen05.mma and the commits
-//   warps 2..5  epilogue: tcgen05.ld 32 lanes x 32 columns at a time, convert, store
+//   warps 2..9  epilogue: two warps per group of 32 TMEM lanes, each takes half of the columns;
+//               tcgen05.ld 32 lanes x 32 columns at a time, convert, then either a bulk tensor
+//               store through swizzled shared memory or stores straight from registers
 //
-// The accumulator is double-buffered in TMEM (2 x block_n columns) so the epilogue of tile i
-// overlaps the main loop of tile i+1.  All waits are bounded (see mbar_wait).
+// TMEM holds 512 fp32 columns, used in one of three ways:
+//   128-row tiles   two accumulators of block_n columns, double-buffered across tiles so that the
+//                   epilogue of tile i overlaps the main loop of tile i+1
+//   256-row tiles   two accumulators that share every B operand (half the B traffic per flop)
+//   weight update   up to eight accumulators, one per group of filter taps, that share every
+//                   chunk of the error tensor; taps with few rows are stacked inside one accumulator
+// All waits are bounded (see mbar_wait).
 //
 // It replaces the reference's register-tiled FFMA kernels: hgemm_{nn,nt,tn}_* for ng.dot
 // (nervanagpu/nervanagpu.py:959-1105), hconv_fprop_K64_N64, hconv_bprop_C64_N64/C32_N64 and
@@ -179,7 +186,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         wk.tap = decode_tap(p, wk.trs);
       } else if (p.mode == TC_UPDATE) {
         // with several accumulators per item, A box `bi` belongs to tap it.z * groups + bi
-        const int zt = it.z * p.acc_groups + (is_a ? bi : 0);
+        // (and with several taps stacked in one accumulator, to tap it.z * groups * taps + bi)
+        const int zt = it.z * p.acc_groups * p.acc_taps + (is_a ? bi : 0);
         wk.tap = decode_tap(p, zt);
         tap_live = zt < p.nz_out;
         wk.cp = decode_chunk(p, it.kb0);
@@ -278,15 +286,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
       }
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
-        if (!mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER)) {
+        // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
+        // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
+        int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
+        if (active) coords(wk, c0, c1, c2, c3, c4);
+        const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER);
+        if (lane == 0 && got) mbar_expect_tx(full_bar(stage), p.tx_bytes);
+        if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
-        if (lane == 0) mbar_expect_tx(full_bar(stage), p.tx_bytes);
-        __syncwarp();
         if (active) {
-          int c0, c1, c2, c3, c4;
-          coords(wk, c0, c1, c2, c3, c4);
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
         advance(wk);
@@ -314,14 +324,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const bool wide = p.m_halves == 2;
       // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
       // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
-      const bool grouped = p.acc_groups > 1;
+      const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++local) {
         const WorkItem it = decode_work(p, w);
         const int acc = (wide || grouped) ? 0 : (local & 1);
         const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
         // rows of the second half that lie beyond M need no MMAs; taps beyond the last need none
         int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
-        if (grouped) halves = min(p.acc_groups, p.nz_out - it.z * p.acc_groups);
+        if (grouped) {
+          const int taps_left = p.nz_out - it.z * p.acc_groups * p.acc_taps;
+          halves = min(p.acc_groups, (taps_left + p.acc_taps - 1) / p.acc_taps);
+        }
         if (!wide) {
           if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
           tc_fence_after();
@@ -334,12 +347,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tc_fence_after();
           const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
           const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
+          // accumulator by accumulator (measured faster than interleaving them k-step by k-step)
+          const uint32_t acc_first = kb > it.kb0 ? 1u : 0u;
           for (int h = 0; h < halves; ++h) {
-            if (wide && kb == it.kb0) {
-              if (!mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) {
-                ok = false;
-                break;
-              }
+            if (wide && kb == it.kb0) {   // half h of the previous tile must have been drained
+              ok = mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC);
+              if (!ok) break;
               tc_fence_after();
             }
             const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
@@ -349,7 +362,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                                      (p.a_desc_lo | ((sah + k * p.a_kstep) & 0x3fffu));
               const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
                                      (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
-              tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, (kb > it.kb0 || k > 0) ? 1u : 0u);
+              tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
             }
           }
           if (!ok) break;
@@ -371,7 +384,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
-    const bool grouped = p.acc_groups > 1;
+    const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
     const int n_acc = wide ? 2 : p.acc_groups;   // accumulators of one work item
     int local = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++local) {
@@ -383,13 +396,28 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const int n0 = it.tile_n * p.block_n;
       const bool partial = p.splits > 1;
       for (int h = 0; h < n_acc; ++h) {
-        // accumulator h holds rows of row-tile `rt` of output slice `zt`
+        // accumulator h holds rows of row-tile `rt` of output slice `zt`; with stacked taps
+        // (weight update, few rows per tap) every `pack_rows` lanes belong to the next slice
         const int rt = wide ? it.tile_m * 2 + h : it.tile_m;
-        const int zt = grouped ? it.z * p.acc_groups + h : it.z;
-        const int row = rt * kTileM + lane_group * 32 + lane;
-        const bool row_ok = row < p.M;
+        int zt = it.z, row = rt * kTileM + lane_group * 32 + lane, row0 = rt * kTileM + lane_group * 32;
+        int zt_warp = it.z;               // slice of this warp's first lane (bulk-store path)
+        bool row_ok = row < p.M;
+        if (grouped) {
+          const int first = (it.z * p.acc_groups + h) * p.acc_taps;
+          zt = zt_warp = first;
+          if (p.acc_taps > 1) {
+            const int r = lane_group * 32 + lane;
+            const int sub = r / p.pack_rows;
+            row = r - sub * p.pack_rows;
+            zt = first + sub;
+            row_ok = sub < p.acc_taps && row < p.M && zt < p.nz_out;
+            const int sub_w = (lane_group * 32) / p.pack_rows;
+            row0 = lane_group * 32 - sub_w * p.pack_rows;
+            zt_warp = sub_w < p.acc_taps ? first + sub_w : p.nz_out;
+          }
+        }
         // whole accumulator beyond M (or beyond the last tap): nothing accumulated, nothing to store
-        const bool half_live = rt * kTileM < p.M && zt < p.nz_out;
+        const bool half_live = rt * kTileM < p.M && (grouped ? (it.z * p.acc_groups + h) * p.acc_taps : zt) < p.nz_out;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
         // row base pointers
@@ -412,8 +440,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           // for the per-row writes below), then one bulk tensor store per box. The store clips
           // rows >= M and columns >= N itself.
           const int epi_warp = warp - 2;
-          const int row0 = rt * kTileM + lane_group * 32;
-          const int zc = partial ? it.split * p.nz_out + zt : zt;
+          const int zc = partial ? it.split * p.nz_out + zt_warp : zt_warp;
           const int subs = p.c_box_cols / 32;            // tcgen05.ld groups per box: 2 (fp16) or 1 (fp32)
           const int n_boxes = p.block_n / p.c_box_cols;
           const int cb0 = col_group == 0 ? 0 : (n_boxes + 1) / 2;
@@ -464,7 +491,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             fence_async_smem();
             __syncwarp();
             if (lane == 0) {
-              if (colb < p.N && row0 < p.M) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
+              if (colb < p.N && row0 < p.M && zt_warp < p.nz_out) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
               tma_store_commit();
             }
           }
@@ -529,48 +556,78 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 }
 
 // ------------------------------------------------------------------------------------------
-// split-K second stage: sum the partials in fixed order, then the fused epilogue.
-// One thread finishes 8 consecutive columns of one row.
+// split-K second stage: sum the partials in a fixed order, then the fused epilogue.
+// `lanes` (a power of two, at most 32) neighbouring threads share 8 consecutive columns of one
+// row: thread j adds partitions j, j + lanes, ... in that order, then the lanes are combined by a
+// butterfly. The order depends only on (splits, lanes), so results repeat bit for bit. Several
+// lanes matter when there are many partitions of a small output: one thread walking 70 slices
+// one after the other is a chain of 70 dependent memory latencies.
 // ------------------------------------------------------------------------------------------
-__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int nz, int M, int N, void* C,
-                                     const void* Cold, long long ldc, long long c_zstride, int out_f32,
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int lanes, int nz, int M, int N,
+                                     void* C, const void* Cold, long long ldc, long long c_zstride, int out_f32,
                                      int vec_ok, EpiArgs ea) {
   const int groups_per_row = (N + 7) / 8;
   const long long total = static_cast<long long>(nz) * M * groups_per_row;
   const long long slice = static_cast<long long>(nz) * M * N;
-  for (long long i = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x; i < total;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const int g = static_cast<int>(i % groups_per_row);
-    const long long zr = i / groups_per_row;
-    const int row = static_cast<int>(zr % M);
-    const int z = static_cast<int>(zr / M);
-    const int col = g * 8;
-    const int nvalid = min(8, N - col);
-    float v[8];
+  const long long t = blockIdx.x * static_cast<long long>(blockDim.x) + threadIdx.x;
+  const int sub = static_cast<int>(t % lanes);
+  const long long i = t / lanes;
+  const bool live = i < total;          // whole groups of `lanes` threads are live or not
+  const long long ic = live ? i : 0;
+  const int g = static_cast<int>(ic % groups_per_row);
+  const long long zr = ic / groups_per_row;
+  const int row = static_cast<int>(zr % M);
+  const int z = static_cast<int>(zr / M);
+  const int col = g * 8;
+  const int nvalid = min(8, N - col);
+  float v[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] = 0.0f;
-    const float* src = ws + zr * N + col;
-    const bool v4 = (N & 3) == 0 && nvalid == 8;
-    for (int s = 0; s < splits; ++s, src += slice) {
-      if (v4) {
+  for (int j = 0; j < 8; ++j) v[j] = 0.0f;
+  const float* src = ws + zr * N + col + sub * slice;
+  const long long step = slice * lanes;
+  const bool v4 = (N & 3) == 0 && nvalid == 8;
+  if (live) {
+    if (v4) {
+      int s = sub;
+      // four partitions in flight per thread
+      for (; s + 3 * lanes < splits; s += 4 * lanes, src += 4 * step) {
+        float4 a[4], b[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          a[u] = reinterpret_cast<const float4*>(src + u * step)[0];
+          b[u] = reinterpret_cast<const float4*>(src + u * step)[1];
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          v[0] += a[u].x; v[1] += a[u].y; v[2] += a[u].z; v[3] += a[u].w;
+          v[4] += b[u].x; v[5] += b[u].y; v[6] += b[u].z; v[7] += b[u].w;
+        }
+      }
+      for (; s < splits; s += lanes, src += step) {
         const float4 a = reinterpret_cast<const float4*>(src)[0];
         const float4 b = reinterpret_cast<const float4*>(src)[1];
         v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w;
         v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
-      } else {
-        for (int j = 0; j < nvalid; ++j) v[j] += src[j];
       }
+    } else {
+      for (int s = sub; s < splits; s += lanes, src += step)
+        for (int j = 0; j < nvalid; ++j) v[j] += src[j];
     }
-    const long long off = z * c_zstride + static_cast<long long>(row) * ldc;
-    const int esz = out_f32 ? 4 : 2;
-    uint8_t* crow = static_cast<uint8_t*>(C) + off * esz;
-    const uint8_t* oldrow = Cold ? static_cast<const uint8_t*>(Cold) + off * esz : nullptr;
-    const unsigned long long lin = (static_cast<unsigned long long>(z) * M + row) * static_cast<unsigned long long>(N) + col;
-    if (out_f32)
-      epi_store8<true>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
-    else
-      epi_store8<false>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
   }
+  for (int d = lanes >> 1; d > 0; d >>= 1) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], d);
+  }
+  if (!live || sub != 0) return;
+  const long long off = z * c_zstride + static_cast<long long>(row) * ldc;
+  const int esz = out_f32 ? 4 : 2;
+  uint8_t* crow = static_cast<uint8_t*>(C) + off * esz;
+  const uint8_t* oldrow = Cold ? static_cast<const uint8_t*>(Cold) + off * esz : nullptr;
+  const unsigned long long lin = (static_cast<unsigned long long>(z) * M + row) * static_cast<unsigned long long>(N) + col;
+  if (out_f32)
+    epi_store8<true>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
+  else
+    epi_store8<false>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
 }
 
 }  // namespace ngb

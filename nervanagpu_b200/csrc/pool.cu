@@ -6,11 +6,13 @@
 // Numerics follow the reference kernel: taps are scanned in j,t,r,s order with a strict '>'
 // compare so the first maximum wins (hpool_max.sass:264-281), taps outside the tensor are
 // skipped, and the backward pass adds E[k,m,p,q,n] to dI at the argmax of window (k,m,p,q).
-// Here the backward pass is a gather: each dI element visits the windows that contain it in
-// increasing (k,m,p,q) order, recomputes their argmax and sums the matching errors in fp32,
-// so overlapping windows need neither atomics nor a zero-fill pass and the result is
-// deterministic. The innermost dimension N is contiguous: each thread owns 8 images (one
-// 16-byte lane) when N % 8 == 0, else 1.
+// Here the backward pass is a gather in two stages: the first records the argmax of every window
+// (a scratch array in the library's workspace), the second lets each dI element visit the
+// windows that contain it in increasing (k,m,p,q) order and sum, in fp32, the errors of those
+// whose argmax it is. Overlapping windows so need neither atomics nor a zero-fill pass and the
+// result is deterministic. Windows that do not overlap take one pass. The common 2-D shapes
+// (3x3/2, 2x2/2, 3x3/3 without padding) have compile-time specialisations. The innermost
+// dimension N is contiguous: each thread owns 8 images (one 16-byte lane) when N % 8 == 0, else 1.
 #include <algorithm>
 #include <cfloat>
 #include <cuda_fp16.h>
@@ -183,46 +185,6 @@ __global__ void pool_gather_kernel(PoolGeo g, const int* __restrict__ arg, const
   }
 }
 
-template <typename T, int V>
-__global__ void pool_bprop_kernel(PoolGeo g, const T* __restrict__ I, const T* __restrict__ E, T* __restrict__ dI) {
-  const int nvec = g.N / V;
-  const long long total = 1ll * g.C * g.D * g.H * g.W * nvec;
-  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
-    long long r = i;
-    const int nv = r % nvec; r /= nvec;
-    const int flat = static_cast<int>(r);
-    const int x = r % g.W; r /= g.W;
-    const int y = r % g.H; r /= g.H;
-    const int z = r % g.D; r /= g.D;
-    const int c = static_cast<int>(r);
-    int k0, k1, m0, m1, p0, p1, q0, q1;
-    window_range(c, g.pad_j, g.J, g.str_j, g.K, k0, k1);
-    window_range(z, g.pad_d, g.T, g.str_d, g.M, m0, m1);
-    window_range(y, g.pad_h, g.R, g.str_h, g.P, p0, p1);
-    window_range(x, g.pad_w, g.S, g.str_w, g.Q, q0, q1);
-    float acc[V];
-#pragma unroll
-    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
-    for (int k = k0; k <= k1; ++k)
-      for (int m = m0; m <= m1; ++m)
-        for (int p = p0; p <= p1; ++p)
-          for (int q = q0; q <= q1; ++q) {
-            float best[V];
-            int arg[V];
-            window_max<T, V>(g, I, k, m, p, q, nv, best, arg);
-            const long long o = ((((1ll * k * g.M + m) * g.P + p) * g.Q + q) * g.N) + nv * V;
-            const Vec<T, V> e = *reinterpret_cast<const Vec<T, V>*>(E + o);
-#pragma unroll
-            for (int j = 0; j < V; ++j)
-              if (arg[j] == flat) acc[j] += e.get(j);
-          }
-    Vec<T, V> out;
-#pragma unroll
-    for (int j = 0; j < V; ++j) out.set(j, acc[j]);
-    *reinterpret_cast<Vec<T, V>*>(dI + i * V) = out;
-  }
-}
-
 // ------------------------------------------------------------------------------------------
 // Specialised 2-D windows (J = T = 1, no padding, fp16, N % 8 == 0): compile-time R,S and strides,
 // grid (x: q|block column and image lane, y: p|block row, z: channel) so no index division.
@@ -274,8 +236,8 @@ __device__ __forceinline__ void window2d(const __half* __restrict__ plane, int H
 
 template <int R, int S, int SH, int SW>
 __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O,
-                                                          int* __restrict__ arg_out, int H, int W, int N, int P,
-                                                          int Q) {
+                                                          uint8_t* __restrict__ arg_out, int H, int W, int N,
+                                                          int P, int Q) {
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int q = t / nvec;
@@ -288,18 +250,19 @@ __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restr
   const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
   if (O) store8(O + o, best);
   if (arg_out) {
-    int flat[8];
-#pragma unroll
-    for (int i = 0; i < 8; ++i) flat[i] = (c * H + p * SH + arg[i] / S) * W + q * SW + arg[i] % S;
-    reinterpret_cast<int4*>(arg_out + o)[0] = make_int4(flat[0], flat[1], flat[2], flat[3]);
-    reinterpret_cast<int4*>(arg_out + o)[1] = make_int4(flat[4], flat[5], flat[6], flat[7]);
+    // one byte per output: the tap (r*S + s) of the first maximum
+    uint2 packed;
+    packed.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
+    packed.y = arg[4] | (arg[5] << 8) | (arg[6] << 16) | (arg[7] << 24);
+    *reinterpret_cast<uint2*>(arg_out + o) = packed;
   }
 }
 
 // Backward, second stage: the thread that owns the SH x SW input block (a, b) reads the recorded
 // argmax and the error of each overlapping window once and credits the block input it names.
 template <int R, int S, int SH, int SW>
-__global__ void __launch_bounds__(256) pool2d_gather_kernel(const int* __restrict__ arg, const __half* __restrict__ E,
+__global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __restrict__ arg,
+                                                           const __half* __restrict__ E,
                                                            __half* __restrict__ dI, int H, int W, int N, int P, int Q,
                                                            int BW) {
   constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
@@ -325,19 +288,24 @@ __global__ void __launch_bounds__(256) pool2d_gather_kernel(const int* __restric
       const int q = b - (WQ - 1) + wq;
       if (q < 0 || q >= Q) continue;
       const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
-      const int4 i0 = reinterpret_cast<const int4*>(arg + o)[0], i1 = reinterpret_cast<const int4*>(arg + o)[1];
-      const int idx[8] = {i0.x, i0.y, i0.z, i0.w, i1.x, i1.y, i1.z, i1.w};
+      const uint2 pk = *reinterpret_cast<const uint2*>(arg + o);
+      const int idx[8] = {static_cast<int>(pk.x & 255u), static_cast<int>((pk.x >> 8) & 255u),
+                          static_cast<int>((pk.x >> 16) & 255u), static_cast<int>(pk.x >> 24),
+                          static_cast<int>(pk.y & 255u), static_cast<int>((pk.y >> 8) & 255u),
+                          static_cast<int>((pk.y >> 16) & 255u), static_cast<int>(pk.y >> 24)};
       const Lanes8 e = load8(E + o);
 #pragma unroll
       for (int dy = 0; dy < SH; ++dy) {
-        if ((WP - 1 - wp) * SH + dy >= R) continue;
+        const int r = (WP - 1 - wp) * SH + dy;     // tap row of block input dy inside window p
+        if (r >= R) continue;
 #pragma unroll
         for (int dx = 0; dx < SW; ++dx) {
-          if ((WQ - 1 - wq) * SW + dx >= S) continue;
-          const int flat = (c * H + a * SH + dy) * W + b * SW + dx;
+          const int s = (WQ - 1 - wq) * SW + dx;
+          if (s >= S) continue;
+          const int tap = r * S + s;
 #pragma unroll
           for (int i = 0; i < 8; ++i)
-            if (idx[i] == flat) acc[dy][dx][i] += e.v[i];
+            if (idx[i] == tap) acc[dy][dx][i] += e.v[i];
         }
       }
     }
@@ -438,12 +406,13 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
         g.Q, BW);
     NG_CHECK_LAUNCH();
   } else {
-    pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(static_cast<const __half*>(I), nullptr, arg_ws, g.H,
+    uint8_t* arg8 = reinterpret_cast<uint8_t*>(arg_ws);
+    pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(static_cast<const __half*>(I), nullptr, arg8, g.H,
                                                                 g.W, g.N, g.P, g.Q);
     NG_CHECK_LAUNCH();
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
     dim3 grid((BW * nvec + 255) / 256, BH, g.C);
-    pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(arg_ws, static_cast<const __half*>(EO),
+    pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(arg8, static_cast<const __half*>(EO),
                                                                  static_cast<__half*>(out), g.H, g.W, g.N, g.P, g.Q, BW);
     NG_CHECK_LAUNCH();
   }

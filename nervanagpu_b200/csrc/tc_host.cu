@@ -28,7 +28,9 @@ uint32_t desc_lo(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3fffu) << 16
 static uint32_t a_overread(const TcParams& p) {
   if (p.a_mn_major) return 0u;
   const uint32_t full = kTileM * p.m_halves * 128u;
-  const uint32_t last_end = (p.a_boxes > 1 ? (p.a_boxes - 1) * p.a_box_bytes : 0u) + full;
+  // the last accumulator's descriptor starts at its first box and spans a full tile
+  const uint32_t acc_stride = static_cast<uint32_t>(std::max(1, p.acc_taps)) * p.a_box_bytes;
+  const uint32_t last_end = (p.acc_groups > 1 ? (p.acc_groups - 1) * acc_stride : 0u) + full;
   return last_end > p.a_bytes ? last_end - p.a_bytes : 0u;
 }
 
@@ -57,15 +59,17 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
     p.a_half_step = (2u * mn_box) >> 4;
   } else {
     if (p.acc_groups < 1) p.acc_groups = 1;
-    p.a_boxes = p.acc_groups;   // grouped update: one A box per accumulator
+    if (p.acc_taps < 1) p.acc_taps = 1;
+    p.a_boxes = p.acc_groups * p.acc_taps;   // grouped update: one A box per tap of every accumulator
     // a box may deliver fewer rows than the tile has (few-channel update): the rest of the
     // slot keeps stale data whose products land in rows that are never stored
     p.a_box_bytes = (lay.a_box_rows ? lay.a_box_rows : tile_rows) * 128u;
     p.a_desc_lo = desc_lo(16);
     p.a_kstep = 32u >> 4;
-    p.a_half_step = (p.acc_groups > 1 ? p.a_box_bytes : kTileM * 128u) >> 4;
+    p.a_half_step = ((p.acc_groups > 1 || p.acc_taps > 1) ? p.acc_taps * p.a_box_bytes : kTileM * 128u) >> 4;
   }
   if (p.acc_groups < 1) p.acc_groups = 1;
+  if (p.acc_taps < 1) p.acc_taps = 1;
   p.a_desc_hi = desc_hi(1024);
   // A slot: the rows the box delivers. When that is fewer than the MMA's 128 rows the instruction
   // also reads what follows (the B slot, the next stage, the staging area: all inside this CTA's
@@ -99,6 +103,8 @@ static bool make_store_map(CUtensorMap* map, TcParams& p) {
   static const char* off = getenv("NG_TMA_STORE");
   if (off && off[0] == '0') return false;
   if ((p.N & 7) != 0) return false;
+  // stacked taps: a warp's 32 rows must belong to one tap
+  if (p.acc_taps > 1 && (p.pack_rows & 31) != 0) return false;
   const bool partial = p.splits > 1;
   const int esz = (partial || p.out_f32) ? 4 : 2;
   uint64_t dims[5] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), 1, 1, 1};
@@ -169,12 +175,23 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
   return static_cast<int>(best);
 }
 
+// Threads that share one 8-column group of the split-K reduction: more when the output is small
+// and the partitions many, so that the device is filled and no thread walks a long chain.
+static int splitk_reduce_lanes(long long groups, int splits, int sm_count) {
+  int lanes = 1;
+  while (lanes < 32 && lanes * 4 <= splits && groups * lanes < sm_count * 2048ll) lanes *= 2;
+  return lanes;
+}
+
 int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream) {
   if (p.num_kb < 1) return fail(NG_ERR_INVALID_ARG, "empty reduction");
   if (p.splits < 1) p.splits = 1;
   if (p.acc_groups < 1) p.acc_groups = 1;
+  if (p.acc_taps < 1) p.acc_taps = 1;
   if (p.nz_out < 1) p.nz_out = p.nz;
-  if (p.acc_groups > 1 && (p.m_halves != 1 || p.acc_groups * p.block_n > 512)) {
+  if ((p.acc_groups > 1 || p.acc_taps > 1) &&
+      (p.m_halves != 1 || p.tiles_m != 1 || p.acc_groups * p.block_n > 512 ||
+       (p.acc_taps > 1 && (p.pack_rows < 8 || p.acc_taps * p.pack_rows > kTileM)))) {
     return fail(NG_ERR_INVALID_ARG, "internal: grouped accumulators do not fit tensor memory");
   }
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
@@ -184,7 +201,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     // NG_L2_PREFETCH=<bits> / NG_L2_AHEAD=<k-blocks> override the policy (tuning aid)
     static const char* pf = getenv("NG_L2_PREFETCH");
     static const char* ahead = getenv("NG_L2_AHEAD");
-    p.l2_prefetch = pf ? atoi(pf) : (p.mode == TC_UPDATE ? 3 : 0);
+    p.l2_prefetch = pf ? atoi(pf) : 0;   // measured: the extra requests cost the copy engine more than they save
     p.l2_ahead = ahead ? std::max(1, atoi(ahead)) : 8;
   }
   // TMA counts the whole box (including zero-filled parts) against the barrier
@@ -222,10 +239,12 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
     const long long groups = static_cast<long long>(p.nz_out) * p.M * ((p.N + 7) / 8);
-    const int threads = 256;
-    const int blocks = static_cast<int>(std::min<long long>((groups + threads - 1) / threads, c->sm_count * 8ll));
-    splitk_reduce_kernel<<<blocks, threads, 0, stream>>>(p.ws, p.splits, p.nz_out, p.M, p.N, p.C, p.Cold, p.ldc,
-                                                         p.c_zstride, p.out_f32, p.vec_ok, ea);
+    const int lanes = splitk_reduce_lanes(groups, p.splits, c->sm_count);
+    const long long blocks = (groups * lanes + 255) / 256;
+    if (blocks > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "output too large for the split-K reduction");
+    splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p.ws, p.splits, lanes, p.nz_out, p.M, p.N, p.C,
+                                                                        p.Cold, p.ldc, p.c_zstride, p.out_f32,
+                                                                        p.vec_ok, ea);
     NG_CHECK_LAUNCH();
   }
   return NG_OK;
@@ -376,8 +395,10 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = rng_offset;
   if (p.splits > 1) {
     const long long groups = static_cast<long long>(m) * ((n + 7) / 8);
-    const int blocks = static_cast<int>(std::min<long long>((groups + 255) / 256, slots->sm_count * 8ll));
-    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.ws, p.splits, 1, m, n, C, p.Cold, ldc, 0, 0, p.vec_ok, ea);
+    const int lanes = ngb::splitk_reduce_lanes(groups, p.splits, slots->sm_count);
+    const int blocks = static_cast<int>((groups * lanes + 255) / 256);
+    splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.ws, p.splits, lanes, 1, m, n, C, p.Cold, ldc, 0, 0, p.vec_ok,
+                                                     ea);
     NG_CHECK_LAUNCH();
   }
   return NG_OK;

@@ -76,6 +76,9 @@ CASES = {
     "c32_1x1": (64, 32, 48, 1, 5, 5, 1, 1, 1, 0, 0, 0, 1, 1, 1),
     "c8_n16_flattened_q8": (16, 8, 16, 1, 8, 8, 1, 3, 3, 0, 1, 1, 1, 1, 1),
     "stride_h_only": (64, 16, 16, 1, 9, 8, 1, 3, 3, 0, 1, 1, 1, 2, 1),
+    # update: two 48-row taps stacked per accumulator, 192-column tiles
+    "c48_k384_stacked_taps": (64, 48, 384, 1, 6, 6, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "c64_k192_5x5_n128": (128, 64, 192, 1, 7, 7, 1, 5, 5, 0, 2, 2, 1, 1, 1),
 }
 
 
