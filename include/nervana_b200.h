@@ -67,6 +67,18 @@ int ng_device_status(int* code);
  * generated element-wise ones; memcpy / memset / NCCL calls are not counted). */
 int ng_launch_count(unsigned long long* count);
 
+/* Record-and-replay of a sequence of calls (a CUDA graph). The reference drives every kernel
+ * with its own pycuda launch (nervanagpu/nervanagpu.py:642-734, 959-1105) and has nothing like
+ * this; it exists because a training step of ~40 short kernels is otherwise bound by the host.
+ * Between begin and end, the library's calls on `stream` (not the default stream) are recorded,
+ * not run; the sequence must have run once before, so that scratch memory has its final size and
+ * generated kernels are compiled. A replay repeats the recorded pointers, scalars and random
+ * offsets; ng_launch_count counts the kernels of every replay. */
+int ng_graph_capture_begin(void* stream);
+int ng_graph_capture_end(void* stream, void** graph);
+int ng_graph_launch(void* graph, void* stream);
+int ng_graph_destroy(void* graph);
+
 /* ---- GEMM --------------------------------------------------------------------------------
  * C[m x n] = relu?(alpha * op(A) * op(B)) + beta * C, row-major, fp16 storage, fp32 accumulate.
  * a_t: A is stored k x m; b_t: B is stored n x k; leading dimensions in elements.

@@ -66,6 +66,10 @@ SIGNATURES = {
     "ng_sync": (c_int, []),
     "ng_device_status": (c_int, [ctypes.POINTER(c_int)]),
     "ng_launch_count": (c_int, [ctypes.POINTER(c_ulonglong)]),
+    "ng_graph_capture_begin": (c_int, [c_void_p]),
+    "ng_graph_capture_end": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
+    "ng_graph_launch": (c_int, [c_void_p, c_void_p]),
+    "ng_graph_destroy": (c_int, [c_void_p]),
     "ng_hgemm": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                          c_float, c_float, c_int, c_int, c_ulonglong, c_uint, c_void_p]),
     "ng_hgemm_simt": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -173,6 +173,25 @@ class ConvStack(object):
         self._prefetch_pending = False
         self._consumed_recorded = False
 
+    def record_steps(self):
+        """Record one step per input buffer (the live one and the prefetch spare); step_prefetched
+        then replays the recording that reads the buffer it swapped in. step() must have run before.
+        Single GPU only: the all-reduce of a multi-GPU step stays a live call."""
+        if self.comm is not None:
+            raise ValueError("recorded steps are limited to single-GPU stacks")
+        if not hasattr(self, "_copy_stream"):
+            self._init_prefetch()
+        probe, self.probe = self.probe, None
+        live = self.input
+        self._recorded = {}
+        try:
+            for buf in (live, self._next_input):
+                self.input = buf
+                self._recorded[buf.ptr] = self.ng.capture(self.step)
+        finally:
+            self.input = live
+            self.probe = probe
+
     def prefetch_input(self, pinned_host_ptr):
         """Start the host-to-device copy of the next minibatch (pinned host memory) on a separate
         stream into the spare input buffer. It overlaps whatever the compute stream is doing."""
@@ -191,7 +210,7 @@ class ConvStack(object):
         """Swap in the prefetched minibatch (waiting for its copy on the device, not on the host)
         and run one step."""
         lib = self.ng.lib
-        if self._prefetch_pending:
+        if getattr(self, "_prefetch_pending", False):
             _lib.check(lib.ng_stream_wait_event(self.ng.stream, self._copied))
             self.input, self._next_input = self._next_input, self.input
             self._prefetch_pending = False
@@ -199,7 +218,11 @@ class ConvStack(object):
             # buffer) is done when this event fires; the next copy waits for it, not for this step
             _lib.check(lib.ng_event_record(self._consumed, self.ng.stream))
             self._consumed_recorded = True
-        self.step()
+        recorded = getattr(self, "_recorded", None)
+        if recorded:
+            recorded[self.input.ptr].launch()
+        else:
+            self.step()
 
 
 def _relu_mask(grad, act):

@@ -18,6 +18,8 @@ struct DeviceCtx {
   float* ws = nullptr;       // split-K / conv scratch, grown on demand
   size_t ws_bytes = 0;
   bool smem_attr_set = false;
+  bool capturing = false;    // a stream capture is open: nothing may allocate or synchronise
+  unsigned long long capture_launches0 = 0;
 };
 
 // Error reporting: returns `code` after storing a printf-style message for ng_last_error().

@@ -73,6 +73,10 @@ DeviceCtx* current_ctx() {
 
 int ensure_workspace(DeviceCtx* c, size_t bytes) {
   if (bytes <= c->ws_bytes) return NG_OK;
+  if (c->capturing) {
+    return fail(NG_ERR_UNSUPPORTED,
+                "the workspace would have to grow during a capture: run the sequence once before recording it");
+  }
   // growing: earlier launches may still read the old buffer
   NG_CUDA(cudaDeviceSynchronize());
   if (c->ws) NG_CUDA(cudaFree(c->ws));
@@ -313,6 +317,68 @@ int ng_launch_count(unsigned long long* count) {
 int ng_sync(void) {
   NG_CUDA(cudaDeviceSynchronize());
   return ng_device_status(nullptr);
+}
+
+// ---- replaying a recorded sequence of calls (CUDA graphs) ---------------------------------
+// Between ng_graph_capture_begin and ng_graph_capture_end every call of this library on `stream`
+// is recorded instead of run. The recording keeps the pointers, shapes, scalars and random
+// offsets of the calls; replaying it costs one launch on the host.
+struct NgGraph {
+  cudaGraphExec_t exec = nullptr;
+  unsigned long long kernels = 0;   // kernel launches one replay stands for
+};
+
+int ng_graph_capture_begin(void* stream) {
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (!stream) return fail(NG_ERR_INVALID_ARG, "capture needs a stream of its own, not the default stream");
+  if (c->capturing) return fail(NG_ERR_INVALID_ARG, "a capture is already open");
+  NG_CUDA(cudaStreamBeginCapture(static_cast<cudaStream_t>(stream), cudaStreamCaptureModeThreadLocal));
+  c->capturing = true;
+  c->capture_launches0 = g_launches.load(std::memory_order_relaxed);
+  return NG_OK;
+}
+
+int ng_graph_capture_end(void* stream, void** graph_out) {
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (!c->capturing) return fail(NG_ERR_INVALID_ARG, "no capture is open");
+  c->capturing = false;
+  cudaGraph_t graph = nullptr;
+  NG_CUDA(cudaStreamEndCapture(static_cast<cudaStream_t>(stream), &graph));
+  if (!graph_out) {
+    cudaGraphDestroy(graph);
+    return fail(NG_ERR_INVALID_ARG, "graph_out is null");
+  }
+  NgGraph* g = new NgGraph;
+  cudaError_t e = cudaGraphInstantiate(&g->exec, graph, 0);
+  cudaGraphDestroy(graph);
+  if (e != cudaSuccess) {
+    delete g;
+    return cuda_fail(e, "cudaGraphInstantiate");
+  }
+  const unsigned long long now = g_launches.load(std::memory_order_relaxed);
+  g->kernels = now - c->capture_launches0;
+  // the recorded launches did not run
+  g_launches.fetch_sub(g->kernels, std::memory_order_relaxed);
+  *graph_out = g;
+  return NG_OK;
+}
+
+int ng_graph_launch(void* graph, void* stream) {
+  NgGraph* g = static_cast<NgGraph*>(graph);
+  if (!g || !g->exec) return fail(NG_ERR_INVALID_ARG, "graph is null");
+  NG_CUDA(cudaGraphLaunch(g->exec, static_cast<cudaStream_t>(stream)));
+  g_launches.fetch_add(g->kernels, std::memory_order_relaxed);
+  return NG_OK;
+}
+
+int ng_graph_destroy(void* graph) {
+  NgGraph* g = static_cast<NgGraph*>(graph);
+  if (!g) return NG_OK;
+  if (g->exec) NG_CUDA(cudaGraphExecDestroy(g->exec));
+  delete g;
+  return NG_OK;
 }
 
 }  // extern "C"

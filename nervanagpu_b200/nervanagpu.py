@@ -149,6 +149,8 @@ class GPUTensor(object):
         ary = np.empty(self.shape, self.dtype)
         if self.size:
             lib = _lib.init()
+            if stream is None:
+                stream = self.backend.stream     # ordered after the work queued on the backend's stream
             _lib.check(lib.ng_memcpy_d2h_async(ary.ctypes.data, self.ptr, self.nbytes, stream))
             _lib.check(lib.ng_stream_sync(stream))
         return ary
@@ -379,6 +381,29 @@ class RandState(object):
         return off
 
 
+class RecordedSequence(object):
+    """Device work recorded by NervanaGPU.capture(); launch() queues all of it with one call.
+    A replay repeats the recorded pointers, scalars and random offsets exactly."""
+
+    def __init__(self, backend, handle):
+        self.backend = backend
+        self.handle = handle
+
+    def launch(self):
+        _lib.check(self.backend.lib.ng_graph_launch(self.handle, self.backend.stream))
+
+    def release(self):
+        if self.handle is not None:
+            _lib.check(self.backend.lib.ng_graph_destroy(self.handle))
+            self.handle = None
+
+    def __del__(self):
+        try:
+            self.release()
+        except Exception:
+            pass
+
+
 class NervanaGPU(object):
 
     def __init__(self, stochastic_round=False, bench=False, cubin_path=None, scratch_size=9 * 1024 * 1024,
@@ -434,6 +459,28 @@ class NervanaGPU(object):
 
     def synchronize(self):
         _lib.check(self.lib.ng_sync())
+
+    # ---- streams and recorded sequences --------------------------------------------------
+    def new_stream(self):
+        """A new stream handle; assign it to `self.stream` to queue all later work on it."""
+        s = ctypes.c_void_p()
+        _lib.check(self.lib.ng_stream_create(ctypes.byref(s)))
+        return s
+
+    def capture(self, fn):
+        """Record the device work `fn()` queues on `self.stream` (which must be a stream from
+        new_stream, not the default one) and return a RecordedSequence whose launch() replays it
+        with one host call. `fn` must have run once before with the same tensors, so that scratch
+        memory has its final size and generated kernels exist. No pycuda-era counterpart: the
+        reference launches every kernel from Python (nervanagpu/nervanagpu.py:705-729)."""
+        _lib.check(self.lib.ng_graph_capture_begin(self.stream))
+        graph = ctypes.c_void_p()
+        try:
+            fn()
+        finally:
+            rc = self.lib.ng_graph_capture_end(self.stream, ctypes.byref(graph))
+        _lib.check(rc)
+        return RecordedSequence(self, graph)
 
     # ---- timing --------------------------------------------------------------------------
     def _get_events(self):
