@@ -30,6 +30,9 @@ sys.path.insert(0, ROOT)
 
 METRIC = "alexnet_conv_stack_fprop_bprop_update_tflops"
 UNIT = "TFLOP/s"
+# dram__bytes_read.sum + dram__bytes_write.sum per igemm_tc_kernel launch, from the ncu capture summarised
+# in profiles/igemm_tc_kernel_alexnet_step_traffic.md (not measurable from inside this script)
+TRAFFIC_BYTES_PER_CONV_LAUNCH = {("alexnet", 128): 28.04e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -365,7 +368,9 @@ def main():
         "gpu_launches": int(gpu_launches),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                     "frac": achieved / peak if peak else None, "traffic": None,
+                     "frac": achieved / peak if peak else None,
+                     "traffic": TRAFFIC_BYTES_PER_CONV_LAUNCH.get((args.net, stack.N)),
+                     "traffic_unit": "bytes of DRAM read+write per conv launch (ncu, mean of the 14 launches of a step)",
                      "peak_source": "%s bf16_tflops_sustained" % peak_src,
                      "kernel": "igemm_tc_kernel (+ its split-K reduction / im2col satellites)",
                      "launches_timed": n_conv, "avg_launch_ms": conv_ms / n_conv if n_conv else None},

@@ -173,6 +173,12 @@ int ng_pool_fprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, void
 /* gradI[argmax of each window] += E, every other element 0 (no zero-fill pass needed). Replaces
  * the mode-1 launch and the B.fill(0) before it (nervanagpu/nervanagpu.py:780-787,811). */
 int ng_pool_bprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, const void* E, void* gradI, void* stream);
+/* The same followed by the ReLU mask of the layer below, gradI *= (I > 0), in one pass: a window
+ * whose maximum is not positive passes no error on. Equal, bit for bit, to ng_pool_bprop and then
+ * the element-wise mask the reference's layers apply as a separate kernel (Layer.bprop_relu,
+ * nervanagpu/layers.py:87-96), because only a window's maximum receives error at all. */
+int ng_pool_bprop_relu(const ng_pool_desc* desc, int dtype_bytes, const void* I, const void* E, void* gradI,
+                       void* stream);
 
 /* ---- generated element-wise kernels -----------------------------------------------------------
  * Replace pycuda.compiler.SourceModule / Function.prepare / prepared_async_call for the CUDA-C

@@ -91,6 +91,7 @@ SIGNATURES = {
                                     ctypes.POINTER(c_int), ctypes.POINTER(c_int)]),
     "ng_pool_fprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ng_pool_bprop_relu": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ng_ew_compile": (c_int, [c_char_p, c_char_p, c_int, ctypes.POINTER(c_void_p)]),
     "ng_ew_compile_only": (c_int, [c_char_p, c_int]),
     "ng_ew_compile_log": (c_char_p, []),

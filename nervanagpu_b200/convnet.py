@@ -100,6 +100,7 @@ class ConvStack(object):
         top = (rng.uniform(-1.0, 1.0, self.layers[-1].dimO) * 0.125).astype(np.float16)
         self.top_delta.set(top)
         self.probe = None    # optional callable(name, layer, launch) used to time single launches
+        self.fuse_relu_mask = True   # False: every ReLU mask is its own element-wise kernel, as in the reference
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)
@@ -128,18 +129,26 @@ class ConvStack(object):
     def bprop(self):
         ng = self.ng
         grad = self.top_delta
+        masked = False     # grad already carries the ReLU mask of the conv layer it belongs to
         for i in range(len(self.layers) - 1, -1, -1):
             l = self.layers[i]
             x = self.input if i == 0 else self.acts[i - 1]
             dx = self.deltas[i]
             if isinstance(l, ConvLayer):
                 y = self.acts[i]
-                self._run("bprop_relu", l, lambda grad=grad, y=y: _relu_mask(grad, y))
+                if not masked:
+                    self._run("bprop_relu", l, lambda grad=grad, y=y: _relu_mask(grad, y))
+                masked = False
                 if dx is not None:
                     self._run("bprop_conv", l, lambda l=l, grad=grad, dx=dx: ng.bprop_conv(l, l.weights, grad, dx))
                 self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
             else:
-                self._run("bprop_pool", l, lambda l=l, x=x, grad=grad, dx=dx: ng.bprop_pool(l, x, grad, dx))
+                # the pool reads the (ReLU) output of the conv below it anyway: its backward pass
+                # applies that layer's mask as it writes the deltas
+                fuse = self.fuse_relu_mask and i > 0 and isinstance(self.layers[i - 1], ConvLayer)
+                self._run("bprop_pool", l, lambda l=l, x=x, grad=grad, dx=dx, fuse=fuse:
+                          ng.bprop_pool(l, x, grad, dx, relu_mask=fuse))
+                masked = fuse
             grad = dx
         if self.comm is not None:
             self._run("allreduce_dW", None, self.allreduce_grads)

@@ -119,7 +119,8 @@ __device__ __forceinline__ void window_range(int x, int pad, int f, int str, int
 // O and/or arg_out may be null: the forward pass stores the maxima, the first stage of the
 // backward pass stores the flat (c,z,y,x) index of each window's first maximum.
 template <typename T, int V>
-__global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restrict__ O, int* __restrict__ arg_out) {
+__global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restrict__ O, int* __restrict__ arg_out,
+                                  int mask_pos) {
   const int nvec = g.N / V;
   const long long total = 1ll * g.K * g.M * g.P * g.Q * nvec;
   for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
@@ -140,7 +141,7 @@ __global__ void pool_fprop_kernel(PoolGeo g, const T* __restrict__ I, T* __restr
     }
     if (arg_out) {
 #pragma unroll
-      for (int j = 0; j < V; ++j) arg_out[i * V + j] = arg[j];
+      for (int j = 0; j < V; ++j) arg_out[i * V + j] = (mask_pos && !(best[j] > 0.0f)) ? -1 : arg[j];
     }
   }
 }
@@ -237,7 +238,7 @@ __device__ __forceinline__ void window2d(const __half* __restrict__ plane, int H
 template <int R, int S, int SH, int SW>
 __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O,
                                                           uint8_t* __restrict__ arg_out, int H, int W, int N,
-                                                          int P, int Q) {
+                                                          int P, int Q, int mask_pos) {
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
   const int q = t / nvec;
@@ -251,6 +252,11 @@ __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restr
   if (O) store8(O + o, best);
   if (arg_out) {
     // one byte per output: the tap (r*S + s) of the first maximum
+    if (mask_pos) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (!(best[i] > 0.0f)) arg[i] = 255;   // names no tap: the window's error is dropped
+    }
     uint2 packed;
     packed.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
     packed.y = arg[4] | (arg[5] << 8) | (arg[6] << 16) | (arg[7] << 24);
@@ -329,7 +335,7 @@ __global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __res
 template <int R, int S, int SH, int SW>
 __global__ void __launch_bounds__(256) pool2d_bprop_kernel(const __half* __restrict__ I, const __half* __restrict__ E,
                                                           __half* __restrict__ dI, int H, int W, int N, int P, int Q,
-                                                          int BW) {
+                                                          int BW, int mask_pos) {
   constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -356,6 +362,11 @@ __global__ void __launch_bounds__(256) pool2d_bprop_kernel(const __half* __restr
       float best[8];
       int arg[8];
       window2d<R, S, SH, SW>(plane, H, W, N, p, q, n0, best, arg);
+      if (mask_pos) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (!(best[i] > 0.0f)) arg[i] = 255;
+      }
       const Lanes8 e = load8(E + ((static_cast<long long>(c) * P + p) * Q + q) * N + n0);
 #pragma unroll
       for (int dy = 0; dy < SH; ++dy) {
@@ -395,7 +406,7 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
   dim3 fgrid((g.Q * nvec + 255) / 256, g.P, g.C);
   if (mode == 0) {
     pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(
-        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), nullptr, g.H, g.W, g.N, g.P, g.Q);
+        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), nullptr, g.H, g.W, g.N, g.P, g.Q, 0);
     NG_CHECK_LAUNCH();
   } else if (R <= SH && S <= SW) {
     // windows do not overlap: one pass, each block of inputs sees at most one window
@@ -403,12 +414,12 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
     dim3 grid((BW * nvec + 255) / 256, BH, g.C);
     pool2d_bprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
         static_cast<const __half*>(I), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W, g.N, g.P,
-        g.Q, BW);
+        g.Q, BW, mode == 2);
     NG_CHECK_LAUNCH();
   } else {
     uint8_t* arg8 = reinterpret_cast<uint8_t*>(arg_ws);
     pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(static_cast<const __half*>(I), nullptr, arg8, g.H,
-                                                                g.W, g.N, g.P, g.Q);
+                                                                g.W, g.N, g.P, g.Q, mode == 2);
     NG_CHECK_LAUNCH();
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
     dim3 grid((BW * nvec + 255) / 256, BH, g.C);
@@ -448,7 +459,7 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
   // backward = record each window's argmax (scratch: one int per output element, in the
   // library workspace), then gather
   int* arg_ws = nullptr;
-  if (mode == 1) {
+  if (mode != 0) {
     int rc = ensure_workspace(c, static_cast<size_t>(out_elems) * sizeof(int));
     if (rc != NG_OK) return rc;
     arg_ws = reinterpret_cast<int*>(c->ws);
@@ -460,19 +471,20 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
   if (mode == 0) {
     T* O = static_cast<T*>(const_cast<void*>(EO));
     if (vec)
-      pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr);
+      pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr, 0);
     else
-      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr);
+      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), O, nullptr, 0);
     NG_CHECK_LAUNCH();
   } else {
     if (vec) {
       pool_fprop_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, static_cast<const T*>(I), nullptr,
-                                                                               arg_ws);
+                                                                               arg_ws, mode == 2);
       NG_CHECK_LAUNCH();
       pool_gather_kernel<T, VW><<<grid_for(in_elems / VW, c), 256, 0, stream>>>(g, arg_ws, static_cast<const T*>(EO),
                                                                                 static_cast<T*>(out));
     } else {
-      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), nullptr, arg_ws);
+      pool_fprop_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, static_cast<const T*>(I), nullptr, arg_ws,
+                                                                          mode == 2);
       NG_CHECK_LAUNCH();
       pool_gather_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(g, arg_ws, static_cast<const T*>(EO),
                                                                           static_cast<T*>(out));
@@ -523,6 +535,20 @@ int ng_pool_bprop(const ng_pool_desc* d, int dtype_bytes, const void* I, const v
   if (!c) return NG_ERR_CUDA;
   if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
   if (dtype_bytes == 4) return run_pool<float, 4>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
+  return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+int ng_pool_bprop_relu(const ng_pool_desc* d, int dtype_bytes, const void* I, const void* E, void* gradI,
+                       void* stream) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !E || !gradI) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  if (1ll * g.C * g.D * g.H * g.W > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many pixels");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, E, gradI, 2, c, static_cast<cudaStream_t>(stream));
+  if (dtype_bytes == 4) return run_pool<float, 4>(g, I, E, gradI, 2, c, static_cast<cudaStream_t>(stream));
   return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
 }
 

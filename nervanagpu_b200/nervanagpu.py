@@ -587,12 +587,15 @@ class NervanaGPU(object):
         assert layer.sizeO == O.size
         return self._execute_pool(layer, I, O, None, 0, repeat)
 
-    def bprop_pool(self, layer, I, E, grad_I, repeat=1):
+    def bprop_pool(self, layer, I, E, grad_I, repeat=1, relu_mask=False):
+        """relu_mask=True also applies grad_I *= (I > 0), the mask of the ReLU layer that produced
+        I, in the same pass (an extension: the reference runs it as a separate element-wise
+        kernel, nervanagpu/layers.py:87-96)."""
         assert layer.sizeI == I.size
         assert layer.sizeO == E.size
         assert layer.sizeI == grad_I.size
         assert I.dtype == grad_I.dtype
-        return self._execute_pool(layer, I, E, grad_I, 1, repeat)
+        return self._execute_pool(layer, I, E, grad_I, 2 if relu_mask else 1, repeat)
 
     def _execute_pool(self, layer, I, O, B, mode, repeat):
         assert I.dtype == O.dtype
@@ -602,8 +605,10 @@ class NervanaGPU(object):
         lib, stream, esz = self.lib, self.stream, I.dtype.itemsize
         if mode == 0:
             launch = lambda: _lib.check(lib.ng_pool_fprop(desc, esz, I.ptr, O.ptr, stream))
-        else:
+        elif mode == 1:
             launch = lambda: _lib.check(lib.ng_pool_bprop(desc, esz, I.ptr, O.ptr, B.ptr, stream))
+        else:
+            launch = lambda: _lib.check(lib.ng_pool_bprop_relu(desc, esz, I.ptr, O.ptr, B.ptr, stream))
         msecs = self._timed(launch, repeat)
         if msecs is not None:
             print("%7.3f msecs (%s)" % (msecs, layer))

@@ -18,6 +18,8 @@ from . import NervanaGPU, _lib
 CONV = {
     # name: (N, C, K, D, H, W, T, R, S, pad_d, pad_h, pad_w, str_d, str_h, str_w)
     "alex1": (128, 3, 64, 1, 224, 224, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    # conv1 after a 4x4 space-to-depth of its input: 48 channels, 3x3, stride 1 (same flops as alex1 up to padding)
+    "alex1_s2d": (128, 48, 64, 1, 57, 57, 1, 3, 3, 0, 0, 0, 1, 1, 1),
     "alex2": (128, 64, 192, 1, 27, 27, 1, 5, 5, 0, 2, 2, 1, 1, 1),
     "alex3": (128, 192, 384, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),
     "alex4": (128, 384, 256, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),

@@ -54,6 +54,23 @@ def test_bit_exact_against_oracle(ng, name):
     assert np.array_equal(B, refB.astype(np.float16))
 
 
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_fused_relu_mask_equals_bprop_then_mask(ng, name):
+    cfg = CASES[name]
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(31)
+    # a ReLU output: about half zeros (whole windows of zeros included), ties among the rest
+    I = (np.maximum(rng.integers(-8, 6, pd.dimI), 0) / 4.0).astype(np.float16)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float16)
+    _, refB = rm.pool_max(pd, I, E)
+    ref = (refB * (I > 0)).astype(np.float16)           # Layer.bprop_relu on the pool's deltas
+    layer = ng.pool_layer(np.float16, "max", *cfg)
+    dI, dE, dB = ng.array(I), ng.array(E), ng.empty(layer.dimI)
+    ng.bprop_pool(layer, dI, dE, dB, relu_mask=True)
+    assert np.array_equal(dB.get(), ref)
+    assert (ref != refB.astype(np.float16)).any() or not (I[refB != 0] <= 0).any()
+
+
 def test_fp32_pooling(ng):
     cfg = CASES["alexnet_3x3_s2_n64"]
     pd = rm.PoolDims(*cfg)

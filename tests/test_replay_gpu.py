@@ -70,6 +70,21 @@ def test_capture_needs_a_stream_and_counts_launches(streamed):
         plain.capture(lambda: None)          # default stream
 
 
+def test_relu_mask_fused_into_pool_backward_changes_nothing():
+    def run(fuse):
+        ng = NervanaGPU(stochastic_round=False)
+        stack = ConvStack(ng, TINY, seed=11)
+        stack.fuse_relu_mask = fuse
+        for _ in range(2):
+            stack.step()
+        return stack.weights_flat.get(), stack.grads_flat.get()
+
+    w0, g0 = run(False)
+    w1, g1 = run(True)
+    assert np.array_equal(g0, g1)
+    assert np.array_equal(w0, w1)
+
+
 def test_recorded_training_step_equals_live_step():
     def run(record):
         ng = NervanaGPU(stochastic_round=False)
