@@ -39,7 +39,9 @@ def build(force=False, verbose=False):
         o = s[:-3] + ".o"
         objs.append(o)
         if force or _newer(o, [s] + headers):
-            cmd = [nvcc] + NVCC_FLAGS + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
+            # NVCC_EXTRA: extra compiler flags for development builds (e.g. -DNG_TC_TIMELINE)
+            extra = os.environ.get("NVCC_EXTRA", "").split()
+            cmd = [nvcc] + NVCC_FLAGS + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", s, "-o", o]
             procs.append((s, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
     failed = False
     for s, p in procs:

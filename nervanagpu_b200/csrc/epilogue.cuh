@@ -37,6 +37,36 @@ __device__ __forceinline__ void sr_bits8(const EpiArgs& e, unsigned long long e8
   }
 }
 
+// Stochastic rounding of 8 consecutive outputs to fp16, out of line: ten Philox rounds inlined at
+// every use made the tensor-core kernel's code several times larger than the instruction cache
+// (and the round-to-nearest path paid for it in instruction-cache misses). `lin` is the linear
+// index of the first element; groups that do not start on a multiple of 8 (ragged rows) draw
+// per element.
+static __device__ __noinline__ uint4 sr_round8(EpiArgs e, unsigned long long lin, float v0, float v1, float v2, float v3,
+                                        float v4, float v5, float v6, float v7) {
+  const float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  __half h[8];
+  if ((lin & 7ull) == 0ull) {
+    uint32_t rnd[8];
+    sr_bits8(e, lin >> 3, rnd);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) h[i] = f2h_sr(v[i], rnd[i], e.sr_bits);
+  } else {
+#pragma unroll 1
+    for (int i = 0; i < 8; ++i) {
+      uint32_t r8[8];
+      const unsigned long long li = lin + i;
+      sr_bits8(e, li >> 3, r8);
+      h[i] = f2h_sr(v[i], r8[li & 7ull], e.sr_bits);
+    }
+  }
+  uint4 o;
+  __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) oh[i] = __halves2half2(h[2 * i], h[2 * i + 1]);
+  return o;
+}
+
 __device__ __forceinline__ float epi_scale(const EpiArgs& e, float acc) {
   float c = acc * e.alpha;
   if (e.relu) c = fmaxf(c, 0.0f);
@@ -90,21 +120,10 @@ __device__ __forceinline__ void epi_store8(const EpiArgs& e, float (&v)[8], void
   }
   __half h[8];
   if (e.sr_bits) {
-    uint32_t rnd[8];
-    // ragged rows can start a group off an 8-boundary: draw per element then (rare, slow path)
-    if ((lin & 7ull) == 0ull) {
-      sr_bits8(e, lin >> 3, rnd);
+    const uint4 packed = sr_round8(e, lin, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
+    const __half* ph = reinterpret_cast<const __half*>(&packed);
 #pragma unroll
-      for (int i = 0; i < 8; ++i) h[i] = f2h_sr(v[i], rnd[i], e.sr_bits);
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        uint32_t r8[8];
-        const unsigned long long li = lin + i;
-        sr_bits8(e, li >> 3, r8);
-        h[i] = f2h_sr(v[i], r8[li & 7ull], e.sr_bits);
-      }
-    }
+    for (int i = 0; i < 8; ++i) h[i] = ph[i];
   } else {
 #pragma unroll
     for (int i = 0; i < 8; ++i) h[i] = f2h_rn(v[i]);
@@ -120,6 +139,17 @@ __device__ __forceinline__ void epi_store8(const EpiArgs& e, float (&v)[8], void
     for (int i = 0; i < 8; ++i)
       if (i < nvalid) out[i] = h[i];
   }
+}
+
+// epi_store8 as a call, for the tensor-core kernel's register-store path (outputs that cannot be
+// staged: ragged or unaligned rows). That path is rare and the kernel's hot loops must stay within
+// the instruction cache, so its four uses share one copy of the code.
+template <bool F32OUT>
+__device__ __noinline__ void epi_store8_call(EpiArgs e, float v0, float v1, float v2, float v3, float v4, float v5,
+                                             float v6, float v7, void* crow, const void* oldrow, int col,
+                                             unsigned long long lin, int nvalid, bool vec) {
+  float v[8] = {v0, v1, v2, v3, v4, v5, v6, v7};
+  epi_store8<F32OUT>(e, v, crow, oldrow, col, lin, nvalid, vec);
 }
 
 // Same arithmetic as epi_store8 for 8 consecutive, fully valid, 16-byte aligned outputs, but the
@@ -153,11 +183,7 @@ __device__ __forceinline__ void epi_pack8(const EpiArgs& e, float (&v)[8], const
   }
   __half2* oh = reinterpret_cast<__half2*>(&lo);
   if (e.sr_bits) {
-    uint32_t rnd[8];
-    sr_bits8(e, lin >> 3, rnd);
-#pragma unroll
-    for (int i = 0; i < 4; ++i)
-      oh[i] = __halves2half2(f2h_sr(v[2 * i], rnd[2 * i], e.sr_bits), f2h_sr(v[2 * i + 1], rnd[2 * i + 1], e.sr_bits));
+    lo = sr_round8(e, lin, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7]);
   } else {
 #pragma unroll
     for (int i = 0; i < 4; ++i) oh[i] = __floats2half2_rn(v[2 * i], v[2 * i + 1]);

@@ -15,6 +15,14 @@ constexpr int kEpiWarps = 8;       // two per group of 32 TMEM lanes, each takes
 constexpr int kTcThreads = 64 + 32 * kEpiWarps;    // warp 0 TMA, warp 1 MMA, then the epilogue warps
 constexpr uint32_t kEpiStageBytes = kEpiWarps * 4096;  // one [32 rows][128 B] staging box per epilogue warp
 
+// Division of a non-negative 31-bit number by a run-time constant as multiply-high and shift
+// (round-up method: mul = ceil(2^(31+ceil(log2 d)) / d), quotient = umulhi(n, mul) >> shr). The
+// single producer thread decodes a tile with a dozen divisions; as hardware-emulated divides they
+// cost it about 0.8 us per tile.
+struct FastDiv {
+  uint32_t mul, shr, d;
+};
+
 struct TcParams {
   // ---- work decomposition: item = ((split * nz + z) * tiles_n + tile_n) * tiles_m + tile_m
   int tiles_m, tiles_n, nz, splits;
@@ -65,8 +73,6 @@ struct TcParams {
   int x_tap;                       // 0 in flattened mode else 1
   int dec_cpi, dec_q, dec_p, dec_m;  // chunk decode of the pixel space the chunks walk
   int oob_y;                       // a y/p coordinate that is out of range (forces zero fill)
-  int l2_prefetch;                 // bit 0: A boxes, bit 1: B boxes are requested into L2 ahead of the loads
-  int l2_ahead;                    // how many k-blocks ahead
 
   // ---- epilogue
   void* C;                         // fp16 or fp32 output
@@ -83,6 +89,13 @@ struct TcParams {
   uint32_t seed_lo, seed_hi, rng_offset;
   float* ws;                       // split-K partials [split][z][M][N] when splits > 1
   int* status;                     // device status word
+  // divisors of the tile / chunk / tap decodes, filled in by the launch code
+  FastDiv fd_tiles_m, fd_tiles_n, fd_nz, fd_cpi, fd_q, fd_p, fd_RS, fd_S, fd_red;
+  // Development builds (-DNG_TC_TIMELINE) only: %globaltimer stamps of the first CTAs' roles,
+  // [cta][tile][slot]; null otherwise.
+  unsigned long long* timeline;
 };
+
+constexpr int kTimelineCtas = 4, kTimelineTiles = 24, kTimelineSlots = 12;
 
 }  // namespace ngb

@@ -28,9 +28,35 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 
+// Development aid, compiled out unless -DNG_TC_TIMELINE: the first CTAs stamp %globaltimer at the
+// hand-offs between their roles (slots: 0/1 first/last copy of a tile issued, 2 accumulator free,
+// 3 first operands landed, 4 last MMA issued, 5 epilogue starts, 6 epilogue done).
+#ifdef NG_TC_TIMELINE
+#define NG_STAMP(tile, slot)                                                                      \
+  do {                                                                                            \
+    if (p.timeline && blockIdx.x < kTimelineCtas && (tile) < kTimelineTiles)                      \
+      p.timeline[(blockIdx.x * kTimelineTiles + (tile)) * kTimelineSlots + (slot)] = global_timer_ns(); \
+  } while (0)
+// cycle counters of the staged epilogue (warp 2): NG_CLK(k) adds the cycles since the previous
+// NG_CLK to bucket k (1: TMEM load, 2: convert + stage, 3: write-out, 0: everything else)
+#define NG_CLK(k)                                   \
+  do {                                              \
+    const long long now_ = clock64();               \
+    clk_acc[k] += now_ - clk_last;                  \
+    clk_last = now_;                                \
+  } while (0)
+#else
+#define NG_STAMP(tile, slot) do {} while (0)
+#define NG_CLK(k) do {} while (0)
+#endif
+
 namespace ngb {
 
 namespace {
+
+__device__ __forceinline__ int fast_div(int n, const FastDiv& f) {
+  return f.d == 1u ? n : static_cast<int>(__umulhi(static_cast<uint32_t>(n), f.mul) >> f.shr);
+}
 
 struct ChunkPos {
   int inner0, q, p, m;
@@ -41,11 +67,11 @@ struct ChunkPos {
 // (q, n) pair is one dimension of extent Q*N and dec_q == 1.
 __device__ __forceinline__ ChunkPos decode_chunk(const TcParams& p, int chunk) {
   ChunkPos c;
-  const int g = chunk / p.dec_cpi;
+  const int g = fast_div(chunk, p.fd_cpi);
   c.inner0 = (chunk - g * p.dec_cpi) * kChunk;
-  const int g2 = g / p.dec_q;
+  const int g2 = fast_div(g, p.fd_q);
   c.q = g - g2 * p.dec_q;
-  c.m = g2 / p.dec_p;
+  c.m = fast_div(g2, p.fd_p);
   c.p = g2 - c.m * p.dec_p;
   c.valid = c.m < p.dec_m;
   return c;
@@ -56,9 +82,9 @@ struct Tap {
 };
 __device__ __forceinline__ Tap decode_tap(const TcParams& p, int trs) {
   Tap tp;
-  tp.t = trs / p.RS;
+  tp.t = fast_div(trs, p.fd_RS);
   const int rs = trs - tp.t * p.RS;
-  tp.r = rs / p.S;
+  tp.r = fast_div(rs, p.fd_S);
   tp.s = rs - tp.r * p.S;
   return tp;
 }
@@ -90,12 +116,12 @@ struct WorkItem {
 };
 __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
   WorkItem it;
-  it.tile_m = w % p.tiles_m;
-  int r = w / p.tiles_m;
-  it.tile_n = r % p.tiles_n;
-  r /= p.tiles_n;
-  it.z = r % p.nz;
-  it.split = r / p.nz;
+  int r = fast_div(w, p.fd_tiles_m);
+  it.tile_m = w - r * p.tiles_m;
+  const int r2 = fast_div(r, p.fd_tiles_n);
+  it.tile_n = r - r2 * p.tiles_n;
+  it.split = fast_div(r2, p.fd_nz);
+  it.z = r2 - it.split * p.nz;
   it.kb0 = it.split * p.kb_per_split;
   it.kb1 = min(p.num_kb, it.kb0 + p.kb_per_split);
   return it;
@@ -166,6 +192,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    int ptile = 0;
+    (void)ptile;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const WorkItem it = decode_work(p, w);
       const int m0 = it.tile_m * kTileM * p.m_halves;
@@ -181,7 +209,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       bool tap_live = true;         // update: this A box's tap exists (last group may be short)
       if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
         if (!is_a) wk.cp = decode_chunk(p, n0 / kChunk + bi);
-        wk.trs = it.kb0 / p.red_chunks;
+        wk.trs = fast_div(it.kb0, p.fd_red);
         wk.rc = it.kb0 - wk.trs * p.red_chunks;
         wk.tap = decode_tap(p, wk.trs);
       } else if (p.mode == TC_UPDATE) {
@@ -270,21 +298,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           }
         }
       };
-      // A second walker runs `l2_ahead` k-blocks in front and asks the L2 for those boxes, so that
-      // the loads proper find their lines there: a load that waits for DRAM holds up the copy
-      // engine's queue behind it.
-      Walk pre = wk;
-      const bool pf_lane = active && tap_live && ((is_a ? p.l2_prefetch & 1 : p.l2_prefetch & 2) != 0);
-      if (p.l2_prefetch) {
-        for (int i = 0; i < p.l2_ahead && pre.kb < it.kb1; ++i) {
-          if (pf_lane) {
-            int c0, c1, c2, c3, c4;
-            coords(pre, c0, c1, c2, c3, c4);
-            tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
-          }
-          advance(pre);
-        }
-      }
+      // (Asking the L2 for the boxes of later k-blocks with prefetch copies was tried and was
+      // slower everywhere: a prefetch costs the copy engine as much as the load it precedes.)
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
@@ -299,17 +314,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         if (active) {
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
-        advance(wk);
-        if (p.l2_prefetch && pre.kb < it.kb1) {
-          if (pf_lane) {
-            int c0, c1, c2, c3, c4;
-            coords(pre, c0, c1, c2, c3, c4);
-            tma_prefetch_l2_5d(map, c0, c1, c2, c3, c4);
-          }
-          advance(pre);
+        if (lane == 0) {
+          if (kb == it.kb0) NG_STAMP(ptile, 0);       // first copy of the tile issued
+          if (kb == it.kb1 - 1) NG_STAMP(ptile, 1);   // last copy of the tile issued
         }
+        advance(wk);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
       }
+      ++ptile;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -339,11 +351,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
           tc_fence_after();
         }
+        NG_STAMP(local, 2);                           // accumulator is free
         for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
+          if (kb == it.kb0) NG_STAMP(local, 3);       // first operands have landed
           tc_fence_after();
           const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
           const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
@@ -370,17 +384,24 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
         if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
+        NG_STAMP(local, 4);                           // last MMA of the tile issued
       }
     }
     __syncwarp();
   } else {
     // =========================== epilogue ===========================
     const int lane_group = warp & 3;  // TMEM lanes [32*lane_group, +32) are visible to this warp
+    // One set of output-stage scalars, held in registers: split-K partials leave as untouched
+    // fp32 accumulators. (Choosing between two argument structs by reference put both in local
+    // memory, and every use became a load.)
+    const bool partial = p.splits > 1;
+    const bool f32 = partial || p.out_f32 != 0;
     EpiArgs ea;
-    ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
+    ea.alpha = partial ? 1.0f : p.alpha;
+    ea.beta = partial ? 0.0f : p.beta;
+    ea.relu = partial ? 0 : p.relu;
+    ea.sr_bits = partial ? 0 : p.sr_bits;
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
-    EpiArgs raw = ea;  // split-K partials: untouched accumulators
-    raw.alpha = 1.0f; raw.beta = 0.0f; raw.relu = 0; raw.sr_bits = 0;
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
@@ -392,9 +413,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const int acc = (wide || grouped) ? 0 : (local & 1);
       const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
+      if (warp == 2 && lane == 0) NG_STAMP(local, 5);   // accumulator complete, epilogue starts
+#ifdef NG_TC_TIMELINE
+      long long clk_acc[4] = {0, 0, 0, 0};
+      long long clk_last = clock64();
+#endif
       tc_fence_after();
       const int n0 = it.tile_n * p.block_n;
-      const bool partial = p.splits > 1;
       for (int h = 0; h < n_acc; ++h) {
         // accumulator h holds rows of row-tile `rt` of output slice `zt`; with stacked taps
         // (weight update, few rows per tap) every `pack_rows` lanes belong to the next slice
@@ -450,9 +475,19 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const int colb = n0 + cb * p.c_box_cols;
             for (int sub = 0; sub < subs; ++sub) {
               uint32_t r[32];
+              NG_CLK(0);
               tc_ld_32x32(taddr + static_cast<uint32_t>(cb * p.c_box_cols + sub * 32), r);
               tc_wait_ld();
-              if (sub == 0) {
+#ifdef NG_TC_TIMELINE
+              {   // touch every loaded register so that the load's real latency lands in bucket 1
+                uint32_t x = 0;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) x ^= r[i];
+                if (x == 0x9e3779b9u) clk_acc[0] += 1;
+              }
+#endif
+              NG_CLK(1);
+              if (sub == 0 && p.tma_store == 1) {
                 // the previous store from this warp's buffer must have read it before we overwrite
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
@@ -465,34 +500,69 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
                 uint4 lo, hi;
                 const bool live = row_ok && col < p.N;
-                if (partial) {
-                  epi_pack8<true>(raw, v, nullptr, 0ull, lo, hi);
-                } else if (p.out_f32) {
+                const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
+                // (no "memory" clobber on these stores: they are ordered with the loads of the
+                // write-out by being volatile and by the __syncwarp between them)
+                if (f32) {   // 8 fp32 = two chunks
                   epi_pack8<true>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 4 : nullptr,
                                   lin_row + col, lo, hi);
-                } else {
-                  epi_pack8<false>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 2 : nullptr,
-                                   lin_row + col, lo, hi);
-                }
-                const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
-                if (partial || p.out_f32) {   // 8 fp32 = two chunks
                   const int j = g * 2;
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + (((j) ^ (lane & 7)) << 4)),
-                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w));
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + (((j + 1) ^ (lane & 7)) << 4)),
-                               "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w) : "memory");
+                               "r"(hi.x), "r"(hi.y), "r"(hi.z), "r"(hi.w));
                 } else {                       // 8 fp16 = one chunk
+                  epi_pack8<false>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 2 : nullptr,
+                                   lin_row + col, lo, hi);
                   const int j = sub * 4 + g;
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + ((j ^ (lane & 7)) << 4)),
-                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w) : "memory");
+                               "r"(lo.x), "r"(lo.y), "r"(lo.z), "r"(lo.w));
                 }
               }
             }
-            fence_async_smem();
-            __syncwarp();
-            if (lane == 0) {
-              if (colb < p.N && row0 < p.M && zt_warp < p.nz_out) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
-              tma_store_commit();
+            NG_CLK(2);
+            if (p.tma_store == 1) {
+              fence_async_smem();
+              __syncwarp();
+              if (lane == 0) {
+                if (colb < p.N && row0 < p.M && zt_warp < p.nz_out) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
+                tma_store_commit();
+              }
+            } else {
+              // Write-out by the warp itself: each instruction stores four whole 128-byte rows
+              // (lane = row within the group of four, 16-byte chunk). A bulk tensor store would
+              // queue behind the operand loads of the copy engine, and the wait for it to release
+              // the staging buffer then costs ~2 us per box.
+              __syncwarp();
+              const int esz = (partial || p.out_f32) ? 4 : 2;
+              uint8_t* gbase;
+              long long gstride;
+              if (partial) {
+                gbase = reinterpret_cast<uint8_t*>(p.ws + static_cast<long long>(zc) * p.M * p.N);
+                gstride = static_cast<long long>(p.N) * 4;
+              } else {
+                gbase = static_cast<uint8_t*>(p.C) + static_cast<long long>(zt_warp) * p.c_zstride * esz;
+                gstride = p.ldc * esz;
+              }
+              const int j = lane & 7;
+              const int gcol = colb + j * (16 / esz);
+              const bool col_live = gcol < p.N && zt_warp < p.nz_out;
+              uint8_t* gp = gbase + (row0 + (lane >> 3)) * gstride + static_cast<long long>(gcol) * esz;
+              uint4 v[8];
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int t = i * 4 + (lane >> 3);
+                asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                             : "=r"(v[i].x), "=r"(v[i].y), "=r"(v[i].z), "=r"(v[i].w)
+                             : "r"(buf + static_cast<uint32_t>(t) * 128u + static_cast<uint32_t>((j ^ (t & 7)) << 4)));
+              }
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                if (col_live && row0 + i * 4 + (lane >> 3) < p.M) *reinterpret_cast<uint4*>(gp) = v[i];
+                gp += 4 * gstride;
+              }
+              __syncwarp();   // the buffer is free for the next box
+              NG_CLK(3);
             }
           }
         }
@@ -513,12 +583,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               float v[8];
 #pragma unroll
               for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
-              if (partial) {
-                epi_store8<true>(raw, v, crow, nullptr, col, 0ull, nvalid, (p.N & 3) == 0);
-              } else if (p.out_f32) {
-                epi_store8<true>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+              const bool vec = partial ? (p.N & 3) == 0 : p.vec_ok != 0;
+              if (f32) {
+                epi_store8_call<true>(ea, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], crow, oldrow, col,
+                                      lin_row + col, nvalid, vec);
               } else {
-                epi_store8<false>(ea, v, crow, oldrow, col, lin_row + col, nvalid, p.vec_ok != 0);
+                epi_store8_call<false>(ea, v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], crow, oldrow, col,
+                                       lin_row + col, nvalid, vec);
               }
             }
           }
@@ -527,6 +598,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acce_bar(h));
+          if (warp == 2 && lane == 0 && h == 0) NG_STAMP(local, 7);   // first half handed back
         }
       }
       if (!wide) {
@@ -534,6 +606,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(acce_bar(acc));
       }
+      if (warp == 2 && lane == 0) NG_STAMP(local, 6);   // this warp's share of the tile is stored
+#ifdef NG_TC_TIMELINE
+      if (warp == 2 && lane == 0 && p.timeline && blockIdx.x < kTimelineCtas && local < kTimelineTiles)
+        for (int k = 0; k < 4; ++k)
+          p.timeline[(blockIdx.x * kTimelineTiles + local) * kTimelineSlots + 8 + k] = clk_acc[k];
+#endif
     }
     // outstanding bulk stores must be complete before the CTA (and its shared memory) goes away
     if (p.tma_store && lane == 0) tma_store_wait_all();

@@ -1,7 +1,9 @@
 // Host side of the tensor-core engine: UMMA descriptor construction, ring sizing, split-K
 // choice and the launch itself.
 #include <algorithm>
+#include <cstdio>
 #include <mutex>
+#include <vector>
 
 #include "../../include/nervana_b200.h"
 #include "epilogue.cuh"
@@ -23,6 +25,30 @@ uint32_t desc_hi(uint32_t sbo_bytes) {
 // Lower 32 bits without the start address: leading byte offset in [16,30).
 uint32_t desc_lo(uint32_t lbo_bytes) { return ((lbo_bytes >> 4) & 0x3fffu) << 16; }
 }  // namespace
+
+static FastDiv make_fast_div(int d) {
+  FastDiv f = {0u, 0u, 1u};
+  if (d <= 1) return f;
+  uint32_t lg = 0;
+  while ((1u << lg) < static_cast<uint32_t>(d)) ++lg;        // ceil(log2 d), d >= 2 so lg >= 1
+  const unsigned pw = 31u + lg;
+  f.mul = static_cast<uint32_t>(((1ull << pw) + static_cast<uint32_t>(d) - 1u) / static_cast<uint32_t>(d));
+  f.shr = pw - 32u;
+  f.d = static_cast<uint32_t>(d);
+  return f;
+}
+
+static void fill_fast_divs(TcParams& p) {
+  p.fd_tiles_m = make_fast_div(p.tiles_m);
+  p.fd_tiles_n = make_fast_div(p.tiles_n);
+  p.fd_nz = make_fast_div(p.nz);
+  p.fd_cpi = make_fast_div(p.dec_cpi);
+  p.fd_q = make_fast_div(p.dec_q);
+  p.fd_p = make_fast_div(p.dec_p);
+  p.fd_RS = make_fast_div(p.RS);
+  p.fd_S = make_fast_div(p.S);
+  p.fd_red = make_fast_div(p.red_chunks);
+}
 
 // Bytes a K-major A descriptor may read past its (short) slot; kept inside the allocation.
 static uint32_t a_overread(const TcParams& p) {
@@ -96,15 +122,18 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
                                                p.stage_bytes);
 }
 
-// Output tensor map for the bulk-store epilogue: (columns, rows, z) over C, or over the split-K
-// workspace. Returns false when the output cannot be addressed that way (the kernel then stores
-// straight from registers).
-static bool make_store_map(CUtensorMap* map, TcParams& p) {
-  static const char* off = getenv("NG_TMA_STORE");
-  if (off && off[0] == '0') return false;
-  if ((p.N & 7) != 0) return false;
+// How tiles leave the epilogue: 2 = staged through swizzled shared memory and written out by the
+// warps in whole 128-byte rows (default), 1 = staged and written by bulk tensor stores over a
+// (columns, rows, z) map of C or of the split-K workspace (NG_TMA_STORE=1: measured slower, the
+// stores queue behind the operand loads), 0 = straight from registers (output not 16-byte
+// addressable, or NG_TMA_STORE=0).
+static int pick_store_mode(CUtensorMap* map, TcParams& p) {
+  static const char* sel = getenv("NG_TMA_STORE");
+  if (sel && sel[0] == '0') return 0;
+  const bool bulk = sel && sel[0] == '1';
+  if ((p.N & 7) != 0) return 0;
   // stacked taps: a warp's 32 rows must belong to one tap
-  if (p.acc_taps > 1 && (p.pack_rows & 31) != 0) return false;
+  if (p.acc_taps > 1 && (p.pack_rows & 31) != 0) return 0;
   const bool partial = p.splits > 1;
   const int esz = (partial || p.out_f32) ? 4 : 2;
   uint64_t dims[5] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), 1, 1, 1};
@@ -116,19 +145,20 @@ static bool make_store_map(CUtensorMap* map, TcParams& p) {
     str[0] = static_cast<uint64_t>(p.N) * 4;
     str[1] = str[0] * p.M;
   } else {
-    if (!p.vec_ok) return false;
+    if (!p.vec_ok) return 0;
     base = p.C;
     dims[2] = p.nz_out;
     str[0] = static_cast<uint64_t>(p.ldc) * esz;
     str[1] = p.nz_out > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : str[0] * p.M;
-    if (str[1] == 0) return false;
+    if (str[1] == 0) return 0;
   }
   str[2] = str[3] = std::max(str[1] * dims[2], str[0] * dims[1]);
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (str[0] & 15u) || (str[1] & 15u)) return false;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (str[0] & 15u) || (str[1] & 15u)) return 0;
   p.c_box_cols = 128 / esz;
+  if (!bulk) return 2;
   const uint32_t box[5] = {static_cast<uint32_t>(p.c_box_cols), 32, 1, 1, 1};
-  if (make_tensor_map(map, base, dims, str, box, esz) != NG_OK) return false;
-  return true;
+  if (make_tensor_map(map, base, dims, str, box, esz) != NG_OK) return 0;
+  return 1;
 }
 
 void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int num_kb) {
@@ -197,13 +227,6 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   p.splits = (p.num_kb + p.kb_per_split - 1) / p.kb_per_split;  // no empty partitions
   p.status = c->status;
-  {
-    // NG_L2_PREFETCH=<bits> / NG_L2_AHEAD=<k-blocks> override the policy (tuning aid)
-    static const char* pf = getenv("NG_L2_PREFETCH");
-    static const char* ahead = getenv("NG_L2_AHEAD");
-    p.l2_prefetch = pf ? atoi(pf) : 0;   // measured: the extra requests cost the copy engine more than they save
-    p.l2_ahead = ahead ? std::max(1, atoi(ahead)) : 8;
-  }
   // TMA counts the whole box (including zero-filled parts) against the barrier
   // stage_bytes was sized from padded regions; the bytes that actually land are:
   const uint32_t landed = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
@@ -223,17 +246,54 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   if (total > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many work items");
   const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
   CUtensorMap mapC = mapA;   // placeholder when the bulk-store epilogue is off
-  p.tma_store = make_store_map(&mapC, p) ? 1 : 0;
+  p.tma_store = pick_store_mode(&mapC, p);
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u) +
                         a_overread(p);
+  fill_fast_divs(p);
   TcParams launch = p;
   launch.stage_bytes = p.stage_bytes;
   // expect_tx must equal the bytes the boxes deliver
   if (landed != p.tx_bytes || landed > p.stage_bytes) {
     return fail(NG_ERR_INVALID_ARG, "internal: stage layout and box sizes disagree");
   }
+  launch.timeline = nullptr;
+#ifdef NG_TC_TIMELINE
+  static unsigned long long* tl_dev = nullptr;
+  const size_t tl_count = static_cast<size_t>(kTimelineCtas) * kTimelineTiles * kTimelineSlots;
+  const char* tl_out = getenv("NG_TC_TIMELINE_OUT");
+  if (tl_out) {
+    if (!tl_dev) NG_CUDA(cudaMalloc(&tl_dev, tl_count * 8));
+    NG_CUDA(cudaMemsetAsync(tl_dev, 0, tl_count * 8, stream));
+    launch.timeline = tl_dev;
+  }
+#endif
   igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, launch);
   NG_CHECK_LAUNCH();
+#ifdef NG_TC_TIMELINE
+  if (tl_out) {
+    std::vector<unsigned long long> tl(tl_count);
+    NG_CUDA(cudaStreamSynchronize(stream));
+    NG_CUDA(cudaMemcpy(tl.data(), tl_dev, tl_count * 8, cudaMemcpyDeviceToHost));
+    if (FILE* f = fopen(tl_out, "a")) {
+      unsigned long long t0 = ~0ull;
+      for (size_t i = 0; i < tl.size(); ++i) if (i % kTimelineSlots < 8 && tl[i] && tl[i] < t0) t0 = tl[i];
+      fprintf(f, "launch mode=%d M=%d N=%d tiles=%dx%dx%d splits=%d num_kb=%d stages=%d block_n=%d halves=%d groups=%dx%d\n",
+              p.mode, p.M, p.N, p.tiles_m, p.tiles_n, p.nz, p.splits, p.num_kb, p.stages, p.block_n, p.m_halves,
+              p.acc_groups, p.acc_taps);
+      for (int c2 = 0; c2 < kTimelineCtas; ++c2)
+        for (int t = 0; t < kTimelineTiles; ++t) {
+          const unsigned long long* s = &tl[(static_cast<size_t>(c2) * kTimelineTiles + t) * kTimelineSlots];
+          if (!s[0] && !s[2]) continue;
+          fprintf(f, "cta %d tile %2d:", c2, t);
+          for (int k = 0; k < 8; ++k) fprintf(f, " %8lld", s[k] ? static_cast<long long>(s[k] - t0) : -1ll);
+          fprintf(f, "  epilogue cycles other/tmem/convert/write:");
+          for (int k = 8; k < 12; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
+          fprintf(f, "\n");
+        }
+      fclose(f);
+    }
+  }
+#endif
   if (p.splits > 1) {
     EpiArgs ea;
     ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
@@ -388,6 +448,8 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   const int grid = static_cast<int>(std::min<long long>(total, slots->sm_count));
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
   p.tma_store = 0;   // this variant stores straight from registers
+  p.timeline = nullptr;
+  ngb::fill_fast_divs(p);
   igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;

@@ -36,6 +36,8 @@ CONV = {
 POOL = {
     # name: (N, C, D, H, W, J, T, R, S, pad_j, pad_d, pad_h, pad_w, str_j, str_d, str_h, str_w)
     "alexpool1": (128, 64, 1, 55, 55, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
+    "alexpool2": (128, 192, 1, 27, 27, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
+    "alexpool3": (128, 256, 1, 13, 13, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
     "vggpool1": (64, 64, 1, 224, 224, 1, 1, 2, 2, 0, 0, 0, 0, 1, 1, 2, 2),
     "pool4d": (32, 64, 16, 56, 56, 2, 2, 2, 2, 0, 0, 0, 0, 2, 2, 2, 2),
 }
@@ -87,8 +89,8 @@ def _fill(ng, shape, dtype=np.float16, seed=0, lo=-1.0, hi=1.0):
 
 def run_case(name, warm=3, reps=10, sr=False):
     ng = NervanaGPU(stochastic_round=sr)
-    if "_" in name and name.split("_")[0] in CONV and name.split("_")[1] in ("fprop", "bprop", "update"):
-        layer_name, op = name.split("_")[:2]
+    if "_" in name and name.rsplit("_", 1)[0] in CONV and name.rsplit("_", 1)[1] in ("fprop", "bprop", "update"):
+        layer_name, op = name.rsplit("_", 1)
         cfg = CONV[layer_name]
         layer = ng.conv_layer(np.float16, *cfg)
         I = _fill(ng, layer.dimI, seed=1, lo=0.0)
