@@ -402,6 +402,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     ea.relu = partial ? 0 : p.relu;
     ea.sr_bits = partial ? 0 : p.sr_bits;
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
+    // the common case gets a short path of its own: the epilogue is bound by instruction latency
+    // (two warps per scheduler), so every instruction fewer counts
+    const bool plain = ea.alpha == 1.0f && ea.beta == 0.0f && ea.sr_bits == 0;
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
@@ -492,6 +495,45 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
               }
+              const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
+              const uint32_t swz = static_cast<uint32_t>(lane & 7);
+              // (no "memory" clobber on the staging stores: they are ordered with the loads of the
+              // write-out by being volatile and by the __syncwarp between them)
+              if (plain && f32) {
+                // raw fp32 (split-K partials; fp32 results with alpha 1, beta 0): registers to staging
+#pragma unroll
+                for (int g = 0; g < 8; ++g) {
+                  uint32_t a = r[g * 4], b = r[g * 4 + 1], c = r[g * 4 + 2], d = r[g * 4 + 3];
+                  if (ea.relu) {
+                    a = __float_as_uint(fmaxf(__uint_as_float(a), 0.0f));
+                    b = __float_as_uint(fmaxf(__uint_as_float(b), 0.0f));
+                    c = __float_as_uint(fmaxf(__uint_as_float(c), 0.0f));
+                    d = __float_as_uint(fmaxf(__uint_as_float(d), 0.0f));
+                  }
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowb + ((g ^ swz) << 4)), "r"(a),
+                               "r"(b), "r"(c), "r"(d));
+                }
+                continue;
+              }
+              if (plain) {
+                // fp16 with alpha 1, beta 0, round to nearest: convert pairs, ReLU on the packed halves
+                // (rounding is monotonic, so max(round(x), 0) == round(max(x, 0)))
+                const __half2 zero2 = __float2half2_rn(0.0f);
+#pragma unroll
+                for (int g = 0; g < 4; ++g) {
+                  uint32_t w[4];
+#pragma unroll
+                  for (int i = 0; i < 4; ++i) {
+                    __half2 h = __floats2half2_rn(__uint_as_float(r[g * 8 + 2 * i]), __uint_as_float(r[g * 8 + 2 * i + 1]));
+                    if (ea.relu) h = __hmax2(h, zero2);
+                    w[i] = *reinterpret_cast<uint32_t*>(&h);
+                  }
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(
+                                   rowb + ((static_cast<uint32_t>(sub * 4 + g) ^ swz) << 4)),
+                               "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3]));
+                }
+                continue;
+              }
 #pragma unroll
               for (int g = 0; g < 4; ++g) {
                 const int col = colb + sub * 32 + g * 8;
@@ -500,9 +542,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[g * 8 + i]);
                 uint4 lo, hi;
                 const bool live = row_ok && col < p.N;
-                const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
-                // (no "memory" clobber on these stores: they are ordered with the loads of the
-                // write-out by being volatile and by the __syncwarp between them)
                 if (f32) {   // 8 fp32 = two chunks
                   epi_pack8<true>(ea, v, (live && oldrow) ? oldrow + static_cast<long long>(col) * 4 : nullptr,
                                   lin_row + col, lo, hi);
