@@ -179,6 +179,17 @@ int ng_pool_bprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, cons
  * nervanagpu/layers.py:87-96), because only a window's maximum receives error at all. */
 int ng_pool_bprop_relu(const ng_pool_desc* desc, int dtype_bytes, const void* I, const void* E, void* gradI,
                        void* stream);
+/* Forward pass that records each window's argmax (one byte per output element) in a buffer of the
+ * caller, and backward pass from that record, which then reads neither the input nor recomputes
+ * any window. The reference's backward kernel rescans every window (hpool_max.sass mode 1,
+ * launched at nervanagpu/nervanagpu.py:780-787); a training step that keeps the record between
+ * its forward and backward pass saves that scan. ng_pool_argmax_bytes gives the buffer size, or 0
+ * for shapes without this path (then use ng_pool_fprop / ng_pool_bprop). relu_mask as in
+ * ng_pool_bprop_relu. Results equal ng_pool_fprop / ng_pool_bprop / ng_pool_bprop_relu bit for bit. */
+int ng_pool_argmax_bytes(const ng_pool_desc* desc, int dtype_bytes, size_t* bytes);
+int ng_pool_fprop_argmax(const ng_pool_desc* desc, int dtype_bytes, const void* I, void* O, void* argmax, void* stream);
+int ng_pool_bprop_argmax(const ng_pool_desc* desc, int dtype_bytes, const void* argmax, const void* E, void* gradI,
+                         int relu_mask, void* stream);
 
 /* ---- generated element-wise kernels -----------------------------------------------------------
  * Replace pycuda.compiler.SourceModule / Function.prepare / prepared_async_call for the CUDA-C

@@ -92,6 +92,10 @@ SIGNATURES = {
     "ng_pool_fprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop_relu": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ng_pool_argmax_bytes": (c_int, [ctypes.POINTER(PoolDesc), c_int, ctypes.POINTER(c_size_t)]),
+    "ng_pool_fprop_argmax": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ng_pool_bprop_argmax": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                     c_void_p]),
     "ng_ew_compile": (c_int, [c_char_p, c_char_p, c_int, ctypes.POINTER(c_void_p)]),
     "ng_ew_compile_only": (c_int, [c_char_p, c_int]),
     "ng_ew_compile_log": (c_char_p, []),

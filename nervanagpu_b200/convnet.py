@@ -99,6 +99,13 @@ class ConvStack(object):
         self.input.set(self.host_input)
         top = (rng.uniform(-1.0, 1.0, self.layers[-1].dimO) * 0.125).astype(np.float16)
         self.top_delta.set(top)
+        # pooling layers keep their windows' argmax between the forward and the backward pass
+        self.argmax = [None] * len(self.layers)
+        for i, l in enumerate(self.layers):
+            if not isinstance(l, ConvLayer):
+                nbytes = ng.pool_argmax_bytes(l)
+                if nbytes:
+                    self.argmax[i] = ng.empty((nbytes,), dtype=np.uint8)
         self.probe = None    # optional callable(name, layer, launch) used to time single launches
         self.fuse_relu_mask = True   # False: every ReLU mask is its own element-wise kernel, as in the reference
 
@@ -122,7 +129,7 @@ class ConvStack(object):
             if isinstance(l, ConvLayer):
                 self._run("fprop_conv", l, lambda l=l, x=x, y=y: ng.fprop_conv(l, x, l.weights, y, relu=True))
             else:
-                self._run("fprop_pool", l, lambda l=l, x=x, y=y: ng.fprop_pool(l, x, y))
+                self._run("fprop_pool", l, lambda l=l, x=x, y=y, a=self.argmax[i]: ng.fprop_pool(l, x, y, argmax=a))
             x = y
         return x
 
@@ -146,8 +153,8 @@ class ConvStack(object):
                 # the pool reads the (ReLU) output of the conv below it anyway: its backward pass
                 # applies that layer's mask as it writes the deltas
                 fuse = self.fuse_relu_mask and i > 0 and isinstance(self.layers[i - 1], ConvLayer)
-                self._run("bprop_pool", l, lambda l=l, x=x, grad=grad, dx=dx, fuse=fuse:
-                          ng.bprop_pool(l, x, grad, dx, relu_mask=fuse))
+                self._run("bprop_pool", l, lambda l=l, x=x, grad=grad, dx=dx, fuse=fuse, a=self.argmax[i]:
+                          ng.bprop_pool(l, x, grad, dx, relu_mask=fuse, argmax=a))
                 masked = fuse
             grad = dx
         if self.comm is not None:

@@ -251,11 +251,13 @@ __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restr
   const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
   if (O) store8(O + o, best);
   if (arg_out) {
-    // one byte per output: the tap (r*S + s) of the first maximum
+    // one byte per output: the tap (r*S + s) of the first maximum. mask_pos 1: a window whose
+    // maximum is not positive names no tap (its error is dropped); mask_pos 2: such windows are
+    // flagged in bit 7 and the backward pass decides whether the flag counts.
     if (mask_pos) {
 #pragma unroll
       for (int i = 0; i < 8; ++i)
-        if (!(best[i] > 0.0f)) arg[i] = 255;   // names no tap: the window's error is dropped
+        if (!(best[i] > 0.0f)) arg[i] = mask_pos == 1 ? 255 : (arg[i] | 0x80);
     }
     uint2 packed;
     packed.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
@@ -270,7 +272,9 @@ template <int R, int S, int SH, int SW>
 __global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __restrict__ arg,
                                                            const __half* __restrict__ E,
                                                            __half* __restrict__ dI, int H, int W, int N, int P, int Q,
-                                                           int BW) {
+                                                           int BW, uint32_t byte_and) {
+  // byte_and 0x7f7f7f7f drops the "maximum not positive" flag of recorded argmax bytes (no ReLU
+  // mask wanted); with 0xffffffff a flagged byte is >= 128 and matches no tap.
   constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
@@ -294,7 +298,9 @@ __global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __res
       const int q = b - (WQ - 1) + wq;
       if (q < 0 || q >= Q) continue;
       const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
-      const uint2 pk = *reinterpret_cast<const uint2*>(arg + o);
+      uint2 pk = *reinterpret_cast<const uint2*>(arg + o);
+      pk.x &= byte_and;
+      pk.y &= byte_and;
       const int idx[8] = {static_cast<int>(pk.x & 255u), static_cast<int>((pk.x >> 8) & 255u),
                           static_cast<int>((pk.x >> 16) & 255u), static_cast<int>(pk.x >> 24),
                           static_cast<int>(pk.y & 255u), static_cast<int>((pk.y >> 8) & 255u),
@@ -408,6 +414,21 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
     pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(
         static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), nullptr, g.H, g.W, g.N, g.P, g.Q, 0);
     NG_CHECK_LAUNCH();
+  } else if (mode == 3) {
+    // forward pass that also records each window's argmax (bit 7: maximum not positive) in the
+    // caller's buffer, for a later backward pass that then need not look at the input again
+    pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(
+        static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), reinterpret_cast<uint8_t*>(arg_ws),
+        g.H, g.W, g.N, g.P, g.Q, 2);
+    NG_CHECK_LAUNCH();
+  } else if (mode == 4 || mode == 5) {
+    // backward pass from a recorded argmax; mode 5 also applies the ReLU mask of the layer below
+    const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
+    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
+        reinterpret_cast<const uint8_t*>(arg_ws), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W,
+        g.N, g.P, g.Q, BW, mode == 5 ? 0xffffffffu : 0x7f7f7f7fu);
+    NG_CHECK_LAUNCH();
   } else if (R <= SH && S <= SW) {
     // windows do not overlap: one pass, each block of inputs sees at most one window
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
@@ -424,7 +445,8 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
     dim3 grid((BW * nvec + 255) / 256, BH, g.C);
     pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(arg8, static_cast<const __half*>(EO),
-                                                                 static_cast<__half*>(out), g.H, g.W, g.N, g.P, g.Q, BW);
+                                                                 static_cast<__half*>(out), g.H, g.W, g.N, g.P, g.Q, BW,
+                                                                 0xffffffffu);
     NG_CHECK_LAUNCH();
   }
   return NG_OK;
@@ -536,6 +558,47 @@ int ng_pool_bprop(const ng_pool_desc* d, int dtype_bytes, const void* I, const v
   if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
   if (dtype_bytes == 4) return run_pool<float, 4>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
   return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+int ng_pool_argmax_bytes(const ng_pool_desc* d, int dtype_bytes, size_t* bytes) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!bytes) return fail(NG_ERR_INVALID_ARG, "bytes is null");
+  const bool plain = dtype_bytes == 2 && g.J == 1 && g.T == 1 && g.D == 1 && g.str_j == 1 && g.str_d == 1 &&
+                     g.pad_j == 0 && g.pad_d == 0 && g.pad_h == 0 && g.pad_w == 0 && g.N % 8 == 0 && g.C <= 65535 &&
+                     g.H <= 65535 && g.str_h == g.str_w && g.R == g.S &&
+                     ((g.R == 3 && (g.str_h == 2 || g.str_h == 3)) || (g.R == 2 && g.str_h == 2));
+  *bytes = plain ? static_cast<size_t>(g.K) * g.M * g.P * g.Q * g.N : 0;
+  return NG_OK;
+}
+
+int ng_pool_fprop_argmax(const ng_pool_desc* d, int dtype_bytes, const void* I, void* O, void* argmax, void* stream) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !O || !argmax) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  if (dtype_bytes != 2 || (reinterpret_cast<uintptr_t>(argmax) & 7u))
+    return fail(NG_ERR_UNSUPPORTED, "recorded argmax needs fp16 tensors and an 8-byte aligned buffer");
+  if (!current_ctx()) return NG_ERR_CUDA;
+  rc = try_pool2d(g, I, O, O, 3, static_cast<int*>(argmax), static_cast<cudaStream_t>(stream));
+  if (rc > 0) return fail(NG_ERR_UNSUPPORTED, "this pooling shape has no recorded-argmax path (see ng_pool_argmax_bytes)");
+  return rc;
+}
+
+int ng_pool_bprop_argmax(const ng_pool_desc* d, int dtype_bytes, const void* argmax, const void* E, void* gradI,
+                         int relu_mask, void* stream) {
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!argmax || !E || !gradI) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  if (dtype_bytes != 2 || (reinterpret_cast<uintptr_t>(argmax) & 7u))
+    return fail(NG_ERR_UNSUPPORTED, "recorded argmax needs fp16 tensors and an 8-byte aligned buffer");
+  if (!current_ctx()) return NG_ERR_CUDA;
+  rc = try_pool2d(g, nullptr, E, gradI, relu_mask ? 5 : 4,
+                  static_cast<int*>(const_cast<void*>(argmax)), static_cast<cudaStream_t>(stream));
+  if (rc > 0) return fail(NG_ERR_UNSUPPORTED, "this pooling shape has no recorded-argmax path (see ng_pool_argmax_bytes)");
+  return rc;
 }
 
 int ng_pool_bprop_relu(const ng_pool_desc* d, int dtype_bytes, const void* I, const void* E, void* gradI,

@@ -582,28 +582,45 @@ class NervanaGPU(object):
         return PoolLayer(self, dtype, op, N, C, D, H, W, J, T, R, S, pad_j, pad_d, pad_h, pad_w,
                          str_j, str_d, str_h, str_w)
 
-    def fprop_pool(self, layer, I, O, repeat=1):
+    def pool_argmax_bytes(self, layer, dtype=np.float16):
+        """Size of the buffer fprop_pool(..., argmax=) fills, or 0 when this layer has no such path."""
+        n = ctypes.c_size_t()
+        _lib.check(self.lib.ng_pool_argmax_bytes(ctypes.byref(layer.desc), np.dtype(dtype).itemsize, ctypes.byref(n)))
+        return n.value
+
+    def fprop_pool(self, layer, I, O, repeat=1, argmax=None):
+        """argmax: optional uint8 tensor of pool_argmax_bytes(layer) elements that receives each
+        window's argmax, for bprop_pool(..., argmax=) (an extension: the reference's backward
+        kernel rescans the windows, nervanagpu/nervanagpu.py:780-787)."""
         assert layer.sizeI == I.size
         assert layer.sizeO == O.size
-        return self._execute_pool(layer, I, O, None, 0, repeat)
+        return self._execute_pool(layer, I, O, None, 0, repeat, argmax)
 
-    def bprop_pool(self, layer, I, E, grad_I, repeat=1, relu_mask=False):
+    def bprop_pool(self, layer, I, E, grad_I, repeat=1, relu_mask=False, argmax=None):
         """relu_mask=True also applies grad_I *= (I > 0), the mask of the ReLU layer that produced
         I, in the same pass (an extension: the reference runs it as a separate element-wise
-        kernel, nervanagpu/layers.py:87-96)."""
+        kernel, nervanagpu/layers.py:87-96). argmax: the record a forward pass over the same I
+        left (see fprop_pool); I is then not read."""
         assert layer.sizeI == I.size
         assert layer.sizeO == E.size
         assert layer.sizeI == grad_I.size
         assert I.dtype == grad_I.dtype
-        return self._execute_pool(layer, I, E, grad_I, 2 if relu_mask else 1, repeat)
+        return self._execute_pool(layer, I, E, grad_I, 2 if relu_mask else 1, repeat, argmax)
 
-    def _execute_pool(self, layer, I, O, B, mode, repeat):
+    def _execute_pool(self, layer, I, O, B, mode, repeat, argmax=None):
         assert I.dtype == O.dtype
         if I.dtype.type not in (np.float16, np.float32):
             raise TypeError("pooling supports fp16 and fp32 tensors")
         desc = ctypes.byref(layer.desc)
         lib, stream, esz = self.lib, self.stream, I.dtype.itemsize
-        if mode == 0:
+        if argmax is not None:
+            assert argmax.nbytes >= layer.sizeO
+            if mode == 0:
+                launch = lambda: _lib.check(lib.ng_pool_fprop_argmax(desc, esz, I.ptr, O.ptr, argmax.ptr, stream))
+            else:
+                launch = lambda: _lib.check(lib.ng_pool_bprop_argmax(desc, esz, argmax.ptr, O.ptr, B.ptr,
+                                                                     int(mode == 2), stream))
+        elif mode == 0:
             launch = lambda: _lib.check(lib.ng_pool_fprop(desc, esz, I.ptr, O.ptr, stream))
         elif mode == 1:
             launch = lambda: _lib.check(lib.ng_pool_bprop(desc, esz, I.ptr, O.ptr, B.ptr, stream))

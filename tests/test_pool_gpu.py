@@ -71,6 +71,33 @@ def test_fused_relu_mask_equals_bprop_then_mask(ng, name):
     assert (ref != refB.astype(np.float16)).any() or not (I[refB != 0] <= 0).any()
 
 
+@pytest.mark.parametrize("name", ["alexnet_3x3_s2_n64", "vgg_2x2_n32", "stride_larger_than_window"])
+@pytest.mark.parametrize("mask", [False, True])
+def test_recorded_argmax_gives_the_same_backward_pass(ng, name, mask):
+    cfg = CASES[name]
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(77)
+    I = (np.maximum(rng.integers(-8, 6, pd.dimI), 0) / 4.0).astype(np.float16)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float16)
+    layer = ng.pool_layer(np.float16, "max", *cfg)
+    nbytes = ng.pool_argmax_bytes(layer)
+    if name == "stride_larger_than_window":
+        assert nbytes == 0                      # no specialised path: callers fall back
+        return
+    assert nbytes == int(np.prod(pd.dimO))
+    dI, dE = ng.array(I), ng.array(E)
+    O1, O2 = ng.empty(layer.dimO), ng.empty(layer.dimO)
+    B1, B2 = ng.empty(layer.dimI), ng.empty(layer.dimI)
+    rec = ng.empty((nbytes,), dtype=np.uint8)
+    ng.fprop_pool(layer, dI, O1)
+    ng.fprop_pool(layer, dI, O2, argmax=rec)
+    ng.bprop_pool(layer, dI, dE, B1, relu_mask=mask)
+    dI.fill(0)                                  # the recorded pass must not need the input
+    ng.bprop_pool(layer, dI, dE, B2, relu_mask=mask, argmax=rec)
+    assert np.array_equal(O1.get(), O2.get())
+    assert np.array_equal(B1.get(), B2.get())
+
+
 def test_fp32_pooling(ng):
     cfg = CASES["alexnet_3x3_s2_n64"]
     pd = rm.PoolDims(*cfg)
