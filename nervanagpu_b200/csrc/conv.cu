@@ -524,14 +524,12 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   const long long cols = 1ll * g.M * g.P * g.Q * g.N;
   TcParams p = {};
   p.mode = TC_FPROP;
-  p.block_n = 256;
   p.M = g.K; p.N = static_cast<int>(cols);
-  p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {1, 1, pick_kb_rows(g.C)};
   p.red_chunks = (g.C + lay.kb_rows - 1) / lay.kb_rows;
   p.num_kb = RST * p.red_chunks;
-  tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  tc_pick_tile(c, p, cols, p.num_kb, lay.kb_rows);
   tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.Q, g.P, g.M, mode);
@@ -569,14 +567,12 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   const long long cols = 1ll * g.D * g.H * g.W * g.N;
   TcParams p = {};
   p.mode = TC_BPROP;
-  p.block_n = 256;
   p.M = g.C; p.N = static_cast<int>(cols);
-  p.tiles_n = static_cast<int>((cols + p.block_n - 1) / p.block_n);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {0, 1, kChunk};
   p.red_chunks = (g.K + kChunk - 1) / kChunk;
   p.num_kb = RST * p.red_chunks;
-  tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  tc_pick_tile(c, p, cols, p.num_kb, kChunk);
   tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.W, g.H, g.D, mode);

@@ -63,6 +63,8 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
 // L2 -> SM traffic per flop, but no overlap of the epilogue with the next tile and coarser waves).
 // `col_tiles` = column tiles x z x splits. Sets p.m_halves and p.tiles_m.
 void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int num_kb);
+// Chooses m_halves and block_n (256/192/128) together and sets tiles_m / tiles_n; p.M must be set.
+void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, int kb_rows);
 
 // Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
 constexpr int kMaxSplits = 160;

@@ -182,6 +182,43 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
   }
 }
 
+// Tile rows (128 / 256) and tile columns (256 / 192 / 128) of a convolution's forward or backward
+// pass together, by modelled time: tiles run in waves of one per SM; a k-block costs the larger
+// of its operand feed (copy engine: ~68 bytes/ns per SM) and its MMAs (~(rows + columns)/2 cycles
+// per K=16 step); a 256-row tile pays for its epilogue (not overlapped), a 128-row tile does not.
+// 85 tiles of 256 columns on 148 SMs (the 13x13 AlexNet layers) lose to 113 tiles of 192.
+void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, int kb_rows) {
+  static const char* force_rows = getenv("NG_TILE_ROWS");
+  static const char* force_cols = getenv("NG_TILE_COLS");
+  const double sm = c->sm_count;
+  double best = -1.0;
+  int best_h = 1, best_bn = 256;
+  for (int h = 1; h <= 2; ++h) {
+    if (h == 2 && p.M <= kTileM) continue;
+    if (force_rows && (force_rows[0] == '2') != (h == 2) && p.M > kTileM) continue;
+    for (int bn = 256; bn >= 128; bn -= 64) {
+      if (force_cols && atoi(force_cols) != bn) continue;
+      const long long tm = (p.M + kTileM * h - 1) / (kTileM * h);
+      const long long tn = (cols + bn - 1) / bn;
+      const double waves = static_cast<double>((tm * tn + c->sm_count - 1) / c->sm_count);
+      (void)sm;
+      const double feed_ns = (kTileM * h + bn) * kb_rows * 2.0 / 68.0;
+      const double mma_ns = h * (kb_rows / 16) * (kTileM + bn) * 0.5 / 1.9;
+      const double epi_ns = h == 2 ? 5500.0 * bn / 256.0 : 600.0;
+      const double t = waves * (num_kb * std::max(feed_ns, mma_ns) + epi_ns);
+      if (best < 0.0 || t < best) {
+        best = t;
+        best_h = h;
+        best_bn = bn;
+      }
+    }
+  }
+  p.m_halves = best_h;
+  p.block_n = best_bn;
+  p.tiles_m = (p.M + kTileM * best_h - 1) / (kTileM * best_h);
+  p.tiles_n = static_cast<int>((cols + best_bn - 1) / best_bn);
+}
+
 int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems) {
   if (tiles >= c->sm_count || num_kb < 8) return 1;
   // Makespan model: items run in waves of one per SM; an item costs its k-blocks plus a fixed
