@@ -108,6 +108,10 @@ class ConvStack(object):
                     self.argmax[i] = ng.empty((nbytes,), dtype=np.uint8)
         self.probe = None    # optional callable(name, layer, launch) used to time single launches
         self.fuse_relu_mask = True   # False: every ReLU mask is its own element-wise kernel, as in the reference
+        # weight updates on a second stream beside the backward chain (needs a stream of the
+        # backend's own: work on the default stream would serialise with it anyway)
+        self.overlap_update = ng.stream is not None
+        self._side, self._side_busy = None, False
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)
@@ -146,9 +150,20 @@ class ConvStack(object):
                 if not masked:
                     self._run("bprop_relu", l, lambda grad=grad, y=y: _relu_mask(grad, y))
                 masked = False
+                # The weight gradient is needed only at the end of the step, the input gradient by
+                # the next layer down: with a side stream the update runs beside the backward chain
+                # and fills the SMs that kernels with fewer than 148 tiles leave idle.
+                side = self._fork_side() if self.overlap_update and self.probe is None else None
                 if dx is not None:
                     self._run("bprop_conv", l, lambda l=l, grad=grad, dx=dx: ng.bprop_conv(l, l.weights, grad, dx))
-                self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
+                if side is not None:
+                    main, ng.stream = ng.stream, side
+                    try:
+                        ng.update_conv(l, x, grad, l.updat_out)
+                    finally:
+                        ng.stream = main
+                else:
+                    self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
             else:
                 # the pool reads the (ReLU) output of the conv below it anyway: its backward pass
                 # applies that layer's mask as it writes the deltas
@@ -157,9 +172,30 @@ class ConvStack(object):
                           ng.bprop_pool(l, x, grad, dx, relu_mask=fuse, argmax=a))
                 masked = fuse
             grad = dx
+        self._join_side()
         if self.comm is not None:
             self._run("allreduce_dW", None, self.allreduce_grads)
         self._run("grad_descent", None, self.grad_descent)
+
+    def _fork_side(self):
+        """The side stream, made to wait for everything queued on the main stream so far."""
+        lib = self.ng.lib
+        if self._side is None:
+            self._side = self.ng.new_stream()
+            self._fork_ev, self._join_ev = ctypes.c_void_p(), ctypes.c_void_p()
+            _lib.check(lib.ng_event_create(ctypes.byref(self._fork_ev)))
+            _lib.check(lib.ng_event_create(ctypes.byref(self._join_ev)))
+        _lib.check(lib.ng_event_record(self._fork_ev, self.ng.stream))
+        _lib.check(lib.ng_stream_wait_event(self._side, self._fork_ev))
+        self._side_busy = True
+        return self._side
+
+    def _join_side(self):
+        if self._side_busy:
+            lib = self.ng.lib
+            _lib.check(lib.ng_event_record(self._join_ev, self._side))
+            _lib.check(lib.ng_stream_wait_event(self.ng.stream, self._join_ev))
+            self._side_busy = False
 
     def allreduce_grads(self):
         _lib.check(self.ng.lib.ng_comm_allreduce_f32(self.comm, self.grads_flat.ptr, self.grads_flat.size,

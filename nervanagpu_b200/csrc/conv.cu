@@ -377,7 +377,7 @@ int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I
   const int ntb = g.T * tb.nr * tb.ns;
   const long long cols = 1ll * g.M * g.P * g.Q * g.N;
   const size_t fp_bytes = static_cast<size_t>(tb.rows) * ntb * g.K * 2;
-  int rc = ensure_workspace(c, fp_bytes);
+  int rc = ensure_workspace(c, stream, fp_bytes);
   if (rc != NG_OK) return rc;
   __half* Fp = reinterpret_cast<__half*>(c->ws);
   filter_repack_kernel<<<launch_1d(1ll * tb.rows * ntb * g.K / 8, 256, c), 256, 0, stream>>>(
@@ -421,7 +421,7 @@ int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* 
   // workspace: [split-K partials of the engine, at most 32 splits][Dp]
   const size_t dp_bytes = static_cast<size_t>(ntb) * tb.rows * g.K * 4;
   const size_t dp_off = (kMaxSplits * dp_bytes + 255) & ~size_t(255);
-  int rc = ensure_workspace(c, dp_off + dp_bytes);
+  int rc = ensure_workspace(c, stream, dp_off + dp_bytes);
   if (rc != NG_OK) return rc;
   float* Dp = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c->ws) + dp_off);
   TcParams p = {};
@@ -501,7 +501,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
     if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
     if (im2col) {
       const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
-      rc = ensure_workspace(c, col_bytes);
+      rc = ensure_workspace(c, stream, col_bytes);
       if (rc != NG_OK) return rc;
       __half* col = reinterpret_cast<__half*>(c->ws);
       im2col_kernel<<<im2col_grid(g), 256, 0, stream>>>(g, static_cast<const __half*>(I), col);
@@ -647,7 +647,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     // dF[crst][k] = col[crst][span] * E[k][span]^T  (both K-major: an "nt" GEMM with split-K)
     const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
     const size_t col_off = ((static_cast<size_t>(kMaxSplits) * g.C * RST * g.K * 4) + 255) & ~size_t(255);  // room for partials
-    rc = ensure_workspace(c, col_off + col_bytes);
+    rc = ensure_workspace(c, stream, col_off + col_bytes);
     if (rc != NG_OK) return rc;
     __half* col = reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(c->ws) + col_off);
     const long long total = 1ll * g.C * RST * span / 8;

@@ -1,5 +1,6 @@
 // Host-side internals shared by the translation units of libnervana_b200.so.
 #pragma once
+#include <map>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -15,7 +16,14 @@ struct DeviceCtx {
   int device = -1;
   int sm_count = 0;
   int* status = nullptr;     // device int written by kernels whose bounded wait gave up
-  float* ws = nullptr;       // split-K / conv scratch, grown on demand
+  // split-K / conv / pooling scratch, grown on demand, one buffer per stream; ws / ws_bytes name
+  // the buffer of the stream the last ensure_workspace call was for
+  struct Scratch {
+    float* ptr = nullptr;
+    size_t bytes = 0;
+  };
+  std::map<cudaStream_t, Scratch> scratch;
+  float* ws = nullptr;
   size_t ws_bytes = 0;
   bool smem_attr_set = false;
   bool capturing = false;    // a stream capture is open: nothing may allocate or synchronise
@@ -42,8 +50,9 @@ void count_launch();
 
 // Context of the current device (initialised on first use). Null + error set on failure.
 DeviceCtx* current_ctx();
-// Ensure the workspace holds at least `bytes`; may synchronise the device when it has to grow.
-int ensure_workspace(DeviceCtx* c, size_t bytes);
+// Ensure the workspace of `stream` holds at least `bytes` and make c->ws point at it; may
+// synchronise the device when it has to grow.
+int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes);
 
 // Rank-5 tiled tensor map over fp16 (elem_bytes 2) data. dims[0] is the contiguous dimension;
 // strides_bytes[i] is the byte stride of dims[i+1]. Swizzle is chosen from the inner box width.

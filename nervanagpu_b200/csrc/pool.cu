@@ -482,7 +482,7 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
   // library workspace), then gather
   int* arg_ws = nullptr;
   if (mode != 0) {
-    int rc = ensure_workspace(c, static_cast<size_t>(out_elems) * sizeof(int));
+    int rc = ensure_workspace(c, stream, static_cast<size_t>(out_elems) * sizeof(int));
     if (rc != NG_OK) return rc;
     arg_ws = reinterpret_cast<int*>(c->ws);
   }

@@ -71,21 +71,26 @@ DeviceCtx* current_ctx() {
   return c;
 }
 
-int ensure_workspace(DeviceCtx* c, size_t bytes) {
-  if (bytes <= c->ws_bytes) return NG_OK;
-  if (c->capturing) {
-    return fail(NG_ERR_UNSUPPORTED,
-                "the workspace would have to grow during a capture: run the sequence once before recording it");
+int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes) {
+  // one scratch buffer per stream: calls queued on different streams may run at the same time
+  DeviceCtx::Scratch& s = c->scratch[stream];
+  if (bytes > s.bytes) {
+    if (c->capturing) {
+      return fail(NG_ERR_UNSUPPORTED,
+                  "the workspace would have to grow during a capture: run the sequence once before recording it");
+    }
+    // growing: earlier launches may still read the old buffer
+    NG_CUDA(cudaDeviceSynchronize());
+    if (s.ptr) NG_CUDA(cudaFree(s.ptr));
+    s.ptr = nullptr;
+    s.bytes = 0;
+    size_t want = bytes + (bytes >> 2);
+    want = (want + (1u << 20) - 1) & ~((size_t(1) << 20) - 1);
+    NG_CUDA(cudaMalloc(&s.ptr, want));
+    s.bytes = want;
   }
-  // growing: earlier launches may still read the old buffer
-  NG_CUDA(cudaDeviceSynchronize());
-  if (c->ws) NG_CUDA(cudaFree(c->ws));
-  c->ws = nullptr;
-  c->ws_bytes = 0;
-  size_t want = bytes + (bytes >> 2);
-  want = (want + (1u << 20) - 1) & ~((size_t(1) << 20) - 1);
-  NG_CUDA(cudaMalloc(&c->ws, want));
-  c->ws_bytes = want;
+  c->ws = s.ptr;
+  c->ws_bytes = s.bytes;
   return NG_OK;
 }
 

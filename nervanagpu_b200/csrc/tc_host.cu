@@ -269,7 +269,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   const uint32_t landed = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
   if (p.splits > 1) {
     const size_t need = static_cast<size_t>(p.splits) * p.nz_out * p.M * p.N * sizeof(float);
-    int rc = ensure_workspace(c, need);
+    int rc = ensure_workspace(c, stream, need);
     if (rc != NG_OK) return rc;
     p.ws = c->ws;
   } else {

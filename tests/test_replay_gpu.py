@@ -85,6 +85,23 @@ def test_relu_mask_fused_into_pool_backward_changes_nothing():
     assert np.array_equal(w0, w1)
 
 
+def test_weight_updates_on_a_side_stream_change_nothing():
+    def run(overlap):
+        ng = NervanaGPU(stochastic_round=False)
+        ng.stream = ng.new_stream()
+        stack = ConvStack(ng, TINY, seed=11)
+        assert stack.overlap_update
+        stack.overlap_update = overlap
+        for _ in range(3):
+            stack.step()
+        return stack.weights_flat.get(), stack.grads_flat.get()
+
+    w0, g0 = run(False)
+    w1, g1 = run(True)
+    assert np.array_equal(g0, g1)
+    assert np.array_equal(w0, w1)
+
+
 def test_recorded_training_step_equals_live_step():
     def run(record):
         ng = NervanaGPU(stochastic_round=False)
