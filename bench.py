@@ -262,6 +262,14 @@ def main():
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t[0])
 
+    def min_over_ranks(x):
+        if dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return float(t[0])
+
     def launches():
         c = ctypes.c_ulonglong()
         _lib.check(lib.ng_launch_count(ctypes.byref(c)))
@@ -270,14 +278,24 @@ def main():
     sampler = ClockSampler(local_rank) if rank == 0 else None
 
     # ---- device-resident measurement ------------------------------------------------------
-    # On one GPU the step is recorded once per input buffer and replayed (one host call per step
-    # instead of ~36 launches); with several GPUs the all-reduce stays a live NCCL call.
-    replay = comm is None and not args.no_replay
+    # The step is recorded once per input buffer and replayed (one host call per step instead of
+    # ~33 launches); with several GPUs the per-layer NCCL all-reduces are part of the recording.
+    replay = not args.no_replay
     for _ in range(max(args.warmup, 3)):
         stack.step()
     step_fn = stack.step
     if replay:
-        stack.record_steps()
+        ok = 1
+        try:
+            stack.record_steps()
+        except _lib.NervanaError as exc:
+            sys.stderr.write("recording the step failed (%s): launching kernel by kernel\n" % exc)
+            ok = 0
+        # every rank must take the same route
+        replay = min_over_ranks(ok) == 1
+        if not replay:
+            stack._recorded = None
+    if replay:
         step_fn = stack.step_prefetched          # nothing prefetched yet: replays on the resident input
         step_fn()
     barrier()

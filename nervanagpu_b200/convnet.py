@@ -112,6 +112,7 @@ class ConvStack(object):
         # backend's own: work on the default stream would serialise with it anyway)
         self.overlap_update = ng.stream is not None
         self._side, self._side_busy = None, False
+        self._comm_stream, self._comm_busy = None, False
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)
@@ -162,6 +163,10 @@ class ConvStack(object):
                         ng.update_conv(l, x, grad, l.updat_out)
                     finally:
                         ng.stream = main
+                    if self.comm is not None:
+                        # this layer's gradient is summed over the GPUs while the layers below
+                        # are still computing (a third stream: the sum must not hold up the updates)
+                        self._allreduce_behind(side, l.updat_out)
                 else:
                     self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
             else:
@@ -172,10 +177,23 @@ class ConvStack(object):
                           ng.bprop_pool(l, x, grad, dx, relu_mask=fuse, argmax=a))
                 masked = fuse
             grad = dx
+        summed = self._comm_busy          # per-layer sums were queued behind the updates
         self._join_side()
-        if self.comm is not None:
+        if self.comm is not None and not summed:
             self._run("allreduce_dW", None, self.allreduce_grads)
         self._run("grad_descent", None, self.grad_descent)
+
+    def _allreduce_behind(self, after_stream, grad):
+        lib = self.ng.lib
+        if self._comm_stream is None:
+            self._comm_stream = self.ng.new_stream()
+            self._comm_ev, self._comm_done = ctypes.c_void_p(), ctypes.c_void_p()
+            _lib.check(lib.ng_event_create(ctypes.byref(self._comm_ev)))
+            _lib.check(lib.ng_event_create(ctypes.byref(self._comm_done)))
+        _lib.check(lib.ng_event_record(self._comm_ev, after_stream))
+        _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._comm_ev))
+        _lib.check(lib.ng_comm_allreduce_f32(self.comm, grad.ptr, grad.size, self._comm_stream))
+        self._comm_busy = True
 
     def _fork_side(self):
         """The side stream, made to wait for everything queued on the main stream so far."""
@@ -196,6 +214,11 @@ class ConvStack(object):
             _lib.check(lib.ng_event_record(self._join_ev, self._side))
             _lib.check(lib.ng_stream_wait_event(self.ng.stream, self._join_ev))
             self._side_busy = False
+        if self._comm_busy:
+            lib = self.ng.lib
+            _lib.check(lib.ng_event_record(self._comm_done, self._comm_stream))
+            _lib.check(lib.ng_stream_wait_event(self.ng.stream, self._comm_done))
+            self._comm_busy = False
 
     def allreduce_grads(self):
         _lib.check(self.ng.lib.ng_comm_allreduce_f32(self.comm, self.grads_flat.ptr, self.grads_flat.size,
@@ -228,9 +251,8 @@ class ConvStack(object):
     def record_steps(self):
         """Record one step per input buffer (the live one and the prefetch spare); step_prefetched
         then replays the recording that reads the buffer it swapped in. step() must have run before.
-        Single GPU only: the all-reduce of a multi-GPU step stays a live call."""
-        if self.comm is not None:
-            raise ValueError("recorded steps are limited to single-GPU stacks")
+        With several GPUs the NCCL all-reduces are part of the recording (every rank must record
+        and replay the same sequence)."""
         if not hasattr(self, "_copy_stream"):
             self._init_prefetch()
         probe, self.probe = self.probe, None
