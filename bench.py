@@ -320,13 +320,40 @@ def main():
     ctypes.memmove(pin_in.value, stack.host_input.ctypes.data, in_bytes)
 
     # Every step copies its own minibatch from pinned host memory and returns its last activation
-    # to the host. The copy of minibatch i+1 runs on a second stream while step i computes
-    # (ConvStack.prefetch_input / step_prefetched); the read-back is waited for every step.
+    # to the host. Both copies are pipelined, as a training loop does it: the copy of minibatch i+1
+    # runs on a second stream while step i computes (ConvStack.prefetch_input / step_prefetched),
+    # the result of step i is read back on a third stream while step i+1 computes, and the host
+    # takes delivery of it (waits for that copy) one step later. The host is never more than one
+    # step ahead of the device, and all K reads have completed when the timed region ends.
+    pin_out_b = ctypes.c_void_p()
+    _lib.check(lib.ng_host_alloc(ctypes.byref(pin_out_b), out_bytes))
+    pin_outs = [pin_out, pin_out_b]
+    read_stream = ng.new_stream()
+    ev_step = ctypes.c_void_p()
+    _lib.check(lib.ng_event_create(ctypes.byref(ev_step)))
+    ev_read = [ctypes.c_void_p(), ctypes.c_void_p()]
+    for ev in ev_read:
+        _lib.check(lib.ng_event_create(ctypes.byref(ev)))
+    e2e_count = [0]
+
+    stage = [ng.empty(out_t.shape, dtype=np.float16), ng.empty(out_t.shape, dtype=np.float16)]
+
     def e2e_step():
+        i = e2e_count[0]
         stack.step_prefetched()                      # waits (on the device) for its minibatch
         stack.prefetch_input(pin_in)                 # next minibatch, overlapped with this step
-        _lib.check(lib.ng_memcpy_d2h_async(pin_out, out_t.ptr, out_bytes, ng.stream))
-        _lib.check(lib.ng_stream_sync(ng.stream))
+        # the result leaves through one of two device staging buffers, so that the next step
+        # (which overwrites the activation) does not have to wait for the copy to the host
+        if i > 1:
+            _lib.check(lib.ng_stream_wait_event(ng.stream, ev_read[i % 2]))   # read of step i-2: long done
+        _lib.check(lib.ng_memcpy_d2d_async(stage[i % 2].ptr, out_t.ptr, out_bytes, ng.stream))
+        _lib.check(lib.ng_event_record(ev_step, ng.stream))
+        _lib.check(lib.ng_stream_wait_event(read_stream, ev_step))
+        _lib.check(lib.ng_memcpy_d2h_async(pin_outs[i % 2], stage[i % 2].ptr, out_bytes, read_stream))
+        _lib.check(lib.ng_event_record(ev_read[i % 2], read_stream))
+        if i > 0:     # delivery of the previous step's result
+            _lib.check(lib.ng_event_sync(ev_read[(i - 1) % 2]))
+        e2e_count[0] = i + 1
 
     stack.prefetch_input(pin_in)
     for _ in range(3):

@@ -471,6 +471,45 @@ int grid_for(long long total, const DeviceCtx* c) {
   return static_cast<int>(std::max<long long>(1, std::min<long long>(blocks, c->sm_count * 32ll)));
 }
 
+// Backward pass when the windows tile the input exactly (no padding, stride == window and the
+// extents divisible, in all four pooled dimensions): one thread per window and vector of images
+// reads the window once, finds its first maximum and writes every input of the window (the error
+// at the maximum, zero elsewhere). One pass, no scratch, each byte moved once.
+template <typename T, int V>
+__global__ void pool_bprop_tiled_kernel(PoolGeo g, const T* __restrict__ I, const T* __restrict__ E,
+                                        T* __restrict__ dI, int mask_pos) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.K * g.M * g.P * g.Q * nvec;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int q = r % g.Q; r /= g.Q;
+    const int p = r % g.P; r /= g.P;
+    const int m = r % g.M; r /= g.M;
+    const int k = static_cast<int>(r);
+    float best[V];
+    int arg[V];
+    window_max<T, V>(g, I, k, m, p, q, nv, best, arg);
+    const Vec<T, V> e = *reinterpret_cast<const Vec<T, V>*>(E + i * V);
+    for (int j = 0; j < g.J; ++j)
+      for (int t = 0; t < g.T; ++t)
+        for (int rr = 0; rr < g.R; ++rr)
+          for (int s = 0; s < g.S; ++s) {
+            const int flat = (((k * g.J + j) * g.D + m * g.T + t) * g.H + p * g.R + rr) * g.W + q * g.S + s;
+            Vec<T, V> out;
+#pragma unroll
+            for (int l = 0; l < V; ++l)
+              out.set(l, (arg[l] == flat && !(mask_pos && !(best[l] > 0.0f))) ? e.get(l) : 0.0f);
+            *reinterpret_cast<Vec<T, V>*>(dI + (1ll * flat * g.N + nv * V)) = out;
+          }
+  }
+}
+
+bool tiles_exactly(const PoolGeo& g) {
+  return g.pad_j == 0 && g.pad_d == 0 && g.pad_h == 0 && g.pad_w == 0 && g.str_j == g.J && g.str_d == g.T &&
+         g.str_h == g.R && g.str_w == g.S && g.C % g.J == 0 && g.D % g.T == 0 && g.H % g.R == 0 && g.W % g.S == 0;
+}
+
 template <typename T, int VW>
 int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, DeviceCtx* c,
              cudaStream_t stream) {
@@ -489,6 +528,16 @@ int run_pool(const PoolGeo& g, const void* I, const void* EO, void* out, int mod
   if (sizeof(T) == 2) {
     const int rc = try_pool2d(g, I, EO, out, mode, arg_ws, stream);
     if (rc <= 0) return rc;
+  }
+  if (mode != 0 && tiles_exactly(g)) {
+    if (vec)
+      pool_bprop_tiled_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(
+          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out), mode == 2);
+    else
+      pool_bprop_tiled_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(
+          g, static_cast<const T*>(I), static_cast<const T*>(EO), static_cast<T*>(out), mode == 2);
+    NG_CHECK_LAUNCH();
+    return NG_OK;
   }
   if (mode == 0) {
     T* O = static_cast<T*>(const_cast<void*>(EO));
