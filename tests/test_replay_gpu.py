@@ -118,3 +118,17 @@ def test_recorded_training_step_equals_live_step():
     w_rec, act_rec = run(True)
     assert np.array_equal(w_live, w_rec)
     assert np.array_equal(act_live, act_rec)
+
+
+def test_network_driver_runs_a_small_network_through_the_layer_classes():
+    from nervanagpu_b200 import convnet_benchmarks as cb
+    cb.NETWORKS["tiny"] = (1, [cb._data(64, 3, 20), cb._conv(32, 3, pad=1), cb._pool(2, 2), cb._conv(64, 3, pad=1),
+                               cb._pool(2, 2), cb._full(96), cb._full(40)])
+    lines = []
+    try:
+        res = cb.run_network(NervanaGPU(stochastic_round=False), "tiny", loops=2, out=lines.append)
+    finally:
+        del cb.NETWORKS["tiny"]
+    assert set(res) == {"fprop", "bprop", "total"}
+    assert all(ms > 0 and gflops > 0 for ms, gflops in res.values())
+    assert sum(l.startswith("Avg(2)") for l in lines) == 3
