@@ -188,7 +188,7 @@ __global__ void pool_gather_kernel(PoolGeo g, const int* __restrict__ arg, const
 
 // ------------------------------------------------------------------------------------------
 // Specialised 2-D windows (J = T = 1, no padding, fp16, N % 8 == 0): compile-time R,S and strides,
-// grid (x: q|block column and image lane, y: p|block row, z: channel) so no index division.
+// grid (x: pixel of the plane and image lane, y: channel): two index divisions per thread.
 // ------------------------------------------------------------------------------------------
 struct Lanes8 {
   float v[8];
@@ -219,18 +219,28 @@ __device__ __forceinline__ void window2d(const __half* __restrict__ plane, int H
                                          float (&best)[8], int (&arg)[8]) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) { best[i] = -FLT_MAX; arg[i] = 0; }
+  // all taps are requested before the first compare, so that R*S loads are in flight per thread
+  uint4 raw[R * S];
+  bool ok[R * S];
 #pragma unroll
   for (int r = 0; r < R; ++r) {
-    const int y = p * SH + r;
-    if (y >= H) break;
 #pragma unroll
     for (int s = 0; s < S; ++s) {
-      const int x = q * SW + s;
-      if (x >= W) break;
-      const Lanes8 t = load8(plane + (static_cast<long long>(y) * W + x) * N + n0);
+      const int y = p * SH + r, x = q * SW + s;
+      ok[r * S + s] = y < H && x < W;
+      raw[r * S + s] = make_uint4(0, 0, 0, 0);
+      if (ok[r * S + s]) raw[r * S + s] = __ldg(reinterpret_cast<const uint4*>(plane + (static_cast<long long>(y) * W + x) * N + n0));
+    }
+  }
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (t.v[i] > best[i]) { best[i] = t.v[i]; arg[i] = r * S + s; }
+  for (int k = 0; k < R * S; ++k) {
+    if (!ok[k]) continue;
+    const __half2* h = reinterpret_cast<const __half2*>(&raw[k]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __half22float2(h[i]);
+      if (f.x > best[2 * i]) { best[2 * i] = f.x; arg[2 * i] = k; }
+      if (f.y > best[2 * i + 1]) { best[2 * i + 1] = f.y; arg[2 * i + 1] = k; }
     }
   }
 }
@@ -239,12 +249,15 @@ template <int R, int S, int SH, int SW>
 __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restrict__ I, __half* __restrict__ O,
                                                           uint8_t* __restrict__ arg_out, int H, int W, int N,
                                                           int P, int Q, int mask_pos) {
+  // one thread per output pixel and vector of 8 images; x walks (p, q, lane) of one channel plane
+  // so that no thread of a block is idle whatever Q is
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int q = t / nvec;
-  if (q >= Q) return;
-  const int n0 = (t - q * nvec) << 3;
-  const int p = blockIdx.y, c = blockIdx.z;
+  if (t >= P * Q * nvec) return;
+  const int pq = t / nvec;
+  const int n0 = (t - pq * nvec) << 3;
+  const int p = pq / Q, q = pq - p * Q;
+  const int c = blockIdx.y;
   float best[8];
   int arg[8];
   window2d<R, S, SH, SW>(I + static_cast<long long>(c) * H * W * N, H, W, N, p, q, n0, best, arg);
@@ -278,10 +291,12 @@ __global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __res
   constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int b = t / nvec;
-  if (b >= BW) return;
-  const int n0 = (t - b * nvec) << 3;
-  const int a = blockIdx.y, c = blockIdx.z;
+  const int BH = (H + SH - 1) / SH;
+  if (t >= BH * BW * nvec) return;
+  const int ab = t / nvec;
+  const int n0 = (t - ab * nvec) << 3;
+  const int a = ab / BW, b = ab - a * BW;
+  const int c = blockIdx.y;
   float acc[SH][SW][8];
 #pragma unroll
   for (int dy = 0; dy < SH; ++dy)
@@ -345,10 +360,12 @@ __global__ void __launch_bounds__(256) pool2d_bprop_kernel(const __half* __restr
   constexpr int WP = (R + SH - 1) / SH, WQ = (S + SW - 1) / SW;
   const int nvec = N >> 3;
   const int t = blockIdx.x * blockDim.x + threadIdx.x;
-  const int b = t / nvec;
-  if (b >= BW) return;
-  const int n0 = (t - b * nvec) << 3;
-  const int a = blockIdx.y, c = blockIdx.z;
+  const int BH = (H + SH - 1) / SH;
+  if (t >= BH * BW * nvec) return;
+  const int ab = t / nvec;
+  const int n0 = (t - ab * nvec) << 3;
+  const int a = ab / BW, b = ab - a * BW;
+  const int c = blockIdx.y;
   const __half* plane = I + static_cast<long long>(c) * H * W * N;
   float acc[SH][SW][8];
 #pragma unroll
@@ -409,7 +426,7 @@ template <int R, int S, int SH, int SW>
 int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, int mode, int* arg_ws,
                   cudaStream_t stream) {
   const int nvec = g.N / 8;
-  dim3 fgrid((g.Q * nvec + 255) / 256, g.P, g.C);
+  dim3 fgrid((g.P * g.Q * nvec + 255) / 256, g.C);
   if (mode == 0) {
     pool2d_fprop_kernel<R, S, SH, SW><<<fgrid, 256, 0, stream>>>(
         static_cast<const __half*>(I), static_cast<__half*>(const_cast<void*>(EO)), nullptr, g.H, g.W, g.N, g.P, g.Q, 0);
@@ -424,7 +441,7 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
   } else if (mode == 4 || mode == 5) {
     // backward pass from a recorded argmax; mode 5 also applies the ReLU mask of the layer below
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
-    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    dim3 grid((BH * BW * nvec + 255) / 256, g.C);
     pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
         reinterpret_cast<const uint8_t*>(arg_ws), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W,
         g.N, g.P, g.Q, BW, mode == 5 ? 0xffffffffu : 0x7f7f7f7fu);
@@ -432,7 +449,7 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
   } else if (R <= SH && S <= SW) {
     // windows do not overlap: one pass, each block of inputs sees at most one window
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
-    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    dim3 grid((BH * BW * nvec + 255) / 256, g.C);
     pool2d_bprop_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(
         static_cast<const __half*>(I), static_cast<const __half*>(EO), static_cast<__half*>(out), g.H, g.W, g.N, g.P,
         g.Q, BW, mode == 2);
@@ -443,7 +460,7 @@ int launch_pool2d(const PoolGeo& g, const void* I, const void* EO, void* out, in
                                                                 g.W, g.N, g.P, g.Q, mode == 2);
     NG_CHECK_LAUNCH();
     const int BH = (g.H + SH - 1) / SH, BW = (g.W + SW - 1) / SW;
-    dim3 grid((BW * nvec + 255) / 256, BH, g.C);
+    dim3 grid((BH * BW * nvec + 255) / 256, g.C);
     pool2d_gather_kernel<R, S, SH, SW><<<grid, 256, 0, stream>>>(arg8, static_cast<const __half*>(EO),
                                                                  static_cast<__half*>(out), g.H, g.W, g.N, g.P, g.Q, BW,
                                                                  0xffffffffu);
