@@ -290,9 +290,15 @@ void set_update_groups(TcParams& p, int taps, int a_rows) {
   int g = std::min(std::min(8, 512 / p.block_n), accs);
   if (cap) g = std::max(1, std::min(g, atoi(cap)));
   const int ring = 232448 - 1024 - 512 - static_cast<int>(kEpiStageBytes) - kTileM * 128;
-  while (g > 1 && ((g * t * a_rows * 128 + p.block_n * 128) * 4 > ring || g * t > 24)) --g;
-  p.nz = (accs + g - 1) / g;
-  p.acc_groups = (accs + p.nz - 1) / p.nz;
+  static const char* min_stages_env = getenv("NG_UPDATE_MIN_STAGES");
+  const int min_stages = min_stages_env ? std::max(2, atoi(min_stages_env)) : 3;
+  while (g > 1 && ((g * t * a_rows * 128 + p.block_n * 128) * min_stages > ring || g * t > 24)) --g;
+  // the taps (not the accumulators) are spread evenly over the work items: 9 taps on items of at
+  // most 6 become 5 + 4, not 6 + 3
+  const int nz = (accs + g - 1) / g;
+  p.taps_per_z = (taps + nz - 1) / nz;
+  p.nz = (taps + p.taps_per_z - 1) / p.taps_per_z;
+  p.acc_groups = (p.taps_per_z + t - 1) / t;
   p.acc_taps = t;
   p.pack_rows = a_rows;
   p.nz_out = taps;

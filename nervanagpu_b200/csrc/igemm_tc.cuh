@@ -37,6 +37,8 @@ struct TcParams {
                        // `pack_rows` rows: t * pack_rows <= 128), so that a tap with few rows does
                        // not cost a whole 128-row MMA; 1 otherwise
   int pack_rows;       // rows per stacked tap (= rows of one A box)
+  int taps_per_z;      // weight update with groups / stacking: work item z owns output slices
+                       // [z * taps_per_z, (z + 1) * taps_per_z), at most acc_groups * acc_taps of them
   int nz_out;          // number of output slices (= nz unless taps are grouped or stacked, then
                        // nz = ceil(nz_out / (acc_groups * acc_taps)))
   int M, N;            // logical output extent (rows, cols)

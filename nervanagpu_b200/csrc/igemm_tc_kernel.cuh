@@ -213,11 +213,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         wk.rc = it.kb0 - wk.trs * p.red_chunks;
         wk.tap = decode_tap(p, wk.trs);
       } else if (p.mode == TC_UPDATE) {
-        // with several accumulators per item, A box `bi` belongs to tap it.z * groups + bi
-        // (and with several taps stacked in one accumulator, to tap it.z * groups * taps + bi)
-        const int zt = it.z * p.acc_groups * p.acc_taps + (is_a ? bi : 0);
+        // item z owns taps [z * taps_per_z, (z + 1) * taps_per_z); A box `bi` carries the bi-th of them
+        // (acc_taps consecutive boxes stack into one accumulator)
+        const int zt = it.z * p.taps_per_z + (is_a ? bi : 0);
         wk.tap = decode_tap(p, zt);
-        tap_live = zt < p.nz_out;
+        tap_live = zt < p.nz_out && (!is_a || bi < p.taps_per_z);
         wk.cp = decode_chunk(p, it.kb0);
       }
       // box coordinates of this lane's box at walker position `s`
@@ -344,8 +344,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         // rows of the second half that lie beyond M need no MMAs; taps beyond the last need none
         int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
         if (grouped) {
-          const int taps_left = p.nz_out - it.z * p.acc_groups * p.acc_taps;
-          halves = min(p.acc_groups, (taps_left + p.acc_taps - 1) / p.acc_taps);
+          const int taps_here = min(p.taps_per_z, p.nz_out - it.z * p.taps_per_z);
+          halves = min(p.acc_groups, (taps_here + p.acc_taps - 1) / p.acc_taps);
         }
         if (!wide) {
           if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
@@ -430,22 +430,27 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         int zt = it.z, row = rt * kTileM + lane_group * 32 + lane, row0 = rt * kTileM + lane_group * 32;
         int zt_warp = it.z;               // slice of this warp's first lane (bulk-store path)
         bool row_ok = row < p.M;
+        int acc_first = zt;               // first slice of this accumulator
+        int z_end = p.nz_out;             // one past the last slice this work item owns
         if (grouped) {
-          const int first = (it.z * p.acc_groups + h) * p.acc_taps;
-          zt = zt_warp = first;
+          acc_first = it.z * p.taps_per_z + h * p.acc_taps;
+          z_end = min(p.nz_out, (it.z + 1) * p.taps_per_z);
+          zt = acc_first;
+          zt_warp = acc_first < z_end ? acc_first : p.nz_out;
+          row_ok = row_ok && acc_first < z_end;
           if (p.acc_taps > 1) {
             const int r = lane_group * 32 + lane;
             const int sub = r / p.pack_rows;
             row = r - sub * p.pack_rows;
-            zt = first + sub;
-            row_ok = sub < p.acc_taps && row < p.M && zt < p.nz_out;
+            zt = acc_first + sub;
+            row_ok = sub < p.acc_taps && row < p.M && zt < z_end;
             const int sub_w = (lane_group * 32) / p.pack_rows;
             row0 = lane_group * 32 - sub_w * p.pack_rows;
-            zt_warp = sub_w < p.acc_taps ? first + sub_w : p.nz_out;
+            zt_warp = (sub_w < p.acc_taps && acc_first + sub_w < z_end) ? acc_first + sub_w : p.nz_out;
           }
         }
         // whole accumulator beyond M (or beyond the last tap): nothing accumulated, nothing to store
-        const bool half_live = rt * kTileM < p.M && (grouped ? (it.z * p.acc_groups + h) * p.acc_taps : zt) < p.nz_out;
+        const bool half_live = rt * kTileM < p.M && acc_first < z_end;
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
         // row base pointers

@@ -256,8 +256,10 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   if (p.acc_groups < 1) p.acc_groups = 1;
   if (p.acc_taps < 1) p.acc_taps = 1;
   if (p.nz_out < 1) p.nz_out = p.nz;
+  if (p.taps_per_z < 1) p.taps_per_z = p.acc_groups * p.acc_taps;
   if ((p.acc_groups > 1 || p.acc_taps > 1) &&
       (p.m_halves != 1 || p.tiles_m != 1 || p.acc_groups * p.block_n > 512 ||
+       p.taps_per_z > p.acc_groups * p.acc_taps || static_cast<long long>(p.nz) * p.taps_per_z < p.nz_out ||
        (p.acc_taps > 1 && (p.pack_rows < 8 || p.acc_taps * p.pack_rows > kTileM)))) {
     return fail(NG_ERR_INVALID_ARG, "internal: grouped accumulators do not fit tensor memory");
   }
