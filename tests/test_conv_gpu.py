@@ -166,6 +166,39 @@ def test_full_size_alexnet_layer_properties(ng):
         assert_close(outs[0][:, 0, p, q, :], ref, rn16_tol(ref, absd, cd.C * 9), "pixel %d,%d" % (p, q))
 
 
+FULL_SIZE = {
+    # BASELINE configs at their real sizes: (N, C, K, D, H, W, T, R, S, pads, strides)
+    "alexnet_conv1_tap_blocks": (128, 3, 64, 1, 224, 224, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    "alexnet_conv2_stacked_update": (128, 64, 192, 1, 27, 27, 1, 5, 5, 0, 2, 2, 1, 1, 1),
+    "vgg_conv4_256_rows": (64, 256, 256, 1, 56, 56, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "config5_3d_conv": (32, 64, 64, 16, 56, 56, 3, 3, 3, 1, 1, 1, 1, 1, 1),
+}
+
+
+@pytest.mark.parametrize("name", sorted(FULL_SIZE))
+def test_full_size_adjoint_identity(ng, name):
+    """At full size the three passes are checked against each other: they are the three partial
+    derivatives of one bilinear form, so <fprop(I, F), E> = <I, bprop(F, E)> = <F, update(I, E)>."""
+    cfg = FULL_SIZE[name]
+    cd = rm.ConvDims(*cfg)
+    rng = np.random.default_rng(1004)
+    I = rng.uniform(0, 1, cd.dimI).astype(np.float16)
+    F = rng.normal(0, 0.05, cd.dimF).astype(np.float16)
+    E = (rng.uniform(-1, 1, cd.dimO) * 0.125).astype(np.float16)
+    got = _run_all(ng, _layer(ng, cfg), I, F, E)
+    f64 = np.float64
+    via_fprop = np.sum(got["O"].astype(f64) * E.astype(f64))
+    via_bprop = np.sum(got["gradI"].astype(f64) * I.astype(f64))
+    via_update = np.sum(got["gradF"].astype(f64) * F.astype(f64))
+    scale = np.sum(np.abs(got["O"].astype(f64)) * np.abs(E.astype(f64)))
+    assert np.isfinite([via_fprop, via_bprop, via_update]).all() and scale > 0
+    # fp16 rounding of O and gradI: relative 2^-11 per element, random in sign; a dropped tap or a
+    # misplaced tile would show at the percent level
+    assert abs(via_fprop - via_update) <= 1e-3 * scale, (via_fprop, via_update, scale)
+    assert abs(via_fprop - via_bprop) <= 1e-3 * scale, (via_fprop, via_bprop, scale)
+    assert abs(via_bprop - via_update) <= 1e-3 * scale, (via_bprop, via_update, scale)
+
+
 def test_layer_argument_checks(ng):
     with pytest.raises(AssertionError):
         ng.conv_layer(np.float16, 12, 3, 8, 1, 8, 8, 1, 3, 3)       # N % 8
