@@ -258,23 +258,55 @@ __global__ void __launch_bounds__(256) pool2d_fprop_kernel(const __half* __restr
   const int n0 = (t - pq * nvec) << 3;
   const int p = pq / Q, q = pq - p * Q;
   const int c = blockIdx.y;
-  float best[8];
-  int arg[8];
-  window2d<R, S, SH, SW>(I + static_cast<long long>(c) * H * W * N, H, W, N, p, q, n0, best, arg);
+  const __half* plane = I + static_cast<long long>(c) * H * W * N;
+  // All taps are requested before the first compare. The compares stay in fp16 (the inputs are
+  // fp16, so the order is the same as in fp32) on packed pairs: a mask per pair says which of
+  // the two running maxima a tap beats, and maxima and tap numbers are merged under that mask;
+  // three instructions per pair and tap instead of converting every value to fp32.
+  uint4 raw[R * S];
+  bool ok[R * S];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+      const int y = p * SH + r, x = q * SW + s;
+      ok[r * S + s] = y < H && x < W;
+      raw[r * S + s] = make_uint4(0, 0, 0, 0);
+      if (ok[r * S + s])
+        raw[r * S + s] = __ldg(reinterpret_cast<const uint4*>(plane + (static_cast<long long>(y) * W + x) * N + n0));
+    }
+  }
+  uint32_t best[4], arg[4];   // two fp16 maxima / two 16-bit tap numbers per word
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { best[i] = 0xfc00fc00u; arg[i] = 0u; }   // -inf, tap 0
+#pragma unroll
+  for (int k = 0; k < R * S; ++k) {
+    if (!ok[k]) continue;
+    const uint32_t w[4] = {raw[k].x, raw[k].y, raw[k].z, raw[k].w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t m = __hgt2_mask(*reinterpret_cast<const __half2*>(&w[i]), *reinterpret_cast<const __half2*>(&best[i]));
+      best[i] = (w[i] & m) | (best[i] & ~m);
+      arg[i] = ((static_cast<uint32_t>(k) * 0x00010001u) & m) | (arg[i] & ~m);
+    }
+  }
   const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
-  if (O) store8(O + o, best);
+  if (O) *reinterpret_cast<uint4*>(O + o) = make_uint4(best[0], best[1], best[2], best[3]);
   if (arg_out) {
     // one byte per output: the tap (r*S + s) of the first maximum. mask_pos 1: a window whose
     // maximum is not positive names no tap (its error is dropped); mask_pos 2: such windows are
     // flagged in bit 7 and the backward pass decides whether the flag counts.
     if (mask_pos) {
+      const uint32_t zero2 = 0u;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        if (!(best[i] > 0.0f)) arg[i] = mask_pos == 1 ? 255 : (arg[i] | 0x80);
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t pos = __hgt2_mask(*reinterpret_cast<const __half2*>(&best[i]), *reinterpret_cast<const __half2*>(&zero2));
+        arg[i] = mask_pos == 1 ? ((arg[i] & pos) | (0x00ff00ffu & ~pos)) : (arg[i] | (0x00800080u & ~pos));
+      }
     }
     uint2 packed;
-    packed.x = arg[0] | (arg[1] << 8) | (arg[2] << 16) | (arg[3] << 24);
-    packed.y = arg[4] | (arg[5] << 8) | (arg[6] << 16) | (arg[7] << 24);
+    packed.x = __byte_perm(arg[0], arg[1], 0x6420);   // low byte of each 16-bit tap number
+    packed.y = __byte_perm(arg[2], arg[3], 0x6420);
     *reinterpret_cast<uint2*>(arg_out + o) = packed;
   }
 }
