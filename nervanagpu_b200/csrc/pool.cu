@@ -336,23 +336,48 @@ __global__ void __launch_bounds__(256) pool2d_gather_kernel(const uint8_t* __res
     for (int dx = 0; dx < SW; ++dx)
 #pragma unroll
       for (int i = 0; i < 8; ++i) acc[dy][dx][i] = 0.0f;
+  // the records and errors of all overlapping windows are requested before any is used
+  uint2 rec[WP * WQ];
+  uint4 err[WP * WQ];
+  bool live[WP * WQ];
 #pragma unroll
   for (int wp = 0; wp < WP; ++wp) {
-    const int p = a - (WP - 1) + wp;
-    if (p < 0 || p >= P) continue;
 #pragma unroll
     for (int wq = 0; wq < WQ; ++wq) {
-      const int q = b - (WQ - 1) + wq;
-      if (q < 0 || q >= Q) continue;
-      const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
-      uint2 pk = *reinterpret_cast<const uint2*>(arg + o);
+      const int p = a - (WP - 1) + wp, q = b - (WQ - 1) + wq;
+      const int w = wp * WQ + wq;
+      live[w] = p >= 0 && p < P && q >= 0 && q < Q;
+      rec[w] = make_uint2(0xffffffffu, 0xffffffffu);
+      err[w] = make_uint4(0, 0, 0, 0);
+      if (live[w]) {
+        const long long o = ((static_cast<long long>(c) * P + p) * Q + q) * N + n0;
+        rec[w] = __ldg(reinterpret_cast<const uint2*>(arg + o));
+        err[w] = __ldg(reinterpret_cast<const uint4*>(E + o));
+      }
+    }
+  }
+#pragma unroll
+  for (int wp = 0; wp < WP; ++wp) {
+#pragma unroll
+    for (int wq = 0; wq < WQ; ++wq) {
+      if (!live[wp * WQ + wq]) continue;
+      uint2 pk = rec[wp * WQ + wq];
       pk.x &= byte_and;
       pk.y &= byte_and;
       const int idx[8] = {static_cast<int>(pk.x & 255u), static_cast<int>((pk.x >> 8) & 255u),
                           static_cast<int>((pk.x >> 16) & 255u), static_cast<int>(pk.x >> 24),
                           static_cast<int>(pk.y & 255u), static_cast<int>((pk.y >> 8) & 255u),
                           static_cast<int>((pk.y >> 16) & 255u), static_cast<int>(pk.y >> 24)};
-      const Lanes8 e = load8(E + o);
+      Lanes8 e;
+      {
+        const __half2* h = reinterpret_cast<const __half2*>(&err[wp * WQ + wq]);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const float2 f = __half22float2(h[i]);
+          e.v[2 * i] = f.x;
+          e.v[2 * i + 1] = f.y;
+        }
+      }
 #pragma unroll
       for (int dy = 0; dy < SH; ++dy) {
         const int r = (WP - 1 - wp) * SH + dy;     // tap row of block input dy inside window p
