@@ -10,8 +10,8 @@ timed with events. Output lines have the reference's form ("Avg(10) fprop: ... m
 flops per layer from Layer.flops with the backward pass counted twice.
 
 Networks: the convolution/pooling/fully-connected stacks of AlexNet (one-column variant), Overfeat
-(fast), VGG model A and VGG model E as the public convnet-benchmarks lists them, fp16 only (fp32
-layers are outside this library). The per-layer grid hints of the reference's tables tuned its
+(fast), VGG model A and VGG model E as the public convnet-benchmarks lists them, and GoogLeNet (v1,
+nine Inception modules), fp16 only (fp32 layers are outside this library). The per-layer grid hints of the reference's tables tuned its
 Maxwell kernels and have no meaning here.
 """
 import argparse
@@ -20,7 +20,7 @@ import ctypes
 import numpy as np
 
 from . import NervanaGPU, _lib
-from .layers import ConvLayer, DataLayer, FullLayer, Layer, PoolLayer
+from .layers import ConvLayer, DataLayer, FullLayer, Inception, Layer, PoolLayer
 
 
 def _conv(K, R, pad=0, stride=1):
@@ -37,6 +37,22 @@ def _full(n_out):
 
 def _data(N, C, H):
     return {"layer": DataLayer, "N": N, "C": C, "H": H, "W": H}
+
+
+def _inception(n1x1, red3, n3x3, red5, n5x5, proj):
+    """GoogLeNet module: 1x1 | 1x1 -> 3x3 | 1x1 -> 5x5 | 3x3 max-pool (stride 1) -> 1x1."""
+    pool = dict(_pool(3, 1), pad_h=1, pad_w=1)
+    return {"layer": Inception, "partitions": [
+        [_conv(n1x1, 1)],
+        [_conv(red3, 1), _conv(n3x3, 3, pad=1)],
+        [_conv(red5, 1), _conv(n5x5, 5, pad=2)],
+        [pool, _conv(proj, 1)],
+    ]}
+
+
+def _pool_same(R, stride):
+    # padded so that 112 -> 56 -> 28 -> 14 -> 7, the map sizes the published network uses
+    return dict(_pool(R, stride), pad_h=1, pad_w=1)
 
 
 _CLASSIFIER = [_full(3072), _full(3072), _full(1000)]
@@ -56,6 +72,14 @@ NETWORKS = {
                     _conv(384, 3, pad=1), _conv(256, 3, pad=1), _conv(256, 3, pad=1), _pool(3, 2)] + _CLASSIFIER),
     "Overfeat": (1, [_data(128, 3, 231), _conv(96, 11, stride=4), _pool(2, 2), _conv(256, 5), _pool(2, 2),
                      _conv(512, 3, pad=1), _conv(1024, 3, pad=1), _conv(1024, 3, pad=1), _pool(2, 2)] + _CLASSIFIER),
+    "GoogLeNet1": (1, [_data(128, 3, 224), _conv(64, 7, pad=3, stride=2), _pool_same(3, 2), _conv(64, 1),
+                       _conv(192, 3, pad=1), _pool_same(3, 2),
+                       _inception(64, 96, 128, 16, 32, 32), _inception(128, 128, 192, 32, 96, 64), _pool_same(3, 2),
+                       _inception(192, 96, 208, 16, 48, 64), _inception(160, 112, 224, 24, 64, 64),
+                       _inception(128, 128, 256, 24, 64, 64), _inception(112, 144, 288, 32, 64, 64),
+                       _inception(256, 160, 320, 32, 128, 128), _pool_same(3, 2),
+                       _inception(256, 160, 320, 32, 128, 128), _inception(384, 192, 384, 48, 128, 128),
+                       _pool(7, 1), _full(1000)]),
     "VGG": (1, _vgg([(1, 64), (1, 128), (2, 256), (2, 512), (2, 512)])),
     "VGG_E": (1, _vgg([(2, 64), (2, 128), (4, 256), (4, 512), (4, 512)])),
 }
@@ -160,7 +184,7 @@ def run_network(ng, name, loops=10, stats=False, zeros=False, out=print):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--nets", default="Alexnet,Overfeat,VGG,VGG_E")
+    ap.add_argument("--nets", default="Alexnet,Overfeat,VGG,GoogLeNet1,VGG_E")
     ap.add_argument("--loops", type=int, default=10)
     ap.add_argument("--layer-bench", action="store_true", help="print the time of every conv / pool / GEMM call")
     ap.add_argument("--stats", action="store_true", help="print activation / delta / update statistics per layer")

@@ -126,6 +126,18 @@ class Layer(object):
         N, C, H, W (or nIn) are propagated from the previous layer."""
         config = dict(conf)
         layer_type = config.pop("layer")
+        if layer_type is Inception:
+            # every branch is a chain of layers that starts on the container's input
+            partitions = []
+            for branch in config["partitions"]:
+                chain, prev = [], prev_layer
+                for inner in branch:
+                    prev = Layer.create(lib, inner, prev, dtype)
+                    chain.append(prev)
+                partitions.append(chain)
+            last = partitions[0][-1]
+            return Inception(lib, dtype, partitions, prev_layer.N, prev_layer.K, sum(p[-1].K for p in partitions),
+                             prev_layer.M, prev_layer.P, prev_layer.Q, last.M, last.P, last.Q)
         config["dtype"] = dtype
         config.update(config.pop(dtype, {}))
         config.update(config.pop("common", {}))
@@ -347,3 +359,100 @@ class PoolLayer(Layer):
     def __str__(self):
         return ("PoolLayer: NCK: (%d, %d, %d) DHW:%s JTRS:%s MPQ:%s op: %s " %
                 (self.N, self.C, self.K, self.DHW, self.JTRS, self.MPQ, self.op))
+
+
+class Inception(Layer):
+    """Parallel branches over one input whose outputs are concatenated along the feature-map
+    dimension (nervanagpu/layers.py:643-755). `partitions` is a list of branches, each a list of
+    layers already created on the container's input shape.
+
+    The output of every branch's last layer is a channel slice of the container's output, so the
+    concatenation costs nothing. On the way back each branch takes its slice of the incoming
+    deltas; the branches' input deltas are summed: the first branch writes the container's delta
+    buffer, the others write a scratch buffer that is then added to it. (The reference lets every
+    branch overwrite the same buffer and leaves the sum as a TODO, nervanagpu/layers.py:737.)
+    """
+
+    def __init__(self, lib, dtype, partitions, N, C, K, D=1, H=1, W=1, M=1, P=1, Q=1):
+        super(Inception, self).__init__(lib, dtype, N)
+        self.partitions = [list(part) for part in partitions]
+        self.C, self.K, self.M, self.P, self.Q = C, K, M, P, Q
+        self.NCK = (N, C, K)
+        self.DHW = (D, H, W)
+        self.MPQ = (M, P, Q)
+        self.dimI = (C, D, H, W, N)
+        self.dimO = (K, M, P, Q, N)
+        self.dimI2 = (C * D * H * W, N)
+        self.dimO2 = (K * M * P * Q, N)
+        self.sizeI = _prod(self.dimI)
+        self.sizeO = _prod(self.dimO)
+        self.nOut = M * P * Q * K
+        inner = [layer for part in self.partitions for layer in part]
+        assert sum(part[-1].K for part in self.partitions) == K
+        assert all(part[-1].MPQ == self.MPQ for part in self.partitions), "branches must end on one map size"
+        self.flops = sum(layer.flops for layer in inner)
+        widest = max(inner, key=lambda layer: layer.sizeF)
+        self.sizeF = widest.sizeF
+        if self.sizeF:
+            self.dimF = widest.dimF
+
+    def init_activations(self):
+        super(Inception, self).init_activations()
+        k0 = 0
+        for part in self.partitions:
+            for layer in part[:-1]:
+                layer.init_activations()
+            last = part[-1]
+            last.fprop_out = self.fprop_out[k0:k0 + last.K]
+            last.act_stats = self.lib.empty((last.dimO2[0], 1), dtype=np.float32)
+            k0 += last.K
+
+    def init_deltas(self, shared=None):
+        super(Inception, self).init_deltas(shared)
+        self._branch_delta = self.lib.empty(self.dimI, dtype=self.dtype) if len(self.partitions) > 1 else None
+        for b, part in enumerate(self.partitions):
+            part[0].bprop_out = self.bprop_out if b == 0 else self._branch_delta
+            part[0].delta_stats = self.delta_stats
+            for layer in part[1:]:
+                layer.init_deltas()
+
+    def init_weights(self, loc=0.0, scale=0.1, shared=None, zeros=False, rng=None):
+        for part in self.partitions:
+            for layer in part:
+                layer.init_weights(loc, scale, shared, zeros, rng)
+
+    def fprop(self, fprop_in, scale_weights=0):
+        fprop_in = super(Inception, self).fprop(fprop_in)
+        for part in self.partitions:
+            x = fprop_in
+            for layer in part:
+                x = layer.fprop(x, scale_weights)
+        return self.fprop_out
+
+    def bprop(self, bprop_in):
+        k0 = 0
+        for b, part in enumerate(self.partitions):
+            delta = bprop_in.reshape(self.dimO)[k0:k0 + part[-1].K]
+            k0 += part[-1].K
+            for layer in part[::-1]:
+                delta = layer.bprop(delta)
+            if b > 0 and self.bprop_out is not None:
+                self.bprop_out[:] = self.bprop_out + self._branch_delta
+        return self.bprop_out
+
+    def fprop_stats(self):
+        for part in self.partitions:
+            for layer in part:
+                layer.fprop_stats()
+
+    def bprop_stats(self):
+        for part in self.partitions[::-1]:
+            for layer in part[::-1]:
+                layer.bprop_stats()
+
+    def __str__(self):
+        lines = ["Inception: NCK: (%d, %d, %d) DHW:%s MPQ:%s" % (self.N, self.C, self.K, self.DHW, self.MPQ)]
+        for i, part in enumerate(self.partitions):
+            lines.append("  Part%d:" % (i + 1))
+            lines.extend("    %s" % layer for layer in part)
+        return "\n".join(lines)

@@ -128,3 +128,30 @@ def test_layer_create_propagates_dimensions():
     assert layers[1].dimI == (3, 1, 32, 32, 64) and layers[1].dimO == (16, 1, 32, 32, 64)
     assert layers[2].dimO == (16, 1, 16, 16, 64)
     assert layers[3].nIn == 16 * 16 * 16 and layers[3].dimF == (100, 4096)
+
+
+def test_network_tables_build_with_consistent_shapes():
+    """Every network of the whole-network driver, created through Layer.create without a device:
+    map sizes follow the published architectures and every Inception module concatenates its
+    four branches."""
+    from nervanagpu_b200 import convnet_benchmarks as cb
+    from nervanagpu_b200.layers import Inception
+    for name, (_, confs) in cb.NETWORKS.items():
+        prev, layers = None, []
+        for conf in confs:
+            prev = Layer.create(None, conf, prev, np.float16)
+            layers.append(prev)
+        assert layers[-1].nOut == 1000, name
+        for a, b in zip(layers, layers[1:]):
+            assert b.sizeI == a.sizeO, (name, str(a), str(b))
+    _, confs = cb.NETWORKS["GoogLeNet1"]
+    prev, modules = None, []
+    for conf in confs:
+        prev = Layer.create(None, conf, prev, np.float16)
+        if isinstance(prev, Inception):
+            modules.append(prev)
+    assert [m.K for m in modules] == [256, 480, 512, 512, 512, 528, 832, 832, 1024]
+    assert [m.P for m in modules] == [28, 28, 14, 14, 14, 14, 14, 7, 7]
+    first = modules[0]
+    assert [len(part) for part in first.partitions] == [1, 2, 2, 2]
+    assert first.flops == sum(l.flops for part in first.partitions for l in part) > 0
