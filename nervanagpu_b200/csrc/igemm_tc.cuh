@@ -28,6 +28,8 @@ struct TcParams {
   int tiles_m, tiles_n, nz, splits;
   int num_kb;          // k-blocks in the whole reduction
   int kb_per_split;    // ceil(num_kb / splits)
+  int full_items;      // items [0, full_items) are whole tiles; from there on, item pairs are the two
+  int total_items;     // 128-row halves of one 256-row tile (the cut last wave); all items
   int block_n;         // UMMA N: 64, 128 or 256
   int m_halves;        // 1: 128-row tiles, accumulator double-buffered across tiles
                        // 2: 256-row tiles, two accumulators that share every B operand

@@ -113,9 +113,20 @@ __device__ __forceinline__ bool div_exact(int num, int den, int& out) {
 
 struct WorkItem {
   int tile_m, tile_n, z, split, kb0, kb1;
+  int m0;     // first output row of the item
+  int live;   // 256-row tiles: accumulators (row halves) the item computes, 0 = nothing to do; else 1
 };
+// Items [0, full_items) are whole tiles. With 256-row tiles the tiles of the last, partly filled
+// wave are cut into their two 128-row halves, items full_items + 2 * t + h, so that this wave
+// takes half a tile time on twice as many SMs.
 __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
   WorkItem it;
+  int half = -1;
+  if (w >= p.full_items) {
+    const int hw = w - p.full_items;
+    w = p.full_items + (hw >> 1);
+    half = hw & 1;
+  }
   int r = fast_div(w, p.fd_tiles_m);
   it.tile_m = w - r * p.tiles_m;
   const int r2 = fast_div(r, p.fd_tiles_n);
@@ -124,6 +135,12 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
   it.z = r2 - it.split * p.nz;
   it.kb0 = it.split * p.kb_per_split;
   it.kb1 = min(p.num_kb, it.kb0 + p.kb_per_split);
+  it.m0 = it.tile_m * kTileM * p.m_halves + (half > 0 ? kTileM : 0);
+  it.live = 1;
+  if (p.m_halves == 2) {
+    it.live = half >= 0 ? 1 : (it.m0 + kTileM < p.M ? 2 : 1);
+    if (it.m0 >= p.M) it.live = 0;
+  }
   return it;
 }
 
@@ -152,7 +169,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int total_work = p.tiles_m * p.tiles_n * p.nz * p.splits;
+  const int total_work = p.total_items;   // tiles_m * tiles_n * nz * splits, plus the halves of a cut last wave
   const uint32_t tmem_cols = 512;  // 2 accumulators of up to 256 columns
 
   if (threadIdx.x == 0) {
@@ -196,8 +213,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     (void)ptile;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const WorkItem it = decode_work(p, w);
-      const int m0 = it.tile_m * kTileM * p.m_halves;
+      if (it.live == 0) continue;
+      const int m0 = it.m0;
       const int n0 = it.tile_n * p.block_n;
+      // an item that computes one half of a 256-row tile needs only that half's A boxes when they
+      // are separate boxes (MN-major A); a K-major A box always carries all its rows
+      const int a_live = (p.m_halves == 2 && it.live == 1 && p.a_mn_major) ? (p.a_boxes >> 1) : p.a_boxes;
+      const bool act = active && (!is_a || bi < a_live);
+      const uint32_t tx_item = p.tx_bytes - static_cast<uint32_t>(p.a_boxes - a_live) * p.a_box_bytes;
       // Per-tile state of this lane's box. Everything that changes from one k-block to the next
       // is kept as counters that are stepped, not re-derived: integer division by run-time
       // values costs this single warp more than the MMAs of a k-block take.
@@ -304,14 +327,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
-        if (active) coords(wk, c0, c1, c2, c3, c4);
+        if (act) coords(wk, c0, c1, c2, c3, c4);
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER);
-        if (lane == 0 && got) mbar_expect_tx(full_bar(stage), p.tx_bytes);
+        if (lane == 0 && got) mbar_expect_tx(full_bar(stage), tx_item);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
-        if (active) {
+        if (act) {
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
         if (lane == 0) {
@@ -337,12 +360,13 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
       // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
       const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x, ++local) {
+      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const WorkItem it = decode_work(p, w);
+        if (it.live == 0) continue;     // `local` counts the items this CTA works on, in every role alike
         const int acc = (wide || grouped) ? 0 : (local & 1);
         const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
         // rows of the second half that lie beyond M need no MMAs; taps beyond the last need none
-        int halves = (wide && it.tile_m * 2 * kTileM + kTileM < p.M) ? 2 : 1;
+        int halves = wide ? it.live : 1;
         if (grouped) {
           const int taps_here = min(p.taps_per_z, p.nz_out - it.z * p.taps_per_z);
           halves = min(p.acc_groups, (taps_here + p.acc_taps - 1) / p.acc_taps);
@@ -385,6 +409,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         }
         if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
         NG_STAMP(local, 4);                           // last MMA of the tile issued
+        ++local;
       }
     }
     __syncwarp();
@@ -411,8 +436,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
     const int n_acc = wide ? 2 : p.acc_groups;   // accumulators of one work item
     int local = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x, ++local) {
+    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
       const WorkItem it = decode_work(p, w);
+      if (it.live == 0) continue;
       const int acc = (wide || grouped) ? 0 : (local & 1);
       const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
@@ -426,7 +452,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       for (int h = 0; h < n_acc; ++h) {
         // accumulator h holds rows of row-tile `rt` of output slice `zt`; with stacked taps
         // (weight update, few rows per tap) every `pack_rows` lanes belong to the next slice
-        const int rt = wide ? it.tile_m * 2 + h : it.tile_m;
+        const int rt = it.m0 / kTileM + (wide ? h : 0);
         int zt = it.z, row = rt * kTileM + lane_group * 32 + lane, row0 = rt * kTileM + lane_group * 32;
         int zt_warp = it.z;               // slice of this warp's first lane (bulk-store path)
         bool row_ok = row < p.M;
@@ -450,7 +476,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           }
         }
         // whole accumulator beyond M (or beyond the last tap): nothing accumulated, nothing to store
-        const bool half_live = rt * kTileM < p.M && acc_first < z_end;
+        const bool half_live = rt * kTileM < p.M && acc_first < z_end && (!wide || h < it.live);
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(lane_group * 32) << 16) +
                                static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
         // row base pointers
@@ -656,6 +682,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         for (int k = 0; k < 4; ++k)
           p.timeline[(blockIdx.x * kTimelineTiles + local) * kTimelineSlots + 8 + k] = clk_acc[k];
 #endif
+      ++local;
     }
     // outstanding bulk stores must be complete before the CTA (and its shared memory) goes away
     if (p.tma_store && lane == 0) tma_store_wait_all();

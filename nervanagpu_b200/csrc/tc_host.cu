@@ -281,8 +281,18 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     c->smem_attr_set = true;
   }
-  const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
-  if (total > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "too many work items");
+  long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
+  if (total > 0x3fffffffll) return fail(NG_ERR_TOO_LARGE, "too many work items");
+  p.full_items = static_cast<int>(total);
+  // 256-row tiles: when the last wave fills at most half of the SMs, its tiles are handed out as
+  // 128-row halves, so that the wave takes about half a tile time on twice as many SMs
+  static const bool split_tail = !(getenv("NG_SPLIT_TAIL") && atoi(getenv("NG_SPLIT_TAIL")) == 0);
+  const long long rem = total % c->sm_count;
+  if (split_tail && p.m_halves == 2 && rem > 0 && 2 * rem <= c->sm_count) {
+    p.full_items = static_cast<int>(total - rem);
+    total += rem;
+  }
+  p.total_items = static_cast<int>(total);
   const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
   CUtensorMap mapC = mapA;   // placeholder when the bulk-store epilogue is off
   p.tma_store = pick_store_mode(&mapC, p);
@@ -488,6 +498,7 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
   p.tma_store = 0;   // this variant stores straight from registers
   p.timeline = nullptr;
+  p.full_items = p.total_items = static_cast<int>(total);
   ngb::fill_fast_divs(p);
   igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, p);
   NG_CHECK_LAUNCH();
