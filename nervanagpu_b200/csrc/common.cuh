@@ -77,13 +77,17 @@ constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
                                           int* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = global_timer_ns();
+  // The clock stays off the path of a wait that ends soon: it is first read after 1024 failed
+  // polls (each of which already blocks for a while in hardware), and the limit counts from there.
+  uint64_t t0 = 0;
   for (uint32_t it = 1;; ++it) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((it & 0x3ff) == 0) {
       if (*abort_flag) return false;
-      if (global_timer_ns() - t0 > kWaitLimitNs) {
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > kWaitLimitNs) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

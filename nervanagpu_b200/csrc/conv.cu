@@ -80,6 +80,43 @@ int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int
   return make_tensor_map(m, base, dims, str, box);
 }
 
+// Tensor map over an activation tensor whose box is a whole column tile of `nb` 64-wide chunks
+// that lie in one image row: (n, chan, x, y, z) with a box of nb pixels when a pixel is one chunk
+// (N = 64), else (n_lo, chan, n_hi, x, y) for 2-D data. The box lands in shared memory chunk by
+// chunk, each [box_chan rows][64], as the per-chunk boxes of act_map would. Returns the value for
+// TcParams::b_merge, 0 when the shape has no such map.
+int act_map_merged(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, uint32_t box_chan, int nb) {
+  static const bool off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;   // tuning aid
+  if (off || N % kChunk != 0 || nb < 2) return 0;
+  const int cpi = N / kChunk;
+  const uint64_t xn = 1ull * X * N * 2;
+  uint64_t dims[5], str[4];
+  uint32_t box[5];
+  if (cpi == 1) {
+    dims[0] = N; dims[1] = chan; dims[2] = X; dims[3] = Y; dims[4] = Z;
+    str[0] = xn * Y * Z; str[1] = 1ull * N * 2; str[2] = xn; str[3] = xn * Y;
+    box[0] = kChunk; box[1] = box_chan; box[2] = nb; box[3] = 1; box[4] = 1;
+    return make_tensor_map(m, base, dims, str, box) == NG_OK ? 1 : 0;
+  }
+  if (Z != 1 || (nb % cpi != 0 && cpi % nb != 0)) return 0;
+  dims[0] = kChunk; dims[1] = chan; dims[2] = cpi; dims[3] = X; dims[4] = Y;
+  str[0] = xn * Y; str[1] = 128; str[2] = 1ull * N * 2; str[3] = xn;
+  box[0] = kChunk; box[1] = box_chan; box[2] = std::min(cpi, nb); box[3] = std::max(1, nb / cpi); box[4] = 1;
+  return make_tensor_map(m, base, dims, str, box) == NG_OK ? 2 : 0;
+}
+
+// filter (C, TRS, K) with K a multiple of 64, seen as (k_lo, c, k_hi, trs): a box of two chunks of
+// 64 filters lands as [chunk][box_c rows][64]
+int filter_map_merged(CUtensorMap* m, const void* base, const Geo& g, uint32_t box_c) {
+  const int RST = g.T * g.R * g.S;
+  uint64_t dims[5] = {kChunk, static_cast<uint64_t>(g.C), static_cast<uint64_t>(g.K / kChunk),
+                      static_cast<uint64_t>(RST), 1};
+  uint64_t str[4];
+  str[0] = 1ull * g.K * 2 * RST; str[1] = 128; str[2] = 1ull * g.K * 2; str[3] = str[0] * g.C;
+  const uint32_t box[5] = {kChunk, box_c, 2, 1, 1};
+  return make_tensor_map(m, base, dims, str, box);
+}
+
 // tensor map over the filter (C, TRS, K) seen as (k, trs, c)
 int filter_map(CUtensorMap* m, const void* base, const Geo& g, uint32_t box_c) {
   const int RST = g.T * g.R * g.S;
@@ -107,6 +144,8 @@ void fill_decode(TcParams& p, int N, int X, int Y, int Z, ChunkMode mode) {
 }
 
 int pick_kb_rows(int C) {
+  static const char* force = getenv("NG_KB_ROWS");   // tuning aid: 16, 32, 48 or 64
+  if (force && atoi(force) >= 16 && atoi(force) <= 64 && atoi(force) % 16 == 0) return atoi(force);
   int best = 64, best_pad = ((C + 63) / 64) * 64;
   for (int r : {48, 32, 16}) {
     const int pad = ((C + r - 1) / r) * r;
@@ -399,6 +438,11 @@ int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I
   p.red_chunks = 1;
   p.num_kb = ntb;
   tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
+  // fewer, larger boxes: the filters of a 128-row half as one box (K a multiple of 64), the two
+  // image groups of a pixel as one box (N = 128, 2-D)
+  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  lay.a_merge = !merge_off && g.K % kChunk == 0;
+  lay.b_pair = !merge_off && g.N == 2 * kChunk && g.D == 1;
   tc_fill_mma(p, lay);
   fill_taps(p, g, CH_PIXEL);
   p.R = tb.nr; p.S = tb.ns; p.RS = tb.nr * tb.ns; p.tap_w = tb.bw; p.tap_h = tb.bh;
@@ -407,21 +451,109 @@ int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I
   p.C = O; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = relu; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
   CUtensorMap mapA, mapB;
-  {  // packed filter seen as (k, tap block, row)
+  {  // packed filter seen as (k, tap block, row), or as (k_lo, row, k_hi, tap block)
     uint64_t dims[5] = {static_cast<uint64_t>(g.K), static_cast<uint64_t>(ntb), static_cast<uint64_t>(tb.rows), 1, 1};
     uint64_t str[4];
     str[0] = 1ull * g.K * 2; str[1] = str[0] * ntb; str[2] = str[1] * tb.rows; str[3] = str[2];
-    const uint32_t box[5] = {kChunk, 1, static_cast<uint32_t>(tb.rows), 1, 1};
+    uint32_t box[5] = {kChunk, 1, static_cast<uint32_t>(tb.rows), 1, 1};
+    if (lay.a_merge) {
+      dims[0] = kChunk; dims[1] = tb.rows; dims[2] = g.K / kChunk; dims[3] = ntb;
+      str[0] = 1ull * g.K * 2 * ntb; str[1] = 128; str[2] = 1ull * g.K * 2; str[3] = str[0] * tb.rows;
+      box[1] = tb.rows; box[2] = 2;
+    }
     rc = make_tensor_map(&mapA, Fp, dims, str, box);
     if (rc != NG_OK) return rc;
   }
-  rc = act_map_tapblock(&mapB, I, g, tb);
+  if (lay.b_pair) {  // (n_lo, x, y, chan, n_hi): both image groups of a pixel's tap block in one box
+    const uint64_t xn = 1ull * g.W * g.N * 2;
+    uint64_t dims[5] = {kChunk, static_cast<uint64_t>(g.W), static_cast<uint64_t>(g.H), static_cast<uint64_t>(g.C), 2};
+    uint64_t str[4] = {1ull * g.N * 2, xn, xn * g.H, 128};
+    const uint32_t box[5] = {kChunk, static_cast<uint32_t>(tb.bw), static_cast<uint32_t>(tb.bh),
+                             static_cast<uint32_t>(g.C), 2};
+    rc = make_tensor_map(&mapB, I, dims, str, box);
+  } else {
+    rc = act_map_tapblock(&mapB, I, g, tb);
+  }
   if (rc != NG_OK) return rc;
   return tc_launch(c, mapA, mapB, p, stream);
 }
 
+// gradient with the filters along the rows, Dt[k][tile][box][row] (fp32; tile stride 256 columns,
+// `per` boxes of tb.rows columns per tile) -> gradF[c][t][r][s][k]
+__global__ void filter_unpack_t_kernel(Geo g, TapBlock tb, int per, int ld, const float* __restrict__ Dt, void* gradF,
+                                       int out_f32) {
+  const long long total = g.sizeF();
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int k = r % g.K; r /= g.K;
+    const int s = r % g.S; r /= g.S;
+    const int rr = r % g.R; r /= g.R;
+    const int t = r % g.T;
+    const int c = static_cast<int>(r / g.T);
+    const int b = (t * tb.nr + rr / tb.bh) * tb.ns + s / tb.bw;
+    const int row = (c * tb.bh + rr % tb.bh) * tb.bw + s % tb.bw;
+    const float v = Dt[1ll * k * ld + (b / per) * 256 + (b % per) * tb.rows + row];
+    if (out_f32) static_cast<float*>(gradF)[i] = v;
+    else static_cast<__half*>(gradF)[i] = __float2half_rn(v);
+  }
+}
+
+// Few filters (K <= 128) as well as few channels: the roles of the operands are exchanged, so that
+// the 128 MMA rows carry the filters and the 256 MMA columns carry the rows of several tap blocks
+// (an MMA with 64 columns costs nearly as much as one with 256). Column tile j owns tap blocks
+// [j * per, (j + 1) * per); its B operand is their input boxes stacked, its A operand the error box.
+int update_tapblock_swapped(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I, const void* E,
+                            void* gradF, int out_f32, float alpha, cudaStream_t stream) {
+  const int ntb = g.T * tb.nr * tb.ns;
+  const long long span = 1ll * g.M * g.P * g.Q * g.N;
+  const int per = 256 / tb.rows;
+  const int tiles = (ntb + per - 1) / per;
+  const int ld = tiles * 256;
+  const size_t dt_bytes = static_cast<size_t>(g.K) * ld * 4;
+  const size_t dt_off = (kMaxSplits * dt_bytes + 255) & ~size_t(255);
+  int rc = ensure_workspace(c, stream, dt_off + dt_bytes);
+  if (rc != NG_OK) return rc;
+  float* Dt = reinterpret_cast<float*>(reinterpret_cast<uint8_t*>(c->ws) + dt_off);
+  TcParams p = {};
+  p.mode = TC_UPDATE;
+  p.swap_ab = 1;
+  p.block_n = 256;
+  p.M = g.K; p.N = ld;
+  p.m_halves = 1; p.tiles_m = 1;
+  p.tiles_n = tiles;
+  p.nz = 1;
+  p.taps_per_z = ntb;
+  TcOperandLayout lay = {0, 0, kChunk};
+  lay.a_box_rows = std::min(g.K, kTileM);
+  lay.b_box_rows = tb.rows;
+  lay.b_box_count = per;
+  p.num_kb = static_cast<int>(span / kChunk);
+  tc_fill_mma(p, lay);
+  fill_taps(p, g, CH_PIXEL);
+  p.R = tb.nr; p.S = tb.ns; p.RS = tb.nr * tb.ns; p.tap_w = tb.bw; p.tap_h = tb.bh;
+  fill_decode(p, g.N, g.Q, g.P, g.M, CH_PIXEL);
+  p.oob_y = g.H;
+  p.C = Dt; p.Cold = nullptr; p.ldc = ld; p.c_zstride = 0;
+  p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 1; p.vec_ok = 1;
+  p.splits = choose_splits(c, p.tiles_n, p.num_kb, 1ll * g.K * ld);
+  CUtensorMap mapA, mapB;
+  rc = act_map(&mapA, E, g.K, g.M, g.P, g.Q, g.N, CH_PIXEL, lay.a_box_rows);
+  if (rc != NG_OK) return rc;
+  rc = act_map_tapblock(&mapB, I, g, tb);
+  if (rc != NG_OK) return rc;
+  rc = tc_launch(c, mapA, mapB, p, stream);
+  if (rc != NG_OK) return rc;
+  filter_unpack_t_kernel<<<launch_1d(g.sizeF(), 256, c), 256, 0, stream>>>(g, tb, per, ld, Dt, gradF, out_f32);
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
+
 int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I, const void* E, void* gradF,
                     int out_f32, float alpha, cudaStream_t stream) {
+  static const bool swap_ok = !(getenv("NG_UPDATE_SWAP") && atoi(getenv("NG_UPDATE_SWAP")) == 0);
+  // (worth it when the tap blocks fill at least half of a 256-column tile)
+  if (swap_ok && g.K <= kTileM && g.T * tb.nr * tb.ns * tb.rows >= 128)
+    return update_tapblock_swapped(c, g, tb, I, E, gradF, out_f32, alpha, stream);
   const int ntb = g.T * tb.nr * tb.ns;
   const long long span = 1ll * g.M * g.P * g.Q * g.N;
   // workspace: [split-K partials of the engine, at most 32 splits][Dp]
@@ -536,18 +668,26 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   p.red_chunks = (g.C + lay.kb_rows - 1) / lay.kb_rows;
   p.num_kb = RST * p.red_chunks;
   tc_pick_tile(c, p, cols, p.num_kb, lay.kb_rows);
+  CUtensorMap mapA, mapB, mapBm;
+  // fewer, larger boxes where the shapes allow: the filters of a 128-row half as one box, the
+  // pixels of a column tile inside one image row as one box
+  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  lay.a_merge = !merge_off && g.K % kChunk == 0 && filter_map_merged(&mapA, F, g, lay.kb_rows) == NG_OK;
   tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.Q, g.P, g.M, mode);
   p.oob_y = g.H;
   p.C = O; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = relu; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
-  CUtensorMap mapA, mapB;
-  rc = filter_map(&mapA, F, g, lay.kb_rows);
-  if (rc != NG_OK) return rc;
+  if (!lay.a_merge) {
+    rc = filter_map(&mapA, F, g, lay.kb_rows);
+    if (rc != NG_OK) return rc;
+  }
   rc = act_map(&mapB, I, g.C, g.D, g.H, g.W, g.N, mode, lay.kb_rows);
   if (rc != NG_OK) return rc;
-  return tc_launch(c, mapA, mapB, p, stream);
+  if (mode == CH_PIXEL && g.str_w == 1)
+    p.b_merge = act_map_merged(&mapBm, I, g.C, g.D, g.H, g.W, g.N, lay.kb_rows, p.block_n / kChunk);
+  return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 
 int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gradI, float alpha, int path,
@@ -585,12 +725,15 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   p.oob_y = g.P;
   p.C = gradI; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
-  CUtensorMap mapA, mapB;
+  CUtensorMap mapA, mapB, mapBm;
   rc = filter_map(&mapA, F, g, kTileM * p.m_halves);
   if (rc != NG_OK) return rc;
   rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk);
   if (rc != NG_OK) return rc;
-  return tc_launch(c, mapA, mapB, p, stream);
+  // the error pixels of a column tile inside one image row as one box
+  if (mode == CH_PIXEL && g.str_w == 1)
+    p.b_merge = act_map_merged(&mapBm, E, g.K, g.M, g.P, g.Q, g.N, kChunk, p.block_n / kChunk);
+  return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 
 int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gradF, int out_f32, float alpha,

@@ -157,6 +157,11 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
   lay.a_mn_major = g.a_t ? 1 : 0;   // stored k x m: m contiguous
   lay.b_mn_major = g.b_t ? 0 : 1;   // stored k x n: n contiguous
   lay.kb_rows = kChunk;
+  // an operand whose contiguous dimension is m (or n), a multiple of 64: the map gets the 64-wide
+  // chunk number as a dimension of its own, and one box brings a 128-row half (a column tile)
+  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  lay.a_merge = !merge_off && g.a_t && g.m % kChunk == 0;
+  lay.b_merge_static = !merge_off && !g.b_t && g.n % kChunk == 0 && p.block_n >= 2 * kChunk;
   tc_fill_mma(p, lay);
   p.a_zmul = g.az != 0; p.b_zmul = g.bz != 0;
   p.C = g.C; p.Cold = g.beta != 0.0f ? g.C : nullptr;
@@ -182,6 +187,13 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     str[1] = g.az != 0 ? static_cast<uint64_t>(g.az) * 2 : str[0] * dims[1];
     str[2] = str[1] * dims[2];
     str[3] = str[2];
+    if (lay.a_merge) {   // (m_lo, k, m_hi, batch)
+      dims[0] = kChunk; dims[1] = g.k; dims[2] = g.m / kChunk; dims[3] = g.az != 0 ? g.batch : 1;
+      str[0] = static_cast<uint64_t>(g.lda) * 2; str[1] = 128;
+      str[2] = g.az != 0 ? static_cast<uint64_t>(g.az) * 2 : str[0] * dims[1];
+      str[3] = str[2] * dims[3];
+      box[1] = kChunk; box[2] = 2;
+    }
     int rc = make_tensor_map(&mapA, g.A, dims, str, box);
     if (rc != NG_OK) return rc;
   }
@@ -196,6 +208,13 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     str[1] = g.bz != 0 ? static_cast<uint64_t>(g.bz) * 2 : str[0] * dims[1];
     str[2] = str[1] * dims[2];
     str[3] = str[2];
+    if (lay.b_merge_static) {   // (n_lo, k, n_hi, batch)
+      dims[0] = kChunk; dims[1] = g.k; dims[2] = g.n / kChunk; dims[3] = g.bz != 0 ? g.batch : 1;
+      str[0] = static_cast<uint64_t>(g.ldb) * 2; str[1] = 128;
+      str[2] = g.bz != 0 ? static_cast<uint64_t>(g.bz) * 2 : str[0] * dims[1];
+      str[3] = str[2] * dims[3];
+      box[1] = kChunk; box[2] = p.block_n / kChunk;
+    }
     int rc = make_tensor_map(&mapB, g.B, dims, str, box);
     if (rc != NG_OK) return rc;
   }

@@ -64,9 +64,20 @@ struct TcOperandLayout {
   int a_mn_major, b_mn_major;
   int kb_rows;   // reduction rows per k-block
   int a_box_rows = 0;   // K-major A only: rows one box delivers (0 = the whole tile)
+  int b_box_rows = 0;   // K-major B only: the column tile is made of b_box_count boxes of this many
+  int b_box_count = 0;  // rows each (0 = one box of block_n rows)
+  // MN-major operands whose tensor map carries the 64-wide chunk number as a dimension of its own
+  // (behind the reduction rows), so that one box delivers several chunks in the order the MMA wants:
+  int a_merge = 0;         // A: one box per 128-row half
+  int b_merge_static = 0;  // B: one box per column tile
+  int b_pair = 0;          // B (tap-block map, N = 128): one box per pixel = its two chunks
 };
 void tc_fill_mma(TcParams& p, const TcOperandLayout& lay);
-int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream);
+// mapBm (optional, convolutions): a second map over B whose box is the whole column tile; the
+// kernel uses it for the tiles that lie inside one image row (p.b_merge says how its dimensions
+// are ordered) and the per-chunk map for the others.
+int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream,
+              const CUtensorMap* mapBm = nullptr);
 
 // 1 = 128-row tiles, 2 = 256-row tiles (two accumulators sharing each B operand: a third less
 // L2 -> SM traffic per flop, but no overlap of the epilogue with the next tile and coarser waves).

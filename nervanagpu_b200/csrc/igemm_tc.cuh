@@ -63,7 +63,15 @@ struct TcParams {
 
   // ---- producer
   int mode;
+  int swap_ab;                     // weight update only: A = error pixels (rows k), B = the input boxes
+                                   // of b_boxes taps per column tile (output transposed: few filters)
   int a_mn_major, b_mn_major;
+  int a_merge;                     // MN-major A: one box per 128-row half, map (64, rows, chunk, ...)
+  int b_merge;                     // MN-major B boxes that span the whole column tile:
+                                   //   1 conv, map (n, chan, x, y, z)        } tiles inside one image row;
+                                   //   2 conv, map (n_lo, chan, n_hi, x, y)  } per-chunk boxes otherwise
+                                   //   3 GEMM, map (n_lo, k, n_hi, batch), every tile
+                                   //   4 tap blocks, N = 128: a box per pixel, map (n_lo, x, y, chan, n_hi)
   int kb_rows;                     // reduction rows per k-block (64, or 16..64 for small C in fprop)
   int a_zmul, b_zmul;              // batched GEMM: coordinate in dim 2 = z * zmul
   // conv geometry (unused by TC_GEMM)
@@ -100,6 +108,6 @@ struct TcParams {
   unsigned long long* timeline;
 };
 
-constexpr int kTimelineCtas = 4, kTimelineTiles = 24, kTimelineSlots = 12;
+constexpr int kTimelineCtas = 4, kTimelineTiles = 24, kTimelineSlots = 20;
 
 }  // namespace ngb

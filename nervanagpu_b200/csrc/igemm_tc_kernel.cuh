@@ -45,9 +45,24 @@
     clk_acc[k] += now_ - clk_last;                  \
     clk_last = now_;                                \
   } while (0)
+// cycle buckets of the MMA issuer (slots 12: wait for operands, 13: issue, 14: commit) and of the
+// producer (slots 15: wait for a free slot, 16: coordinates + issue), summed over a tile
+#define NG_ROLE_CLK(acc)                            \
+  do {                                              \
+    const long long now_ = clock64();               \
+    (acc) += now_ - role_last;                      \
+    role_last = now_;                               \
+  } while (0)
+#define NG_ROLE_PUT(tile, slot, v)                                                                \
+  do {                                                                                            \
+    if (p.timeline && blockIdx.x < kTimelineCtas && (tile) < kTimelineTiles)                      \
+      p.timeline[(blockIdx.x * kTimelineTiles + (tile)) * kTimelineSlots + (slot)] = (v);          \
+  } while (0)
 #else
 #define NG_STAMP(tile, slot) do {} while (0)
 #define NG_CLK(k) do {} while (0)
+#define NG_ROLE_CLK(acc) do {} while (0)
+#define NG_ROLE_PUT(tile, slot, v) do {} while (0)
 #endif
 
 namespace ngb {
@@ -148,7 +163,8 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ TcParams p) {
+                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapBm,
+                const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // ring buffer must be 1024-byte aligned for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -188,6 +204,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
     if (p.tma_store) tma_prefetch_desc(&mapC);
+    if (p.b_merge == 1 || p.b_merge == 2) tma_prefetch_desc(&mapBm);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), tmem_cols);
@@ -205,6 +222,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool is_a = lane < p.a_boxes;
     const int bi = is_a ? lane : lane - p.a_boxes;
     const CUtensorMap* map = is_a ? &mapA : &mapB;
+    bool merged = false;   // this item's B operand comes as one box (convolutions, see b_merge)
     const uint32_t box_off = is_a ? bi * p.a_box_bytes : p.a_bytes + bi * p.b_box_bytes;
     int stage = 0;
     uint32_t phase = 0;
@@ -219,7 +237,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // an item that computes one half of a 256-row tile needs only that half's A boxes when they
       // are separate boxes (MN-major A); a K-major A box always carries all its rows
       const int a_live = (p.m_halves == 2 && it.live == 1 && p.a_mn_major) ? (p.a_boxes >> 1) : p.a_boxes;
-      const bool act = active && (!is_a || bi < a_live);
+      bool act = active && (!is_a || bi < a_live);
       const uint32_t tx_item = p.tx_bytes - static_cast<uint32_t>(p.a_boxes - a_live) * p.a_box_bytes;
       // Per-tile state of this lane's box. Everything that changes from one k-block to the next
       // is kept as counters that are stepped, not re-derived: integer division by run-time
@@ -231,16 +249,31 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       wk.kb = it.kb0;
       bool tap_live = true;         // update: this A box's tap exists (last group may be short)
       if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
-        if (!is_a) wk.cp = decode_chunk(p, n0 / kChunk + bi);
+        // (b_merge 4: a box carries the two chunks of one pixel)
+        if (!is_a) wk.cp = decode_chunk(p, n0 / kChunk + (p.b_merge == 4 ? 2 * bi : bi));
+        if (p.b_merge == 1 || p.b_merge == 2) {
+          // A column tile that lies inside one image row arrives as one box (its chunks are
+          // consecutive pixels / image groups of that row); other tiles chunk by chunk.
+          const ChunkPos first = decode_chunk(p, n0 / kChunk);
+          const int cpi0 = first.inner0 / kChunk;
+          merged = first.valid && (p.dec_q - first.q) * p.dec_cpi - cpi0 >= p.b_boxes;
+          if (merged && !is_a) {
+            act = act && bi == 0;
+            map = &mapBm;
+          } else if (!is_a) {
+            map = &mapB;
+          }
+        }
         wk.trs = fast_div(it.kb0, p.fd_red);
         wk.rc = it.kb0 - wk.trs * p.red_chunks;
         wk.tap = decode_tap(p, wk.trs);
       } else if (p.mode == TC_UPDATE) {
         // item z owns taps [z * taps_per_z, (z + 1) * taps_per_z); A box `bi` carries the bi-th of them
         // (acc_taps consecutive boxes stack into one accumulator)
-        const int zt = it.z * p.taps_per_z + (is_a ? bi : 0);
+        // (swapped operands: column tile tile_n owns taps [tile_n * b_boxes, ...), one per B box)
+        const int zt = p.swap_ab ? it.tile_n * p.b_boxes + (is_a ? 0 : bi) : it.z * p.taps_per_z + (is_a ? bi : 0);
         wk.tap = decode_tap(p, zt);
-        tap_live = zt < p.nz_out && (!is_a || bi < p.taps_per_z);
+        tap_live = p.swap_ab ? zt < p.taps_per_z : (zt < p.nz_out && (!is_a || bi < p.taps_per_z));
         wk.cp = decode_chunk(p, it.kb0);
       }
       // box coordinates of this lane's box at walker position `s`
@@ -253,15 +286,18 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           if (p.mode == TC_GEMM) {
             const int k0 = kb * kChunk;
             if (is_a) {
-              if (p.a_mn_major) { c0 = m0 + kChunk * bi; c1 = k0; } else { c0 = k0; c1 = m0; }
-              c2 = it.z * p.a_zmul;
+              if (p.a_merge) { c1 = k0; c2 = (m0 + kTileM * bi) / kChunk; c3 = it.z * p.a_zmul; }
+              else if (p.a_mn_major) { c0 = m0 + kChunk * bi; c1 = k0; c2 = it.z * p.a_zmul; }
+              else { c0 = k0; c1 = m0; c2 = it.z * p.a_zmul; }
             } else {
-              if (p.b_mn_major) { c0 = n0 + kChunk * bi; c1 = k0; } else { c0 = k0; c1 = n0; }
-              c2 = it.z * p.b_zmul;
+              if (p.b_merge == 3) { c1 = k0; c2 = n0 / kChunk; c3 = it.z * p.b_zmul; }
+              else if (p.b_mn_major) { c0 = n0 + kChunk * bi; c1 = k0; c2 = it.z * p.b_zmul; }
+              else { c0 = k0; c1 = n0; c2 = it.z * p.b_zmul; }
             }
           } else if (p.mode == TC_FPROP) {
             if (is_a) {  // filter rows c of tap trs, 64 output channels wide
-              c0 = m0 + kChunk * bi; c1 = trs; c2 = rc * p.kb_rows;
+              if (p.a_merge) { c1 = rc * p.kb_rows; c2 = (m0 + kTileM * bi) / kChunk; c3 = trs; }
+              else { c0 = m0 + kChunk * bi; c1 = trs; c2 = rc * p.kb_rows; }
             } else {     // input pixels of this chunk shifted by the tap
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
               c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
@@ -286,16 +322,26 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               c1 = q; c2 = v ? pp : p.oob_y; c3 = mm; c4 = rc * kChunk;
             }
           } else {  // TC_UPDATE: k-block = one 64-element chunk of the (m,p,q,n) space
-            if (is_a) {  // input pixels under tap z, 128 channels c
+            if (is_a != (p.swap_ab != 0)) {  // input pixels under tap z, 128 channels c
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
               c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
               c2 = tap_live ? cp.p * p.str_h - p.pad_h + tap.r * p.tap_h : p.oob_y;
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
-              c4 = m0;
+              c4 = p.swap_ab ? 0 : m0;
             } else {     // error pixels, block_n output channels k
-              c0 = cp.inner0; c1 = cp.q * p.x_tap; c2 = cp.p; c3 = cp.m; c4 = n0;
+              c0 = cp.inner0; c1 = cp.q * p.x_tap; c2 = cp.p; c3 = cp.m; c4 = p.swap_ab ? m0 : n0;
             }
           }
+        }
+        if (merged && !is_a) {
+          // the whole-tile box starts where the first chunk's box starts; its map orders the
+          // dimensions (n, chan, x, y, z) or, with several chunks per pixel, (n_lo, chan, n_hi, x, y)
+          const int n = c0, x = c1, y = c2, z = c3, ch = c4;
+          if (p.b_merge == 1) { c0 = n; c1 = ch; c2 = x; c3 = y; c4 = z; }
+          else { c0 = 0; c1 = ch; c2 = n / kChunk; c3 = x; c4 = y; }
+        } else if (p.b_merge == 4 && !is_a) {
+          // tap-block map with the image group last: (n_lo, x, y, chan, n_hi)
+          c3 = c4; c4 = c0 / kChunk; c0 = 0;
         }
       };
       // step a walker to the next k-block
@@ -323,27 +369,44 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       };
       // (Asking the L2 for the boxes of later k-blocks with prefetch copies was tried and was
       // slower everywhere: a prefetch costs the copy engine as much as the load it precedes.)
+#ifdef NG_TC_TIMELINE
+      long long role_last = clock64(), c_pwait = 0, c_pissue = 0, c_psync = 0, c_ptma = 0, c_padv = 0;
+#endif
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
         if (act) coords(wk, c0, c1, c2, c3, c4);
+        NG_ROLE_CLK(c_pissue);
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER);
+        NG_ROLE_CLK(c_pwait);
         if (lane == 0 && got) mbar_expect_tx(full_bar(stage), tx_item);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
+        NG_ROLE_CLK(c_psync);
         if (act) {
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
+        NG_ROLE_CLK(c_ptma);
         if (lane == 0) {
           if (kb == it.kb0) NG_STAMP(ptile, 0);       // first copy of the tile issued
           if (kb == it.kb1 - 1) NG_STAMP(ptile, 1);   // last copy of the tile issued
         }
         advance(wk);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        NG_ROLE_CLK(c_padv);
       }
+#ifdef NG_TC_TIMELINE
+      if (lane == 0) {
+        NG_ROLE_PUT(ptile, 15, c_pwait);
+        NG_ROLE_PUT(ptile, 16, c_pissue);
+        NG_ROLE_PUT(ptile, 17, c_psync);
+        NG_ROLE_PUT(ptile, 18, c_ptma);
+        NG_ROLE_PUT(ptile, 19, c_padv);
+      }
+#endif
       ++ptile;
     }
   } else if (warp == 1) {
@@ -376,11 +439,15 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tc_fence_after();
         }
         NG_STAMP(local, 2);                           // accumulator is free
+#ifdef NG_TC_TIMELINE
+        long long role_last = clock64(), c_mwait = 0, c_missue = 0, c_mcommit = 0;
+#endif
         for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
           if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA)) {
             ok = false;
             break;
           }
+          NG_ROLE_CLK(c_mwait);
           if (kb == it.kb0) NG_STAMP(local, 3);       // first operands have landed
           tc_fence_after();
           const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
@@ -404,9 +471,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             }
           }
           if (!ok) break;
+          NG_ROLE_CLK(c_missue);
           tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          NG_ROLE_CLK(c_mcommit);
         }
+        NG_ROLE_PUT(local, 12, c_mwait);
+        NG_ROLE_PUT(local, 13, c_missue);
+        NG_ROLE_PUT(local, 14, c_mcommit);
         if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
         NG_STAMP(local, 4);                           // last MMA of the tile issued
         ++local;

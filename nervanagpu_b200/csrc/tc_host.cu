@@ -78,8 +78,11 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   if (p.m_halves != 2) p.m_halves = 1;
   const uint32_t tile_rows = kTileM * p.m_halves;
   if (lay.a_mn_major) {
-    p.a_boxes = tile_rows / kChunk;
-    p.a_box_bytes = mn_box;
+    // one box per 64-row chunk, or (a_merge: the map has the chunk number as a dimension of its
+    // own, behind the reduction rows) one box per 128-row half
+    p.a_boxes = lay.a_merge ? p.m_halves : tile_rows / kChunk;
+    p.a_box_bytes = lay.a_merge ? 2u * mn_box : mn_box;
+    p.a_merge = lay.a_merge;
     p.a_desc_lo = desc_lo(mn_box);
     p.a_kstep = 2048u >> 4;
     p.a_half_step = (2u * mn_box) >> 4;
@@ -102,20 +105,28 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   // allocation); those products fall in accumulator rows that are never stored.
   p.a_bytes = p.a_boxes * p.a_box_bytes;
   if (lay.b_mn_major) {
-    p.b_boxes = p.block_n / kChunk;
-    p.b_box_bytes = mn_box;
+    // one box per 64-column chunk, or (b_merge_static) one box for the whole column tile
+    // (b_pair: one box per pixel, its two image groups)
+    const int per_box = lay.b_merge_static ? p.block_n / kChunk : (lay.b_pair ? 2 : 1);
+    p.b_boxes = p.block_n / kChunk / per_box;
+    p.b_box_bytes = per_box * mn_box;
+    if (lay.b_merge_static) p.b_merge = 3;
+    if (lay.b_pair) p.b_merge = 4;
     p.b_desc_lo = desc_lo(mn_box);
     p.b_kstep = 2048u >> 4;
   } else {
-    p.b_boxes = 1;
-    p.b_box_bytes = static_cast<uint32_t>(p.block_n) * 128u;
+    // one box of block_n rows, or several shorter ones stacked (rows past the last box keep stale
+    // data: their products are columns that the caller never reads)
+    p.b_boxes = lay.b_box_count > 0 ? lay.b_box_count : 1;
+    p.b_box_bytes = static_cast<uint32_t>(lay.b_box_count > 0 ? lay.b_box_rows : p.block_n) * 128u;
     p.b_desc_lo = desc_lo(16);
     p.b_kstep = 32u >> 4;
   }
   p.b_desc_hi = desc_hi(1024);
   // every box must start on a 1024-byte boundary for the 128-byte swizzle
   p.a_bytes = (p.a_bytes + 1023u) & ~1023u;
-  const uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
+  uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
+  if (!lay.b_mn_major) b_bytes = std::max(b_bytes, static_cast<uint32_t>(p.block_n) * 128u);
   p.stage_bytes = p.a_bytes + b_bytes;
   p.tx_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
   p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes - a_overread(p)) /
@@ -172,7 +183,9 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
   const long long cost1 = ((t1 + sm - 1) / sm) * num_kb * (kTileM + p.block_n);
   const long long tm2 = (p.M + 2 * kTileM - 1) / (2 * kTileM);
   const long long t2 = tm2 * col_tiles;
-  const long long cost2 = ((t2 + sm - 1) / sm) * (num_kb + 4ll) * (2 * kTileM + p.block_n);
+  long long cost2 = ((t2 + sm - 1) / sm) * (num_kb + 4ll) * (2 * kTileM + p.block_n);
+  if (t2 % sm > 0 && 2 * (t2 % sm) <= sm)   // the last wave runs as 128-row halves (see tc_launch)
+    cost2 -= (num_kb + 4ll) * (2 * kTileM + p.block_n) - (num_kb + 2ll) * (kTileM + p.block_n);
   // NG_TILE_ROWS=128|256 overrides the choice (tuning aid)
   static const char* force = getenv("NG_TILE_ROWS");
   const bool wide = force ? (force[0] == '2') : (cost2 < cost1);
@@ -190,7 +203,6 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
 void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, int kb_rows) {
   static const char* force_rows = getenv("NG_TILE_ROWS");
   static const char* force_cols = getenv("NG_TILE_COLS");
-  const double sm = c->sm_count;
   double best = -1.0;
   int best_h = 1, best_bn = 256;
   for (int h = 1; h <= 2; ++h) {
@@ -200,12 +212,18 @@ void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, i
       if (force_cols && atoi(force_cols) != bn) continue;
       const long long tm = (p.M + kTileM * h - 1) / (kTileM * h);
       const long long tn = (cols + bn - 1) / bn;
-      const double waves = static_cast<double>((tm * tn + c->sm_count - 1) / c->sm_count);
-      (void)sm;
+      const long long tiles = tm * tn;
       const double feed_ns = (kTileM * h + bn) * kb_rows * 2.0 / 68.0;
       const double mma_ns = h * (kb_rows / 16) * (kTileM + bn) * 0.5 / 1.9;
       const double epi_ns = h == 2 ? 5500.0 * bn / 256.0 : 600.0;
-      const double t = waves * (num_kb * std::max(feed_ns, mma_ns) + epi_ns);
+      const double tile_ns = num_kb * std::max(feed_ns, mma_ns) + epi_ns;
+      double t = static_cast<double>((tiles + c->sm_count - 1) / c->sm_count) * tile_ns;
+      const long long rem = tiles % c->sm_count;
+      if (h == 2 && rem > 0 && 2 * rem <= c->sm_count) {
+        // the last wave runs as 128-row halves (see tc_launch)
+        const double half_feed = (kTileM + bn) * kb_rows * 2.0 / 68.0;
+        t += num_kb * std::max(half_feed, mma_ns * 0.5) + epi_ns * 0.5 - tile_ns;
+      }
       if (best < 0.0 || t < best) {
         best = t;
         best_h = h;
@@ -250,7 +268,8 @@ static int splitk_reduce_lanes(long long groups, int splits, int sm_count) {
   return lanes;
 }
 
-int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream) {
+int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, TcParams& p, cudaStream_t stream,
+              const CUtensorMap* mapBm) {
   if (p.num_kb < 1) return fail(NG_ERR_INVALID_ARG, "empty reduction");
   if (p.splits < 1) p.splits = 1;
   if (p.acc_groups < 1) p.acc_groups = 1;
@@ -316,7 +335,8 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     launch.timeline = tl_dev;
   }
 #endif
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, launch);
+  if (!mapBm && (launch.b_merge == 1 || launch.b_merge == 2)) launch.b_merge = 0;
+  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapBm ? *mapBm : mapB, launch);
   NG_CHECK_LAUNCH();
 #ifdef NG_TC_TIMELINE
   if (tl_out) {
@@ -337,6 +357,10 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
           for (int k = 0; k < 8; ++k) fprintf(f, " %8lld", s[k] ? static_cast<long long>(s[k] - t0) : -1ll);
           fprintf(f, "  epilogue cycles other/tmem/convert/write:");
           for (int k = 8; k < 12; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
+          fprintf(f, "  mma wait/issue/commit:");
+          for (int k = 12; k < 15; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
+          fprintf(f, "  producer wait/coords/sync/copy/advance:");
+          for (int k = 15; k < 20; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
           fprintf(f, "\n");
         }
       fclose(f);
@@ -500,7 +524,7 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   p.timeline = nullptr;
   p.full_items = p.total_items = static_cast<int>(total);
   ngb::fill_fast_divs(p);
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, p);
+  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;
   ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;
