@@ -441,7 +441,8 @@ int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I
   // fewer, larger boxes: the filters of a 128-row half as one box (K a multiple of 64), the two
   // image groups of a pixel as one box (N = 128, 2-D)
   static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
-  lay.a_merge = !merge_off && g.K % kChunk == 0;
+  lay.a_merge = !merge_off && g.K % kChunk == 0 && g.K > kChunk;
+  lay.a_chunks = (g.K + kChunk - 1) / kChunk;
   lay.b_pair = !merge_off && g.N == 2 * kChunk && g.D == 1;
   tc_fill_mma(p, lay);
   fill_taps(p, g, CH_PIXEL);
@@ -672,7 +673,9 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   // fewer, larger boxes where the shapes allow: the filters of a 128-row half as one box, the
   // pixels of a column tile inside one image row as one box
   static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
-  lay.a_merge = !merge_off && g.K % kChunk == 0 && filter_map_merged(&mapA, F, g, lay.kb_rows) == NG_OK;
+  lay.a_merge = !merge_off && g.K % kChunk == 0 && g.K > kChunk &&
+                filter_map_merged(&mapA, F, g, lay.kb_rows) == NG_OK;
+  lay.a_chunks = (g.K + kChunk - 1) / kChunk;
   tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.Q, g.P, g.M, mode);
@@ -719,6 +722,9 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   p.red_chunks = (g.K + kChunk - 1) / kChunk;
   p.num_kb = RST * p.red_chunks;
   tc_pick_tile(c, p, cols, p.num_kb, kChunk);
+  // fewer input channels than tile rows (one row tile): the filter box carries the real rows only
+  const int a_rows = p.tiles_m == 1 ? std::min(kTileM * p.m_halves, (g.C + 7) / 8 * 8) : kTileM * p.m_halves;
+  lay.a_box_rows = a_rows;
   tc_fill_mma(p, lay);
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.W, g.H, g.D, mode);
@@ -726,7 +732,7 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   p.C = gradI; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
   CUtensorMap mapA, mapB, mapBm;
-  rc = filter_map(&mapA, F, g, kTileM * p.m_halves);
+  rc = filter_map(&mapA, F, g, a_rows);
   if (rc != NG_OK) return rc;
   rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk);
   if (rc != NG_OK) return rc;

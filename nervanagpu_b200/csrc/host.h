@@ -68,6 +68,7 @@ struct TcOperandLayout {
   int b_box_count = 0;  // rows each (0 = one box of block_n rows)
   // MN-major operands whose tensor map carries the 64-wide chunk number as a dimension of its own
   // (behind the reduction rows), so that one box delivers several chunks in the order the MMA wants:
+  int a_chunks = 0;        // MN-major A, 128-row tiles: 64-row chunks that hold real rows (0 = both)
   int a_merge = 0;         // A: one box per 128-row half
   int b_merge_static = 0;  // B: one box per column tile
   int b_pair = 0;          // B (tap-block map, N = 128): one box per pixel = its two chunks

@@ -161,6 +161,9 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 
 }  // namespace
 
+// One instance per mode (kMode = p.mode): the producer of each carries only its own coordinate
+// code, which keeps the single-warp roles' loops short in the instruction cache.
+template <int kMode>
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapBm,
@@ -248,7 +251,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       wk.trs = 0; wk.rc = 0;        // tap number and reduction-chunk number inside the tap
       wk.kb = it.kb0;
       bool tap_live = true;         // update: this A box's tap exists (last group may be short)
-      if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
+      if (kMode == TC_FPROP || kMode == TC_BPROP) {
         // (b_merge 4: a box carries the two chunks of one pixel)
         if (!is_a) wk.cp = decode_chunk(p, n0 / kChunk + (p.b_merge == 4 ? 2 * bi : bi));
         if (p.b_merge == 1 || p.b_merge == 2) {
@@ -267,7 +270,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         wk.trs = fast_div(it.kb0, p.fd_red);
         wk.rc = it.kb0 - wk.trs * p.red_chunks;
         wk.tap = decode_tap(p, wk.trs);
-      } else if (p.mode == TC_UPDATE) {
+      } else if (kMode == TC_UPDATE) {
         // item z owns taps [z * taps_per_z, (z + 1) * taps_per_z); A box `bi` carries the bi-th of them
         // (acc_taps consecutive boxes stack into one accumulator)
         // (swapped operands: column tile tile_n owns taps [tile_n * b_boxes, ...), one per B box)
@@ -283,7 +286,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int trs = s.trs, rc = s.rc, kb = s.kb;
         c0 = c1 = c2 = c3 = c4 = 0;
         {
-          if (p.mode == TC_GEMM) {
+          if (kMode == TC_GEMM) {
             const int k0 = kb * kChunk;
             if (is_a) {
               if (p.a_merge) { c1 = k0; c2 = (m0 + kTileM * bi) / kChunk; c3 = it.z * p.a_zmul; }
@@ -294,7 +297,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               else if (p.b_mn_major) { c0 = n0 + kChunk * bi; c1 = k0; c2 = it.z * p.b_zmul; }
               else { c0 = k0; c1 = n0; c2 = it.z * p.b_zmul; }
             }
-          } else if (p.mode == TC_FPROP) {
+          } else if (kMode == TC_FPROP) {
             if (is_a) {  // filter rows c of tap trs, 64 output channels wide
               if (p.a_merge) { c1 = rc * p.kb_rows; c2 = (m0 + kTileM * bi) / kChunk; c3 = trs; }
               else { c0 = m0 + kChunk * bi; c1 = trs; c2 = rc * p.kb_rows; }
@@ -305,7 +308,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = rc * p.kb_rows;
             }
-          } else if (p.mode == TC_BPROP) {
+          } else if (kMode == TC_BPROP) {
             if (is_a) {  // filter rows c0.., 64 output channels k of tap trs
               c0 = rc * kChunk; c1 = trs; c2 = m0;
             } else {     // error pixels that reach this input pixel through tap trs
@@ -347,7 +350,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // step a walker to the next k-block
       auto advance = [&](Walk& s) {
         ++s.kb;
-        if (p.mode == TC_FPROP || p.mode == TC_BPROP) {
+        if (kMode == TC_FPROP || kMode == TC_BPROP) {
           if (++s.rc == p.red_chunks) {
             s.rc = 0;
             ++s.trs;
@@ -356,7 +359,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               if (++s.tap.r == p.R) { s.tap.r = 0; ++s.tap.t; }
             }
           }
-        } else if (p.mode == TC_UPDATE) {
+        } else if (kMode == TC_UPDATE) {
           s.cp.inner0 += kChunk;
           if (s.cp.inner0 == p.dec_cpi * kChunk) {
             s.cp.inner0 = 0;
@@ -422,7 +425,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       const bool wide = p.m_halves == 2;
       // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
       // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
-      const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
+      const bool grouped = kMode == TC_UPDATE && (p.acc_groups > 1 || p.acc_taps > 1);
       for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
         const WorkItem it = decode_work(p, w);
         if (it.live == 0) continue;     // `local` counts the items this CTA works on, in every role alike
@@ -491,13 +494,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     // One set of output-stage scalars, held in registers: split-K partials leave as untouched
     // fp32 accumulators. (Choosing between two argument structs by reference put both in local
     // memory, and every use became a load.)
-    const bool partial = p.splits > 1;
-    const bool f32 = partial || p.out_f32 != 0;
+    // (The forward and backward passes always write rounded fp16 without a beta term, the weight
+    // update never rounds stochastically: their instances leave those paths out.)
+    constexpr bool kConvOut = kMode == TC_FPROP || kMode == TC_BPROP;
+    constexpr bool kNoBetaSr = kMode != TC_GEMM;
+    const bool partial = !kConvOut && p.splits > 1;
+    const bool f32 = !kConvOut && (partial || p.out_f32 != 0);
     EpiArgs ea;
     ea.alpha = partial ? 1.0f : p.alpha;
-    ea.beta = partial ? 0.0f : p.beta;
-    ea.relu = partial ? 0 : p.relu;
-    ea.sr_bits = partial ? 0 : p.sr_bits;
+    ea.beta = (partial || kNoBetaSr) ? 0.0f : p.beta;
+    ea.relu = (partial || kMode == TC_UPDATE) ? 0 : p.relu;
+    ea.sr_bits = (partial || kNoBetaSr) ? 0 : p.sr_bits;
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
     // the common case gets a short path of its own: the epilogue is bound by instruction latency
     // (two warps per scheduler), so every instruction fewer counts
@@ -505,7 +512,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
-    const bool grouped = p.acc_groups > 1 || p.acc_taps > 1;
+    const bool grouped = kMode == TC_UPDATE && (p.acc_groups > 1 || p.acc_taps > 1);
     const int n_acc = wide ? 2 : p.acc_groups;   // accumulators of one work item
     int local = 0;
     for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
@@ -676,7 +683,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               // queue behind the operand loads of the copy engine, and the wait for it to release
               // the staging buffer then costs ~2 us per box.
               __syncwarp();
-              const int esz = (partial || p.out_f32) ? 4 : 2;
+              const int esz = f32 ? 4 : 2;
               uint8_t* gbase;
               long long gstride;
               if (partial) {

@@ -80,7 +80,11 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   if (lay.a_mn_major) {
     // one box per 64-row chunk, or (a_merge: the map has the chunk number as a dimension of its
     // own, behind the reduction rows) one box per 128-row half
-    p.a_boxes = lay.a_merge ? p.m_halves : tile_rows / kChunk;
+    // (a_chunks: a 128-row tile over fewer than 128 real rows loads the real chunks only; the
+    // MMA then reads stale shared memory for the others, rows that are never stored)
+    int chunks = tile_rows / kChunk;
+    if (!lay.a_merge && p.m_halves == 1 && lay.a_chunks > 0) chunks = std::min(chunks, lay.a_chunks);
+    p.a_boxes = lay.a_merge ? p.m_halves : chunks;
     p.a_box_bytes = lay.a_merge ? 2u * mn_box : mn_box;
     p.a_merge = lay.a_merge;
     p.a_desc_lo = desc_lo(mn_box);
@@ -297,7 +301,10 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     p.ws = nullptr;
   }
   if (!c->smem_attr_set) {
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_FPROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_BPROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_UPDATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     c->smem_attr_set = true;
   }
   long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
@@ -336,7 +343,14 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   }
 #endif
   if (!mapBm && (launch.b_merge == 1 || launch.b_merge == 2)) launch.b_merge = 0;
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapBm ? *mapBm : mapB, launch);
+  const CUtensorMap& mapB2 = mapBm ? *mapBm : mapB;
+  switch (launch.mode) {
+    case TC_GEMM: igemm_tc_kernel<TC_GEMM><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
+    case TC_FPROP: igemm_tc_kernel<TC_FPROP><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
+    case TC_BPROP: igemm_tc_kernel<TC_BPROP><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
+    case TC_UPDATE: igemm_tc_kernel<TC_UPDATE><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
+    default: return fail(NG_ERR_INVALID_ARG, "internal: unknown tensor-core mode");
+  }
   NG_CHECK_LAUNCH();
 #ifdef NG_TC_TIMELINE
   if (tl_out) {
@@ -429,7 +443,7 @@ int static_setup(int dev, StaticSlots** out) {
     s.scratch = static_cast<float*>(p);
     NG_CUDA(cudaGetSymbolAddress(&p, g_static_status));
     s.status = static_cast<int*>(p);
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     s.ready = true;
   }
   *out = &s;
@@ -524,7 +538,7 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   p.timeline = nullptr;
   p.full_items = p.total_items = static_cast<int>(total);
   ngb::fill_fast_divs(p);
-  igemm_tc_kernel<<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
+  igemm_tc_kernel<TC_GEMM><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;
   ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;
