@@ -163,7 +163,9 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 
 // One instance per mode (kMode = p.mode): the producer of each carries only its own coordinate
 // code, which keeps the single-warp roles' loops short in the instruction cache.
-template <int kMode>
+// kLean instances serve the common output stage only (tiles staged through shared memory,
+// alpha 1, no beta term, round to nearest, or raw split-K partials) and carry no other.
+template <int kMode, bool kLean>
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapBm,
@@ -175,7 +177,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   const uint32_t ring_bytes = static_cast<uint32_t>(p.stages) * p.stage_bytes;
   // output staging (bulk-store epilogue only), then the control block
   const uint32_t epi_base = smem_base + ring_bytes;
-  const uint32_t epi_bytes = p.tma_store ? kEpiStageBytes : 0u;
+  const int store_mode = kLean ? 2 : p.tma_store;
+  const uint32_t epi_bytes = store_mode ? kEpiStageBytes : 0u;
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + ring_bytes + epi_bytes);
   const uint32_t bar_base = smem_base + ring_bytes + epi_bytes;
@@ -206,7 +209,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
-    if (p.tma_store) tma_prefetch_desc(&mapC);
+    if (store_mode == 1) tma_prefetch_desc(&mapC);
     if (p.b_merge == 1 || p.b_merge == 2) tma_prefetch_desc(&mapBm);
   }
   if (warp == 1) {
@@ -508,7 +511,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     ea.seed_lo = p.seed_lo; ea.seed_hi = p.seed_hi; ea.rng_offset = p.rng_offset;
     // the common case gets a short path of its own: the epilogue is bound by instruction latency
     // (two warps per scheduler), so every instruction fewer counts
-    const bool plain = ea.alpha == 1.0f && ea.beta == 0.0f && ea.sr_bits == 0;
+    const bool plain = kLean || (ea.alpha == 1.0f && ea.beta == 0.0f && ea.sr_bits == 0);
     const bool wide = p.m_halves == 2;
     // two warps share each group of 32 TMEM lanes and split the columns between them
     const int col_group = (warp - 2) >> 2;
@@ -572,7 +575,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
           lin_row = (static_cast<unsigned long long>(zt) * p.M + row) * static_cast<unsigned long long>(p.N);
         }
-        if (p.tma_store) {
+        if (store_mode) {
           // Staged path: 32 rows x 128 bytes per box, written to shared memory in the 128-byte
           // swizzle pattern (16-byte chunk j of row t lands at chunk j ^ (t & 7): conflict-free
           // for the per-row writes below), then one bulk tensor store per box. The store clips
@@ -600,7 +603,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               }
 #endif
               NG_CLK(1);
-              if (sub == 0 && p.tma_store == 1) {
+              if (sub == 0 && store_mode == 1) {
                 // the previous store from this warp's buffer must have read it before we overwrite
                 if (lane == 0) tma_store_wait_read<0>();
                 __syncwarp();
@@ -670,7 +673,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               }
             }
             NG_CLK(2);
-            if (p.tma_store == 1) {
+            if (store_mode == 1) {
               fence_async_smem();
               __syncwarp();
               if (lane == 0) {
@@ -718,7 +721,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int n_chunks = p.block_n / 32;
         const int c_begin = col_group == 0 ? 0 : (n_chunks + 1) / 2;
         const int c_end = col_group == 0 ? (n_chunks + 1) / 2 : n_chunks;
-        for (int c = c_begin; !p.tma_store && half_live && c < c_end; ++c) {
+        for (int c = c_begin; !store_mode && half_live && c < c_end; ++c) {
           uint32_t r[32];
           tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
           tc_wait_ld();
@@ -764,7 +767,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       ++local;
     }
     // outstanding bulk stores must be complete before the CTA (and its shared memory) goes away
-    if (p.tma_store && lane == 0) tma_store_wait_all();
+    if (store_mode == 1 && lane == 0) tma_store_wait_all();
   }
 
   // =========================== teardown ===========================

@@ -301,10 +301,14 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     p.ws = nullptr;
   }
   if (!c->smem_attr_set) {
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_FPROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_BPROP>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_UPDATE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+#define NG_TC_SMEM_ATTR(mode)                                                                                        \
+  NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<mode, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit)); \
+  NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<mode, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit))
+    NG_TC_SMEM_ATTR(TC_GEMM);
+    NG_TC_SMEM_ATTR(TC_FPROP);
+    NG_TC_SMEM_ATTR(TC_BPROP);
+    NG_TC_SMEM_ATTR(TC_UPDATE);
+#undef NG_TC_SMEM_ATTR
     c->smem_attr_set = true;
   }
   long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
@@ -344,13 +348,21 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
 #endif
   if (!mapBm && (launch.b_merge == 1 || launch.b_merge == 2)) launch.b_merge = 0;
   const CUtensorMap& mapB2 = mapBm ? *mapBm : mapB;
+  // the lean instances: staged tiles, and either raw split-K partials or alpha 1 / no beta / round to nearest
+  static const bool lean_ok = !(getenv("NG_LEAN_KERNELS") && atoi(getenv("NG_LEAN_KERNELS")) == 0);
+  const bool lean = lean_ok && launch.tma_store == 2 &&
+                    (launch.splits > 1 || (launch.alpha == 1.0f && launch.beta == 0.0f && launch.sr_bits == 0));
+#define NG_TC_LAUNCH(mode)                                                                                      \
+  if (lean) igemm_tc_kernel<mode, true><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch);   \
+  else igemm_tc_kernel<mode, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch)
   switch (launch.mode) {
-    case TC_GEMM: igemm_tc_kernel<TC_GEMM><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
-    case TC_FPROP: igemm_tc_kernel<TC_FPROP><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
-    case TC_BPROP: igemm_tc_kernel<TC_BPROP><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
-    case TC_UPDATE: igemm_tc_kernel<TC_UPDATE><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch); break;
+    case TC_GEMM: NG_TC_LAUNCH(TC_GEMM); break;
+    case TC_FPROP: NG_TC_LAUNCH(TC_FPROP); break;
+    case TC_BPROP: NG_TC_LAUNCH(TC_BPROP); break;
+    case TC_UPDATE: NG_TC_LAUNCH(TC_UPDATE); break;
     default: return fail(NG_ERR_INVALID_ARG, "internal: unknown tensor-core mode");
   }
+#undef NG_TC_LAUNCH
   NG_CHECK_LAUNCH();
 #ifdef NG_TC_TIMELINE
   if (tl_out) {
@@ -443,7 +455,7 @@ int static_setup(int dev, StaticSlots** out) {
     s.scratch = static_cast<float*>(p);
     NG_CUDA(cudaGetSymbolAddress(&p, g_static_status));
     s.status = static_cast<int*>(p);
-    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_GEMM>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
+    NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<TC_GEMM, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit));
     s.ready = true;
   }
   *out = &s;
@@ -538,7 +550,7 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   p.timeline = nullptr;
   p.full_items = p.total_items = static_cast<int>(total);
   ngb::fill_fast_divs(p);
-  igemm_tc_kernel<TC_GEMM><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
+  igemm_tc_kernel<TC_GEMM, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;
   ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;
