@@ -179,6 +179,15 @@ int ng_pool_bprop(const ng_pool_desc* desc, int dtype_bytes, const void* I, cons
  * nervanagpu/layers.py:87-96), because only a window's maximum receives error at all. */
 int ng_pool_bprop_relu(const ng_pool_desc* desc, int dtype_bytes, const void* I, const void* E, void* gradI,
                        void* stream);
+/* The pooling ops the reference declares besides max (PoolLayer(op=...), nervanagpu/layers.py:542-552):
+ * op 0 = max (the two entries above), 1 = avg, 2 = l2. The reference defines avg and l2 only in
+ * numpy (benchmarks/pool_test.py:141-146: mean / root of the sum of squares over all J*T*R*S window
+ * positions, positions outside the tensor counting as zeros) and launches its max kernel for every
+ * op (nervanagpu/nervanagpu.py:797); here they run on the device. Their backward passes are the
+ * derivatives of those definitions: gradI += E / (J*T*R*S), and gradI += E * I / O (0 where O is 0). */
+int ng_pool_fprop_op(const ng_pool_desc* desc, int op, int dtype_bytes, const void* I, void* O, void* stream);
+int ng_pool_bprop_op(const ng_pool_desc* desc, int op, int dtype_bytes, const void* I, const void* E, void* gradI,
+                     void* stream);
 /* Forward pass that records each window's argmax (one byte per output element) in a buffer of the
  * caller, and backward pass from that record, which then reads neither the input nor recomputes
  * any window. The reference's backward kernel rescans every window (hpool_max.sass mode 1,

@@ -92,6 +92,8 @@ SIGNATURES = {
     "ng_pool_fprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop_relu": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "ng_pool_fprop_op": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_int, c_void_p, c_void_p, c_void_p]),
+    "ng_pool_bprop_op": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ng_pool_argmax_bytes": (c_int, [ctypes.POINTER(PoolDesc), c_int, ctypes.POINTER(c_size_t)]),
     "ng_pool_fprop_argmax": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
     "ng_pool_bprop_argmax": (c_int, [ctypes.POINTER(PoolDesc), c_int, c_void_p, c_void_p, c_void_p, c_int,

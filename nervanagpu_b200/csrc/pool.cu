@@ -579,6 +579,142 @@ __global__ void pool_bprop_tiled_kernel(PoolGeo g, const T* __restrict__ I, cons
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Average and L2 pooling. The reference declares both ops and defines them in numpy
+// (benchmarks/pool_test.py:141-146: the mean, and the root of the sum of squares, over all
+// J*T*R*S window positions, positions outside the tensor counting as zeros), but its device path
+// runs the max kernel whatever the op (nervanagpu/nervanagpu.py:797). The backward passes are
+// the derivatives of those definitions: dI += E / (J*T*R*S), and dI += E * I / O (0 where O is 0).
+// ------------------------------------------------------------------------------------------
+enum PoolOp : int { POOL_MAX = 0, POOL_AVG = 1, POOL_L2 = 2 };
+
+// sum (avg) or sum of squares (l2) of window (k,m,p,q), per image lane
+template <typename T, int V>
+__device__ __forceinline__ void window_sum(const PoolGeo& g, const T* __restrict__ I, int k, int m, int p, int q,
+                                           int nv, bool squares, float (&acc)[V]) {
+#pragma unroll
+  for (int i = 0; i < V; ++i) acc[i] = 0.0f;
+  const int c0 = k * g.str_j - g.pad_j, z0 = m * g.str_d - g.pad_d, y0 = p * g.str_h - g.pad_h,
+            x0 = q * g.str_w - g.pad_w;
+  for (int j = 0; j < g.J; ++j) {
+    const int c = c0 + j;
+    if (c < 0 || c >= g.C) continue;
+    for (int t = 0; t < g.T; ++t) {
+      const int z = z0 + t;
+      if (z < 0 || z >= g.D) continue;
+      for (int r = 0; r < g.R; ++r) {
+        const int y = y0 + r;
+        if (y < 0 || y >= g.H) continue;
+        for (int s = 0; s < g.S; ++s) {
+          const int x = x0 + s;
+          if (x < 0 || x >= g.W) continue;
+          const long long flat = ((1ll * c * g.D + z) * g.H + y) * g.W + x;
+          const Vec<T, V> v = *reinterpret_cast<const Vec<T, V>*>(I + (flat * g.N + nv * V));
+#pragma unroll
+          for (int i = 0; i < V; ++i) {
+            const float f = v.get(i);
+            acc[i] += squares ? f * f : f;
+          }
+        }
+      }
+    }
+  }
+}
+
+template <typename T, int V>
+__global__ void pool_fprop_op_kernel(PoolGeo g, int op, const T* __restrict__ I, T* __restrict__ O) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.K * g.M * g.P * g.Q * nvec;
+  const float inv = 1.0f / static_cast<float>(g.J * g.T * g.R * g.S);
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int q = r % g.Q; r /= g.Q;
+    const int p = r % g.P; r /= g.P;
+    const int m = r % g.M; r /= g.M;
+    const int k = static_cast<int>(r);
+    float acc[V];
+    window_sum<T, V>(g, I, k, m, p, q, nv, op == POOL_L2, acc);
+    Vec<T, V> out;
+#pragma unroll
+    for (int j = 0; j < V; ++j) out.set(j, op == POOL_L2 ? sqrtf(acc[j]) : acc[j] * inv);
+    *reinterpret_cast<Vec<T, V>*>(O + i * V) = out;
+  }
+}
+
+// One thread per input element (and image lane group): sums over the windows that contain it, in
+// increasing (k,m,p,q) order. The L2 pass recomputes each such window's norm.
+template <typename T, int V>
+__global__ void pool_bprop_op_kernel(PoolGeo g, int op, const T* __restrict__ I, const T* __restrict__ E,
+                                     T* __restrict__ dI) {
+  const int nvec = g.N / V;
+  const long long total = 1ll * g.C * g.D * g.H * g.W * nvec;
+  const float inv = 1.0f / static_cast<float>(g.J * g.T * g.R * g.S);
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int nv = r % nvec; r /= nvec;
+    const int x = r % g.W; r /= g.W;
+    const int y = r % g.H; r /= g.H;
+    const int z = r % g.D; r /= g.D;
+    const int c = static_cast<int>(r);
+    int k0, k1, m0, m1, p0, p1, q0, q1;
+    window_range(c, g.pad_j, g.J, g.str_j, g.K, k0, k1);
+    window_range(z, g.pad_d, g.T, g.str_d, g.M, m0, m1);
+    window_range(y, g.pad_h, g.R, g.str_h, g.P, p0, p1);
+    window_range(x, g.pad_w, g.S, g.str_w, g.Q, q0, q1);
+    const Vec<T, V> own = *reinterpret_cast<const Vec<T, V>*>(I + i * V);
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.0f;
+    for (int k = k0; k <= k1; ++k)
+      for (int m = m0; m <= m1; ++m)
+        for (int p = p0; p <= p1; ++p)
+          for (int q = q0; q <= q1; ++q) {
+            const long long o = ((((1ll * k * g.M + m) * g.P + p) * g.Q + q) * g.N) + nv * V;
+            const Vec<T, V> e = *reinterpret_cast<const Vec<T, V>*>(E + o);
+            if (op == POOL_AVG) {
+#pragma unroll
+              for (int j = 0; j < V; ++j) acc[j] += e.get(j) * inv;
+            } else {
+              float sq[V];
+              window_sum<T, V>(g, I, k, m, p, q, nv, true, sq);
+#pragma unroll
+              for (int j = 0; j < V; ++j) {
+                // the forward pass stored the norm rounded to T: divide by that value
+                Vec<T, 1> o1;
+                o1.set(0, sqrtf(sq[j]));
+                const float norm = o1.get(0);
+                if (norm > 0.0f) acc[j] += e.get(j) * own.get(j) / norm;
+              }
+            }
+          }
+    Vec<T, V> out;
+#pragma unroll
+    for (int j = 0; j < V; ++j) out.set(j, acc[j]);
+    *reinterpret_cast<Vec<T, V>*>(dI + i * V) = out;
+  }
+}
+
+template <typename T, int VW>
+int run_pool_op(const PoolGeo& g, int op, const void* I, const void* E, void* out, bool backward, DeviceCtx* c,
+                cudaStream_t stream) {
+  const bool vec = g.N % VW == 0 && (reinterpret_cast<uintptr_t>(I) & 15u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(E) & 15u) == 0 && (reinterpret_cast<uintptr_t>(out) & 15u) == 0;
+  const long long out_elems = 1ll * g.K * g.M * g.P * g.Q * g.N;
+  const long long in_elems = 1ll * g.C * g.D * g.H * g.W * g.N;
+  const T* in = static_cast<const T*>(I);
+  if (!backward) {
+    if (vec) pool_fprop_op_kernel<T, VW><<<grid_for(out_elems / VW, c), 256, 0, stream>>>(g, op, in, static_cast<T*>(out));
+    else pool_fprop_op_kernel<T, 1><<<grid_for(out_elems, c), 256, 0, stream>>>(g, op, in, static_cast<T*>(out));
+  } else {
+    const T* err = static_cast<const T*>(E);
+    if (vec) pool_bprop_op_kernel<T, VW><<<grid_for(in_elems / VW, c), 256, 0, stream>>>(g, op, in, err, static_cast<T*>(out));
+    else pool_bprop_op_kernel<T, 1><<<grid_for(in_elems, c), 256, 0, stream>>>(g, op, in, err, static_cast<T*>(out));
+  }
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
+
 bool tiles_exactly(const PoolGeo& g) {
   return g.pad_j == 0 && g.pad_d == 0 && g.pad_h == 0 && g.pad_w == 0 && g.str_j == g.J && g.str_d == g.T &&
          g.str_h == g.R && g.str_w == g.S && g.C % g.J == 0 && g.D % g.T == 0 && g.H % g.R == 0 && g.W % g.S == 0;
@@ -680,6 +816,35 @@ int ng_pool_bprop(const ng_pool_desc* d, int dtype_bytes, const void* I, const v
   if (!c) return NG_ERR_CUDA;
   if (dtype_bytes == 2) return run_pool<__half, 8>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
   if (dtype_bytes == 4) return run_pool<float, 4>(g, I, E, gradI, 1, c, static_cast<cudaStream_t>(stream));
+  return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+int ng_pool_fprop_op(const ng_pool_desc* d, int op, int dtype_bytes, const void* I, void* O, void* stream) {
+  if (op == POOL_MAX) return ng_pool_fprop(d, dtype_bytes, I, O, stream);
+  if (op != POOL_AVG && op != POOL_L2) return fail(NG_ERR_INVALID_ARG, "pooling op must be 0 (max), 1 (avg) or 2 (l2)");
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !O) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (dtype_bytes == 2) return run_pool_op<__half, 8>(g, op, I, nullptr, O, false, c, static_cast<cudaStream_t>(stream));
+  if (dtype_bytes == 4) return run_pool_op<float, 4>(g, op, I, nullptr, O, false, c, static_cast<cudaStream_t>(stream));
+  return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
+}
+
+int ng_pool_bprop_op(const ng_pool_desc* d, int op, int dtype_bytes, const void* I, const void* E, void* gradI,
+                     void* stream) {
+  if (op == POOL_MAX) return ng_pool_bprop(d, dtype_bytes, I, E, gradI, stream);
+  if (op != POOL_AVG && op != POOL_L2) return fail(NG_ERR_INVALID_ARG, "pooling op must be 0 (max), 1 (avg) or 2 (l2)");
+  PoolGeo g;
+  int rc = make_pool_geo(d, g);
+  if (rc != NG_OK) return rc;
+  if (!I || !E || !gradI) return fail(NG_ERR_INVALID_ARG, "null tensor");
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (dtype_bytes == 2) return run_pool_op<__half, 8>(g, op, I, E, gradI, true, c, static_cast<cudaStream_t>(stream));
+  if (dtype_bytes == 4) return run_pool_op<float, 4>(g, op, I, E, gradI, true, c, static_cast<cudaStream_t>(stream));
   return fail(NG_ERR_UNSUPPORTED, "pooling supports fp16 and fp32 tensors");
 }
 

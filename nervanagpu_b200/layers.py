@@ -309,9 +309,10 @@ class DeconvLayer(ConvLayer):
 
 
 class PoolLayer(Layer):
-    """Pooling parameters: windows (J,T,R,S) over (C,D,H,W); only max pooling runs on the device
-    (the reference accepts "avg" and "l2" too but launches its max kernel for every op,
-    nervanagpu/nervanagpu.py:797)."""
+    """Pooling parameters: windows (J,T,R,S) over (C,D,H,W); op is "max", "avg" or "l2". (The
+    reference accepts all three but launches its max kernel for every op,
+    nervanagpu/nervanagpu.py:797, and defines avg / l2 in numpy only, benchmarks/pool_test.py:141-146;
+    here each runs its own kernel.)"""
 
     def __init__(self, lib, dtype, op, N, C, D=1, H=1, W=1, J=1, T=1, R=1, S=1, pad_j=0, pad_d=0, pad_h=0,
                  pad_w=0, str_j=None, str_d=None, str_h=None, str_w=None):

@@ -584,6 +584,8 @@ class NervanaGPU(object):
 
     def pool_argmax_bytes(self, layer, dtype=np.float16):
         """Size of the buffer fprop_pool(..., argmax=) fills, or 0 when this layer has no such path."""
+        if getattr(layer, "op", "max") != "max":
+            return 0
         n = ctypes.c_size_t()
         _lib.check(self.lib.ng_pool_argmax_bytes(ctypes.byref(layer.desc), np.dtype(dtype).itemsize, ctypes.byref(n)))
         return n.value
@@ -613,7 +615,17 @@ class NervanaGPU(object):
             raise TypeError("pooling supports fp16 and fp32 tensors")
         desc = ctypes.byref(layer.desc)
         lib, stream, esz = self.lib, self.stream, I.dtype.itemsize
-        if argmax is not None:
+        op = {"max": 0, "avg": 1, "l2": 2}[getattr(layer, "op", "max")]
+        if op != 0:
+            # avg / l2: defined by the reference in numpy only (benchmarks/pool_test.py:141-146); its
+            # device path runs the max kernel for them (nervanagpu/nervanagpu.py:797)
+            if argmax is not None or mode == 2:
+                raise ValueError("argmax records and the fused ReLU mask exist for max pooling only")
+            if mode == 0:
+                launch = lambda: _lib.check(lib.ng_pool_fprop_op(desc, op, esz, I.ptr, O.ptr, stream))
+            else:
+                launch = lambda: _lib.check(lib.ng_pool_bprop_op(desc, op, esz, I.ptr, O.ptr, B.ptr, stream))
+        elif argmax is not None:
             assert argmax.nbytes >= layer.sizeO
             if mode == 0:
                 launch = lambda: _lib.check(lib.ng_pool_fprop_argmax(desc, esz, I.ptr, O.ptr, argmax.ptr, stream))

@@ -298,6 +298,51 @@ def pool_max(pd, I, E=None):
     return O, gradI
 
 
+def pool_avg_l2(pd, I, op, E=None):
+    """Average / L2 pooling forward as the reference's numpy model defines them
+    (benchmarks/pool_test.py:141-146): np.mean, and np.sqrt(np.sum(x**2)), over ALL J*T*R*S window
+    positions, positions outside the tensor reading the zero padding row (pool_test.py:57-58,100-101).
+
+    The reference has no backward pass for these ops ("bprop not implemented yet", pool_test.py:140);
+    when E is given this returns the derivative of the forward definition: gradI += E / (J*T*R*S)
+    for avg, gradI += E * I / O for l2 with O as the forward pass stored it (rounded to `O_dtype`
+    of pd, default fp16) and nothing where O is 0. Accumulation in fp32, windows in (k,m,p,q) order.
+    Returns (O, gradI)."""
+    assert op in ("avg", "l2")
+    I2 = np.zeros(_slicable(pd.dimI, 1), dtype=np.float32)
+    I2[:-1, :] = np.asarray(I, dtype=np.float32).reshape(_slicable(pd.dimI))
+    O = np.empty(pd.dimO, dtype=np.float32)
+    B = np.zeros(_slicable(pd.dimI, 1), dtype=np.float32)
+    if E is not None:
+        E = np.asarray(E, dtype=np.float32).reshape(pd.dimO)
+    out_dtype = getattr(pd, "O_dtype", np.float16)
+    M, P, Q = pd.MPQ
+    pad_j, pad_d, pad_h, pad_w = pd.padding
+    str_j, str_d, str_h, str_w = pd.strides
+    for k in range(pd.K):
+        for m in range(M):
+            for p in range(P):
+                for q in range(Q):
+                    rows = np.array(_pool_pixel_rows(pd, k * str_j - pad_j, m * str_d - pad_d,
+                                                     p * str_h - pad_h, q * str_w - pad_w))
+                    window = I2[rows, :]
+                    if op == "avg":
+                        O[k, m, p, q, :] = np.mean(window, axis=0)
+                    else:
+                        O[k, m, p, q, :] = np.sqrt(np.sum(window ** 2, axis=0))
+                    if E is not None:
+                        if op == "avg":
+                            contrib = np.broadcast_to(E[k, m, p, q, :] / np.float32(len(rows)), window.shape)
+                        else:
+                            norm = O[k, m, p, q, :].astype(out_dtype).astype(np.float32)
+                            safe = np.where(norm > 0, norm, np.float32(1))
+                            contrib = np.where(norm > 0, E[k, m, p, q, :] * window / safe, np.float32(0))
+                        np.add.at(B, rows, contrib.astype(np.float32))
+    B[-1, :] = 0
+    gradI = B[:-1, :].reshape(pd.dimI) if E is not None else None
+    return O, gradI
+
+
 # ---------------------------------------------------------------------------------------------
 # element-wise
 # ---------------------------------------------------------------------------------------------

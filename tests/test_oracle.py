@@ -107,3 +107,36 @@ def test_fp16_neighbours():
     assert float(lo[3]) <= 3e-6 <= float(hi[3]) and float(hi[3]) - float(lo[3]) == 2.0 ** -24
     assert lo[4] == hi[4] == np.float16(65504.0)
     assert lo[5] == hi[5] == 0
+
+
+@pytest.mark.parametrize("op", ["avg", "l2"])
+def test_pool_avg_l2_oracle_follows_the_reference_numpy_definition(op):
+    """benchmarks/pool_test.py:141-146: mean / root-sum-square over all window positions, the
+    positions outside the tensor reading zeros. Checked against plain loops on a padded case."""
+    pd = rm.PoolDims(4, 3, 1, 5, 5, 1, 1, 3, 3, 0, 0, 1, 1, 1, 1, 2, 2)
+    rng = np.random.default_rng(5)
+    I = rng.uniform(-1, 1, pd.dimI).astype(np.float32)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float32)
+    O, gradI = rm.pool_avg_l2(pd, I, op, E)
+    M, P, Q = pd.MPQ
+    want = np.zeros(pd.dimO, np.float32)
+    grad = np.zeros(pd.dimI, np.float32)
+    for k in range(pd.K):
+        for p in range(P):
+            for q in range(Q):
+                pos = [(k, 0, p * 2 - 1 + r, q * 2 - 1 + s) for r in range(3) for s in range(3)]
+                vals = [I[c, z, y, x, :] if 0 <= y < 5 and 0 <= x < 5 else np.zeros(4, np.float32)
+                        for (c, z, y, x) in pos]
+                if op == "avg":
+                    want[k, 0, p, q] = sum(vals) / 9.0
+                else:
+                    want[k, 0, p, q] = np.sqrt(sum(v * v for v in vals))
+                norm = want[k, 0, p, q].astype(np.float16).astype(np.float32)
+                for (c, z, y, x), v in zip(pos, vals):
+                    if 0 <= y < 5 and 0 <= x < 5:
+                        if op == "avg":
+                            grad[c, z, y, x] += E[k, 0, p, q] / 9.0
+                        else:
+                            grad[c, z, y, x] += np.where(norm > 0, E[k, 0, p, q] * v / np.where(norm > 0, norm, 1), 0)
+    assert np.allclose(O, want, rtol=1e-6, atol=1e-7)
+    assert np.allclose(gradI, grad, rtol=1e-5, atol=1e-6)

@@ -129,3 +129,35 @@ def test_full_size_alexnet_pool1_properties(ng):
     refO, refB = rm.pool_max(sub, I[5:7], E[5:7])
     assert np.array_equal(O[5:7], refO.astype(np.float16))
     assert np.array_equal(B[5:7], refB.astype(np.float16))
+
+
+@pytest.mark.parametrize("op", ["avg", "l2"])
+@pytest.mark.parametrize("name", sorted(CASES))
+def test_avg_and_l2_pooling_against_oracle(ng, name, op):
+    """The ops the reference defines in numpy only (benchmarks/pool_test.py:141-146). Forward: the
+    fp32 result rounded to fp16 (one ulp of slack for the order of the fp32 additions); backward:
+    the derivative of the forward definition, tolerance 2 fp16 ulps of the largest term sum."""
+    cfg = CASES[name]
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(77)
+    I = rng.uniform(-1, 1, pd.dimI).astype(np.float16)
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float16)
+    refO, refB = rm.pool_avg_l2(pd, I, op, E)
+    layer = ng.pool_layer(np.float16, op, *cfg)
+    dI, dE = ng.array(I), ng.array(E)
+    dO, dB = ng.empty(layer.dimO), ng.empty(layer.dimI)
+    ng.fprop_pool(layer, dI, dO)
+    ng.bprop_pool(layer, dI, dE, dB)
+    O, B = dO.get().astype(np.float32), dB.get().astype(np.float32)
+    assert np.all(np.abs(O - refO) <= 2.0 ** -10 * np.maximum(np.abs(refO), 2.0 ** -14))
+    windows = np.prod(pd.JTRS)
+    assert np.all(np.abs(B - refB) <= 2.0 ** -9 * np.maximum(np.abs(refB), 1.0) * max(1, windows // 4))
+    assert np.abs(B).sum() > 0
+
+
+def test_avg_and_l2_refuse_the_max_only_extensions(ng):
+    cfg = CASES["vgg_2x2_n32"]
+    layer = ng.pool_layer(np.float16, "avg", *cfg)
+    dI, dE, dB = ng.empty(layer.dimI), ng.empty(layer.dimO), ng.empty(layer.dimI)
+    with pytest.raises(ValueError):
+        ng.bprop_pool(layer, dI, dE, dB, relu_mask=True)
