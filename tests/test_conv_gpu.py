@@ -79,6 +79,13 @@ CASES = {
     # update: two 48-row taps stacked per accumulator, 192-column tiles
     "c48_k384_stacked_taps": (64, 48, 384, 1, 6, 6, 1, 3, 3, 0, 1, 1, 1, 1, 1),
     "c64_k192_5x5_n128": (128, 64, 192, 1, 7, 7, 1, 5, 5, 0, 2, 2, 1, 1, 1),
+    # tap blocks with two image groups per pixel (one box per pixel), update with exchanged operands
+    "c3_11x11_stride4_n128": (128, 3, 64, 1, 27, 27, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    # 256 output rows: filter halves as single boxes, column tiles as single boxes (N = 64),
+    # and a width (6) that makes some tiles straddle image rows
+    "c64_k256_w6_merged_boxes": (64, 64, 256, 1, 6, 6, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    # K = 96: the first-layer update keeps the filters on the MMA rows (K <= 128), one column tile
+    "c3_7x7_stride2_k96": (64, 3, 96, 1, 21, 21, 1, 7, 7, 0, 3, 3, 1, 2, 2),
 }
 
 
