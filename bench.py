@@ -32,7 +32,7 @@ METRIC = "alexnet_conv_stack_fprop_bprop_update_tflops"
 UNIT = "TFLOP/s"
 # dram__bytes_read.sum + dram__bytes_write.sum per igemm_tc_kernel launch, from the ncu capture summarised
 # in profiles/igemm_tc_kernel_alexnet_step_traffic.md (not measurable from inside this script)
-TRAFFIC_BYTES_PER_CONV_LAUNCH = {("alexnet", 128): 28.04e6}
+TRAFFIC_BYTES_PER_CONV_LAUNCH = {("alexnet", 128): 27.92e6}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
