@@ -267,8 +267,12 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
 // Threads that share one 8-column group of the split-K reduction: more when the output is small
 // and the partitions many, so that the device is filled and no thread walks a long chain.
 static int splitk_reduce_lanes(long long groups, int splits, int sm_count) {
+  static const char* force = getenv("NG_REDUCE_LANES");   // tuning aid: 1, 2, 4, ... 32
+  if (force && atoi(force) >= 1 && atoi(force) <= 32 && (atoi(force) & (atoi(force) - 1)) == 0) return atoi(force);
   int lanes = 1;
-  while (lanes < 32 && lanes * 4 <= splits && groups * lanes < sm_count * 2048ll) lanes *= 2;
+  // only as many as it takes to occupy the SMs: with more, every thread holds fewer loads in flight
+  // and the launch becomes several waves of short threads (AlexNet conv5: 49 -> 38 us for update + sum)
+  while (lanes < 32 && lanes * 4 <= splits && groups * lanes < sm_count * 384ll) lanes *= 2;
   return lanes;
 }
 
