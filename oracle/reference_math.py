@@ -217,6 +217,101 @@ def conv_bprop_fast(cd, F, E, alpha=1.0):
 
 
 # ---------------------------------------------------------------------------------------------
+# convolution at sampled positions (for shapes whose whole im2col matrix would not fit in memory)
+# ---------------------------------------------------------------------------------------------
+def conv_pixel_rows_np(cd, mt, pr, qs):
+    """_conv_pixel_rows without the Python loops: the same (c,t,r,s)-ordered row numbers, taps
+    outside the image pointing at the padding row (conv_test.py:99-130)."""
+    T, R, S = cd.TRS
+    D, H, W = cd.DHW
+    C = cd.C
+    z = (mt + np.arange(T))[:, None, None]
+    y = (pr + np.arange(R))[None, :, None]
+    x = (qs + np.arange(S))[None, None, :]
+    ok = (z >= 0) & (z < D) & (y >= 0) & (y < H) & (x >= 0) & (x < W)
+    rows = np.where(ok, z * (H * W) + y * W + x, -1)
+    full = np.arange(C)[:, None, None, None] * (D * H * W) + rows[None]
+    full = np.where(rows[None] >= 0, full, C * D * H * W)
+    return full.reshape(-1)
+
+
+def conv_fprop_pixels(cd, I, F, pixels, alpha=1.0, relu=False, absolute=False):
+    """The per-pixel arithmetic of conv_test.py:147-161 at the output pixels `pixels`, a list of
+    (m, p, q): returns an array (len(pixels), K, N) with O[:, m, p, q, :] of each. With
+    `absolute` the operands are replaced by their magnitudes (scale of the rounding-error bound)."""
+    I2 = _padded_input(cd, I)
+    F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
+    if absolute:
+        I2, F2 = np.abs(I2), np.abs(F2)
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    out = np.empty((len(pixels), cd.K, cd.N), dtype=np.float32)
+    for i, (m, p, q) in enumerate(pixels):
+        rows = conv_pixel_rows_np(cd, m * str_d - pad_d, p * str_h - pad_h, q * str_w - pad_w)
+        out[i] = np.dot(F2.T, I2[rows, :])
+    out *= np.float32(alpha)
+    if relu:
+        out = np.maximum(out, np.float32(0))
+    return out
+
+
+def conv_bprop_pixels(cd, F, E, positions, alpha=1.0, absolute=False):
+    """Input gradient at the input positions `positions`, a list of (z, y, x): the sum that the
+    scatter of conv_test.py:163-164 leaves there, gathered: every output pixel (m,p,q) and tap
+    (t,r,s) with m*str_d - pad_d + t == z (and likewise y, x) adds F[:, t,r,s, :] @ E[:, m,p,q, :].
+    Returns (len(positions), C, N)."""
+    T, R, S = cd.TRS
+    M, P, Q = cd.MPQ
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    F4 = np.asarray(F, dtype=np.float32).reshape(cd.C, T * R * S, cd.K)
+    E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, M * P * Q, cd.N)
+    if absolute:
+        F4, E2 = np.abs(F4), np.abs(E2)
+    out = np.zeros((len(positions), cd.C, cd.N), dtype=np.float32)
+    for i, (z, y, x) in enumerate(positions):
+        taps, pix = [], []
+        for t in range(T):
+            mz = z + pad_d - t
+            if mz < 0 or mz % str_d or mz // str_d >= M:
+                continue
+            for r in range(R):
+                py = y + pad_h - r
+                if py < 0 or py % str_h or py // str_h >= P:
+                    continue
+                for s in range(S):
+                    qx = x + pad_w - s
+                    if qx < 0 or qx % str_w or qx // str_w >= Q:
+                        continue
+                    taps.append((t * R + r) * S + s)
+                    pix.append(((mz // str_d) * P + py // str_h) * Q + qx // str_w)
+        if taps:
+            Fs = F4[:, taps, :].reshape(cd.C, -1)                       # (C, taps*K)
+            Es = E2[:, pix, :].transpose(1, 0, 2).reshape(-1, cd.N)     # (taps*K, N)
+            out[i] = np.dot(Fs, Es)
+    return out * np.float32(alpha)
+
+
+def conv_update_taps(cd, I, E, taps, alpha=1.0, absolute=False):
+    """Weight gradient of the filter taps `taps`, a list of (t, r, s): the sum over all output
+    pixels of conv_test.py:166-167 restricted to those taps. Returns (len(taps), C, K)."""
+    C, D, H, W, N = cd.dimI
+    M, P, Q = cd.MPQ
+    pad_d, pad_h, pad_w = cd.padding
+    str_d, str_h, str_w = cd.strides
+    Ip = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
+    Ip[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] = np.asarray(I, dtype=np.float32).reshape(cd.dimI)
+    E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, -1)
+    if absolute:
+        Ip, E2 = np.abs(Ip), np.abs(E2)
+    out = np.empty((len(taps), C, cd.K), dtype=np.float32)
+    for i, (t, r, s) in enumerate(taps):
+        sl = Ip[:, t:t + M * str_d:str_d, r:r + P * str_h:str_h, s:s + Q * str_w:str_w, :].reshape(C, -1)
+        out[i] = np.dot(sl, E2.T)
+    return out * np.float32(alpha)
+
+
+# ---------------------------------------------------------------------------------------------
 # pooling
 # ---------------------------------------------------------------------------------------------
 class PoolDims(object):
@@ -295,6 +390,47 @@ def pool_max(pd, I, E=None):
                         hit = rows[np.argmax(window, axis=0)]
                         B[hit, cols] += E[k, m, p, q, :]
     gradI = B[:-1, :].reshape(pd.dimI) if E is not None else None
+    return O, gradI
+
+
+def pool_max_fast(pd, I, E=None):
+    """pool_max for the large configurations: the same windows in the same (m,p,q) order, all
+    feature maps of a window position at once. Needs windows that do not overlap along the
+    feature-map axis (J == 1, or J == str_j with no padding and C a multiple of J), so that the
+    order in which the maps are visited cannot change any sum. Cross-checked against pool_max."""
+    J, T, R, S = pd.JTRS
+    C, D, H, W, N = pd.dimI
+    pad_j, pad_d, pad_h, pad_w = pd.padding
+    str_j, str_d, str_h, str_w = pd.strides
+    assert (J == 1 and str_j == 1 and pad_j == 0) or (J == str_j and pad_j == 0 and C % J == 0)
+    K = pd.K
+    M, P, Q = pd.MPQ
+    I6 = np.asarray(I, dtype=np.float32).reshape(K, J, D, H, W, N)
+    O = np.empty(pd.dimO, dtype=np.float32)
+    B = np.zeros((K, J, D, H, W, N), dtype=np.float32) if E is not None else None
+    if E is not None:
+        E = np.asarray(E, dtype=np.float32).reshape(pd.dimO)
+    kk = np.arange(K)[:, None]
+    nn = np.arange(N)[None, :]
+    for m in range(M):
+        z0, z1 = max(m * str_d - pad_d, 0), min(m * str_d - pad_d + T, D)
+        for p in range(P):
+            y0, y1 = max(p * str_h - pad_h, 0), min(p * str_h - pad_h + R, H)
+            for q in range(Q):
+                x0, x1 = max(q * str_w - pad_w, 0), min(q * str_w - pad_w + S, W)
+                tz, ty, tx = z1 - z0, y1 - y0, x1 - x0
+                win = I6[:, :, z0:z1, y0:y1, x0:x1, :].reshape(K, J * tz * ty * tx, N)
+                if win.shape[1] == 0:
+                    O[:, m, p, q, :] = np.finfo(np.float32).min
+                    continue
+                O[:, m, p, q, :] = win.max(axis=1)
+                if E is not None:
+                    hit = win.argmax(axis=1)                      # first maximum in (j,t,r,s) order
+                    j, rem = np.divmod(hit, tz * ty * tx)
+                    dz, rem = np.divmod(rem, ty * tx)
+                    dy, dx = np.divmod(rem, tx)
+                    B[kk, j, z0 + dz, y0 + dy, x0 + dx, nn] += E[:, m, p, q, :]
+    gradI = B.reshape(pd.dimI) if E is not None else None
     return O, gradI
 
 

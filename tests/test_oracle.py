@@ -140,3 +140,49 @@ def test_pool_avg_l2_oracle_follows_the_reference_numpy_definition(op):
                             grad[c, z, y, x] += np.where(norm > 0, E[k, 0, p, q] * v / np.where(norm > 0, norm, 1), 0)
     assert np.allclose(O, want, rtol=1e-6, atol=1e-7)
     assert np.allclose(gradI, grad, rtol=1e-5, atol=1e-6)
+
+
+SAMPLED_CONV = [(16, 5, 8, 1, 9, 7, 1, 3, 3, 0, 1, 1, 1, 2, 1), (8, 4, 8, 4, 6, 6, 3, 3, 3, 1, 1, 1, 1, 1, 1),
+                (8, 3, 8, 1, 23, 23, 1, 11, 11, 0, 2, 2, 1, 4, 4)]
+
+
+@pytest.mark.parametrize("cfg", SAMPLED_CONV)
+def test_sampled_conv_oracle_equals_the_loop_form(cfg):
+    """The per-position functions used at full size against the loops of conv_test.py:147-167."""
+    cd = rm.ConvDims(*cfg)
+    rng = np.random.default_rng(3)
+    I = rng.uniform(0, 1, cd.dimI).astype(np.float16)
+    F = rng.normal(0, 0.1, cd.dimF).astype(np.float16)
+    E = rng.uniform(-1, 1, cd.dimO).astype(np.float16)
+    (M, P, Q), (D, H, W), (T, R, S) = cd.MPQ, cd.DHW, cd.TRS
+    pix = [(0, 0, 0), (M - 1, P - 1, Q - 1), (M // 2, P // 2, Q // 2)]
+    for m, p, q in pix:
+        args = (cd, m * cd.strides[0] - cd.padding[0], p * cd.strides[1] - cd.padding[1],
+                q * cd.strides[2] - cd.padding[2])
+        assert list(rm.conv_pixel_rows_np(*args)) == rm._conv_pixel_rows(*args)
+    O = rm.conv_fprop(cd, I, F)
+    for got, (m, p, q) in zip(rm.conv_fprop_pixels(cd, I, F, pix), pix):
+        np.testing.assert_array_equal(got, O[:, m, p, q, :])
+    B = rm.conv_bprop(cd, F, E)
+    pos = [(0, 0, 0), (D - 1, H - 1, W - 1), (D // 2, H // 2, W // 3), (0, 1, 2)]
+    for got, (z, y, x) in zip(rm.conv_bprop_pixels(cd, F, E, pos), pos):
+        np.testing.assert_allclose(got, B[:, z, y, x, :], rtol=0, atol=1e-4)
+    U = rm.conv_update(cd, I, E)
+    taps = [(0, 0, 0), (T - 1, R - 1, S - 1), (T // 2, R // 2, S // 2)]
+    for got, (t, r, s) in zip(rm.conv_update_taps(cd, I, E, taps), taps):
+        np.testing.assert_allclose(got, U[:, t, r, s, :], rtol=1e-5, atol=1e-4)
+
+
+@pytest.mark.parametrize("cfg", [(16, 8, 1, 13, 13, 1, 1, 3, 3, 0, 0, 0, 0, 1, 1, 2, 2),
+                                 (8, 8, 4, 6, 6, 2, 2, 2, 2, 0, 0, 0, 0, 2, 2, 2, 2),
+                                 (16, 5, 1, 9, 9, 1, 1, 3, 3, 0, 0, 1, 1, 1, 1, 2, 2),
+                                 (8, 2, 1, 9, 9, 1, 1, 2, 2, 0, 0, 0, 0, 1, 1, 3, 3)])
+def test_fast_pool_oracle_is_bit_identical_to_the_loop_form(cfg):
+    pd = rm.PoolDims(*cfg)
+    rng = np.random.default_rng(4)
+    I = (rng.integers(0, 12, pd.dimI) / 8.0).astype(np.float16)      # many ties
+    E = rng.uniform(-1, 1, pd.dimO).astype(np.float16)
+    O, B = rm.pool_max(pd, I, E)
+    O2, B2 = rm.pool_max_fast(pd, I, E)
+    np.testing.assert_array_equal(O, O2)
+    np.testing.assert_array_equal(B, B2)
