@@ -59,13 +59,26 @@ int ng_event_destroy(void* event);
 int ng_event_record(void* event, void* stream);
 int ng_event_sync(void* event);
 int ng_event_elapsed_ms(void* start, void* end, float* ms);
-/* Synchronise the device, then report (and clear) the device status word: NG_ERR_TIMEOUT if a
- * kernel abandoned one of its bounded waits. */
+/* Synchronise the device, then report (and clear) the device status words: NG_ERR_TIMEOUT if a
+ * kernel abandoned one of its bounded waits (kernels of ng_hgemm_static_scratch included). */
 int ng_sync(void);
 int ng_device_status(int* code);
+/* Every wait inside the kernels is bounded (2 s by default): a kernel whose wait runs out records
+ * the site, unwinds and returns; ng_sync / ng_device_status then report NG_ERR_TIMEOUT and the
+ * context stays usable. ng_set_wait_limit_ns changes the bound for later launches on the current
+ * device (0 = default). ng_test_wait_expires launches one thread that waits, for at most
+ * limit_ns (<= 100 ms), on a barrier nothing arrives at, so that tests can see the error path
+ * work; waited_ns (device memory, may be NULL) receives how long it waited. Neither has a
+ * counterpart in the reference, whose kernels do not wait on anything. */
+int ng_set_wait_limit_ns(unsigned long long limit_ns);
+int ng_test_wait_expires(unsigned long long limit_ns, unsigned long long* waited_ns, void* stream);
 /* Number of kernels this library has launched so far in this process (its own kernels and the
  * generated element-wise ones; memcpy / memset / NCCL calls are not counted). */
 int ng_launch_count(unsigned long long* count);
+/* Number of GEMM / convolution calls so far that ran on the plain CUDA-core fall-back kernels
+ * (operands TMA cannot address, strided layers with fewer than 64 images) instead of the
+ * tensor-core engine. A benchmark that claims the tensor-core path checks that this stays 0. */
+int ng_fallback_launch_count(unsigned long long* count);
 
 /* Record-and-replay of a sequence of calls (a CUDA graph). The reference drives every kernel
  * with its own pycuda launch (nervanagpu/nervanagpu.py:642-734, 959-1105) and has nothing like
@@ -73,7 +86,10 @@ int ng_launch_count(unsigned long long* count);
  * Between begin and end, the library's calls on `stream` (not the default stream) are recorded,
  * not run; the sequence must have run once before, so that scratch memory has its final size and
  * generated kernels are compiled. A replay repeats the recorded pointers, scalars and random
- * offsets; ng_launch_count counts the kernels of every replay. */
+ * offsets; ng_launch_count counts the kernels of every replay. A recording also keeps the
+ * library's scratch pointers of its calls: if a later, larger call on the same stream makes the
+ * scratch grow, the old buffer stays allocated until the last recording is destroyed
+ * (ng_graph_destroy), so replays stay valid. */
 int ng_graph_capture_begin(void* stream);
 int ng_graph_capture_end(void* stream, void** graph);
 int ng_graph_launch(void* graph, void* stream);
@@ -102,21 +118,25 @@ int ng_hgemm_batched(const void* A, const void* B, void* C, int a_t, int b_t, in
 
 /* ng_hgemm for callers that must not allocate device memory. It has no counterpart in the
  * reference. Same arguments and result contract as ng_hgemm, restricted to operands TMA can
- * address (16-byte aligned, leading dimensions multiples of 8), always computed as a split-K
- * product whose fp32 partial tiles live in a fixed device array inside the library instead of
- * the cudaMalloc'ed workspace ng_hgemm grows on demand. The call makes no cudaMalloc / cudaFree
- * and calls no allocating routine.
+ * address (16-byte aligned, leading dimensions multiples of 8), computed as a split-K product
+ * (when k > 64; a single 64-wide block of k is stored directly) whose fp32 partial tiles live in
+ * a fixed device array inside the library instead of the cudaMalloc'ed workspace ng_hgemm grows
+ * on demand. The call makes no cudaMalloc / cudaFree and calls no allocating routine.
  *   - limit: 2 * m * n * 4 bytes must fit in NG_STATIC_SCRATCH_BYTES, else NG_ERR_TOO_LARGE;
  *   - the array costs NG_STATIC_SCRATCH_BYTES of memory on every GPU that loads the library;
  *   - the first call on each device looks up the array's device address (and sets a function
  *     attribute); make that first call outside any stream capture;
  *   - all calls share the one array: calls that can overlap on the GPU (different streams or
  *     threads) race on it; issue them on one stream or serialise them yourself. Nothing in the
- *     array has to start at zero: every call overwrites the part it later reads. */
+ *     array has to start at zero: every call overwrites the part it later reads;
+ *   - its kernels' bounded waits report through a status word in the same fixed memory:
+ *     ng_sync / ng_device_status include it, and ng_static_scratch_status reads (and clears) it
+ *     alone, without allocating anything (it copies four bytes and so waits for the device). */
 #define NG_STATIC_SCRATCH_BYTES (16u << 20)
 int ng_hgemm_static_scratch(const void* A, const void* B, void* C, int a_t, int b_t, int m, int n, int k, int lda,
                             int ldb, int ldc, float alpha, float beta, int relu, int sr_bits,
                             unsigned long long seed, unsigned int rng_offset, void* stream);
+int ng_static_scratch_status(int* code);
 
 /* ---- convolution ---------------------------------------------------------------------------
  * Activations are (C,D,H,W,N), filters (C,T,R,S,K), outputs (K,M,P,Q,N), all fp16, N innermost.

@@ -65,7 +65,11 @@ SIGNATURES = {
     "ng_event_elapsed_ms": (c_int, [c_void_p, c_void_p, ctypes.POINTER(c_float)]),
     "ng_sync": (c_int, []),
     "ng_device_status": (c_int, [ctypes.POINTER(c_int)]),
+    "ng_set_wait_limit_ns": (c_int, [c_ulonglong]),
+    "ng_test_wait_expires": (c_int, [c_ulonglong, c_void_p, c_void_p]),
+    "ng_static_scratch_status": (c_int, [ctypes.POINTER(c_int)]),
     "ng_launch_count": (c_int, [ctypes.POINTER(c_ulonglong)]),
+    "ng_fallback_launch_count": (c_int, [ctypes.POINTER(c_ulonglong)]),
     "ng_graph_capture_begin": (c_int, [c_void_p]),
     "ng_graph_capture_end": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "ng_graph_launch": (c_int, [c_void_p, c_void_p]),

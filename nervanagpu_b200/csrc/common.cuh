@@ -70,13 +70,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Every wait in these kernels is bounded: after kWaitLimitNs without progress the waiter
-// raises the CTA-wide abort flag, records `code` in the global status word (first error
-// wins) and returns false; callers unwind to the common teardown.
+// Every wait in these kernels is bounded: after `limit_ns` without progress (kWaitLimitNs unless
+// the host set another limit) the waiter raises the CTA-wide abort flag, records `code` in the
+// global status word (first error wins) and returns false; callers unwind to the common teardown.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;
 
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
-                                          int* status, int code) {
+                                          int* status, int code, uint64_t limit_ns = kWaitLimitNs) {
   // The clock stays off the path of a wait that ends soon: it is first read after 1024 failed
   // polls (each of which already blocks for a while in hardware), and the limit counts from there.
   uint64_t t0 = 0;
@@ -87,7 +87,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
       const uint64_t now = global_timer_ns();
       if (t0 == 0) {
         t0 = now;
-      } else if (now - t0 > kWaitLimitNs) {
+      } else if (now - t0 > limit_ns) {
         *abort_flag = 1;
         atomicCAS(status, 0, code);
         return false;

@@ -10,7 +10,11 @@
 //   bprop   D[C x DHWN]   = F[c][k] per tap (K-major A)  *  E pixels reached through the tap (MN-major B)
 //   update  D[C x K]/tap  = I pixels under the tap (K-major A)  *  E (K-major B), reduction over (m,p,q,n)
 // A 64-element chunk of the pixel space is either 64 images of one pixel (N % 64 == 0) or, when
-// the W stride is 1, 64 consecutive elements of the flattened (x, n) dimension.
+// the W stride is 1, 64 consecutive elements of the flattened (x, n) dimension of one image row
+// (several pixels of a small minibatch, e.g. the shard of a minibatch that is split over GPUs).
+// Image rows that are not a multiple of 64 elements are padded to whole chunks: the last chunk of
+// a row runs past its end, where TMA zero-fills (or, between rows of the input, reads pixels
+// whose products land in columns that are never stored).
 // Small-C weight updates run as im2col + tensor-core GEMM; shapes neither path can address run
 // on plain SIMT kernels so that every legal call still executes on the GPU.
 #include <algorithm>
@@ -59,10 +63,24 @@ bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) ==
 
 // chunking of a (m,p,q,n)-like pixel space with innermost extents (xdim, N)
 enum ChunkMode { CH_NONE = 0, CH_PIXEL = 1, CH_FLAT = 2 };
-ChunkMode pick_chunk_mode(int N, int xdim, int str_w) {
+ChunkMode pick_chunk_mode(int N, int str_w) {
   if (N % kChunk == 0) return CH_PIXEL;
-  if (str_w == 1 && (1ll * xdim * N) % kChunk == 0) return CH_FLAT;
+  if (str_w == 1) return CH_FLAT;
   return CH_NONE;
+}
+// chunks per image row of `xdim` pixels
+int row_chunks(int N, int xdim, ChunkMode mode) {
+  return mode == CH_FLAT ? static_cast<int>((1ll * xdim * N + kChunk - 1) / kChunk) : xdim * (N / kChunk);
+}
+// Columns of the GEMM view of a (rows, xdim, N) pixel space, and (flattened mode with ragged
+// rows) the mapping of its padded columns to memory.
+long long pixel_columns(TcParams& p, long long rows, int xdim, int N, ChunkMode mode) {
+  const int cpr = row_chunks(N, xdim, mode);
+  if (mode == CH_FLAT && (1ll * xdim * N) % kChunk != 0) {
+    p.c_row_chunks = cpr;
+    p.c_row_len = xdim * N;
+  }
+  return rows * cpr * kChunk;
 }
 
 // tensor map over an activation tensor (chan, z, y, x, n) seen as (n | x*n, x | 1, y, z, chan)
@@ -86,8 +104,7 @@ int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int
 // chunk, each [box_chan rows][64], as the per-chunk boxes of act_map would. Returns the value for
 // TcParams::b_merge, 0 when the shape has no such map.
 int act_map_merged(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, uint32_t box_chan, int nb) {
-  static const bool off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;   // tuning aid
-  if (off || N % kChunk != 0 || nb < 2) return 0;
+  if (tuning().merge_boxes == 0 || N % kChunk != 0 || nb < 2) return 0;
   const int cpi = N / kChunk;
   const uint64_t xn = 1ull * X * N * 2;
   uint64_t dims[5], str[4];
@@ -137,15 +154,15 @@ void fill_taps(TcParams& p, const Geo& g, ChunkMode mode) {
 }
 
 void fill_decode(TcParams& p, int N, int X, int Y, int Z, ChunkMode mode) {
-  p.dec_cpi = mode == CH_FLAT ? (X * N) / kChunk : N / kChunk;
+  p.dec_cpi = mode == CH_FLAT ? row_chunks(N, X, mode) : N / kChunk;
   p.dec_q = mode == CH_FLAT ? 1 : X;
   p.dec_p = Y;
   p.dec_m = Z;
 }
 
 int pick_kb_rows(int C) {
-  static const char* force = getenv("NG_KB_ROWS");   // tuning aid: 16, 32, 48 or 64
-  if (force && atoi(force) >= 16 && atoi(force) <= 64 && atoi(force) % 16 == 0) return atoi(force);
+  const int force = tuning().kb_rows;
+  if (force >= 16 && force <= 64 && force % 16 == 0) return force;
   int best = 64, best_pad = ((C + 63) / 64) * 64;
   for (int r : {48, 32, 16}) {
     const int pad = ((C + r - 1) / r) * r;
@@ -321,16 +338,14 @@ struct TapBlock {
 // Taps with at most 64 rows are also stacked along the 128 rows of one accumulator (`acc_taps`
 // boxes of a_rows rows each), which halves (or better) the MMAs a tap costs.
 void set_update_groups(TcParams& p, int taps, int a_rows) {
-  static const char* cap = getenv("NG_UPDATE_GROUPS");   // tuning aid: limits on groups / stacking
-  static const char* cap_t = getenv("NG_UPDATE_STACK");
+  const int cap = tuning().update_groups, cap_t = tuning().update_stack;   // limits on groups / stacking
   int t = std::max(1, std::min(std::min(kTileM / a_rows, 8), taps));
-  if (cap_t) t = std::max(1, std::min(t, atoi(cap_t)));
+  if (cap_t > 0) t = std::max(1, std::min(t, cap_t));
   const int accs = (taps + t - 1) / t;                    // accumulators the whole filter needs
   int g = std::min(std::min(8, 512 / p.block_n), accs);
-  if (cap) g = std::max(1, std::min(g, atoi(cap)));
+  if (cap > 0) g = std::max(1, std::min(g, cap));
   const int ring = 232448 - 1024 - 512 - static_cast<int>(kEpiStageBytes) - kTileM * 128;
-  static const char* min_stages_env = getenv("NG_UPDATE_MIN_STAGES");
-  const int min_stages = min_stages_env ? std::max(2, atoi(min_stages_env)) : 3;
+  const int min_stages = tuning().update_min_stages > 0 ? std::max(2, tuning().update_min_stages) : 3;
   while (g > 1 && ((g * t * a_rows * 128 + p.block_n * 128) * min_stages > ring || g * t > 24)) --g;
   // the taps (not the accumulators) are spread evenly over the work items: 9 taps on items of at
   // most 6 become 5 + 4, not 6 + 3
@@ -440,7 +455,7 @@ int fprop_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I
   tc_pick_tile_rows(c, p, p.tiles_n, p.num_kb);
   // fewer, larger boxes: the filters of a 128-row half as one box (K a multiple of 64), the two
   // image groups of a pixel as one box (N = 128, 2-D)
-  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  const bool merge_off = tuning().merge_boxes == 0;
   lay.a_merge = !merge_off && g.K % kChunk == 0 && g.K > kChunk;
   lay.a_chunks = (g.K + kChunk - 1) / kChunk;
   lay.b_pair = !merge_off && g.N == 2 * kChunk && g.D == 1;
@@ -551,7 +566,7 @@ int update_tapblock_swapped(DeviceCtx* c, const Geo& g, const TapBlock& tb, cons
 
 int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* I, const void* E, void* gradF,
                     int out_f32, float alpha, cudaStream_t stream) {
-  static const bool swap_ok = !(getenv("NG_UPDATE_SWAP") && atoi(getenv("NG_UPDATE_SWAP")) == 0);
+  const bool swap_ok = tuning().update_swap != 0;
   // (worth it when the tap blocks fill at least half of a 256-column tile)
   if (swap_ok && g.K <= kTileM && g.T * tb.nr * tb.ns * tb.rows >= 128)
     return update_tapblock_swapped(c, g, tb, I, E, gradF, out_f32, alpha, stream);
@@ -620,7 +635,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   DeviceCtx* c = current_ctx();
   if (!c) return NG_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const ChunkMode mode = pick_chunk_mode(g.N, g.Q, g.str_w);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.str_w);
   const bool al = aligned16(I) && aligned16(F) && aligned16(O);
   const bool tc = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al;
   if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
@@ -654,15 +669,18 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
     }
   }
   if (!tc) {
+    count_fallback_launch();
     conv_fprop_simt<<<launch_1d(g.sizeO(), 256, c), 256, 0, stream>>>(
         g, static_cast<const __half*>(I), static_cast<const __half*>(F), static_cast<__half*>(O), alpha, relu);
     NG_CHECK_LAUNCH();
     return NG_OK;
   }
   const int RST = g.T * g.R * g.S;
-  const long long cols = 1ll * g.M * g.P * g.Q * g.N;
+  const long long ldo = 1ll * g.M * g.P * g.Q * g.N;
   TcParams p = {};
   p.mode = TC_FPROP;
+  const long long cols = pixel_columns(p, 1ll * g.M * g.P, g.Q, g.N, mode);
+  if (cols > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "output too large");
   p.M = g.K; p.N = static_cast<int>(cols);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {1, 1, pick_kb_rows(g.C)};
@@ -672,7 +690,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   CUtensorMap mapA, mapB, mapBm;
   // fewer, larger boxes where the shapes allow: the filters of a 128-row half as one box, the
   // pixels of a column tile inside one image row as one box
-  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  const bool merge_off = tuning().merge_boxes == 0;
   lay.a_merge = !merge_off && g.K % kChunk == 0 && g.K > kChunk &&
                 filter_map_merged(&mapA, F, g, lay.kb_rows) == NG_OK;
   lay.a_chunks = (g.K + kChunk - 1) / kChunk;
@@ -680,7 +698,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.Q, g.P, g.M, mode);
   p.oob_y = g.H;
-  p.C = O; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
+  p.C = O; p.Cold = nullptr; p.ldc = ldo; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = relu; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
   if (!lay.a_merge) {
     rc = filter_map(&mapA, F, g, lay.kb_rows);
@@ -702,20 +720,23 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   DeviceCtx* c = current_ctx();
   if (!c) return NG_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const ChunkMode mode = pick_chunk_mode(g.N, g.W, g.str_w);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.str_w);
   // in flattened mode the E row (Q*N) is addressed with the same element offsets as the dI row
   const bool tc = path != NG_PATH_SIMT && mode != CH_NONE && aligned16(F) && aligned16(E) && aligned16(gradI);
   if (path == NG_PATH_TENSOR && !tc) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
   if (!tc) {
+    count_fallback_launch();
     conv_bprop_simt<<<launch_1d(g.sizeI(), 256, c), 256, 0, stream>>>(
         g, static_cast<const __half*>(F), static_cast<const __half*>(E), static_cast<__half*>(gradI), alpha);
     NG_CHECK_LAUNCH();
     return NG_OK;
   }
   const int RST = g.T * g.R * g.S;
-  const long long cols = 1ll * g.D * g.H * g.W * g.N;
+  const long long ldi = 1ll * g.D * g.H * g.W * g.N;
   TcParams p = {};
   p.mode = TC_BPROP;
+  const long long cols = pixel_columns(p, 1ll * g.D * g.H, g.W, g.N, mode);
+  if (cols > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "output too large");
   p.M = g.C; p.N = static_cast<int>(cols);
   p.nz = 1; p.splits = 1;
   TcOperandLayout lay = {0, 1, kChunk};
@@ -729,7 +750,7 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   fill_taps(p, g, mode);
   fill_decode(p, g.N, g.W, g.H, g.D, mode);
   p.oob_y = g.P;
-  p.C = gradI; p.Cold = nullptr; p.ldc = cols; p.c_zstride = 0;
+  p.C = gradI; p.Cold = nullptr; p.ldc = ldi; p.c_zstride = 0;
   p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = 0; p.vec_ok = 1;
   CUtensorMap mapA, mapB, mapBm;
   rc = filter_map(&mapA, F, g, a_rows);
@@ -751,7 +772,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   DeviceCtx* c = current_ctx();
   if (!c) return NG_ERR_CUDA;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_);
-  const ChunkMode mode = pick_chunk_mode(g.N, g.Q, g.str_w);
+  const ChunkMode mode = pick_chunk_mode(g.N, g.str_w);
   const bool al = aligned16(I) && aligned16(E) && aligned16(gradF);
   const int RST = g.T * g.R * g.S;
   const long long span = 1ll * g.M * g.P * g.Q * g.N;
@@ -773,7 +794,9 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     p.tiles_n = (g.K + p.block_n - 1) / p.block_n;
     p.nz = RST;
     TcOperandLayout lay = {0, 0, kChunk};
-    p.num_kb = static_cast<int>(span / kChunk);
+    // one k-block per chunk of the (m, p, q, n) space; ragged image rows are padded to whole
+    // chunks, whose tail TMA zero-fills in the error tensor
+    p.num_kb = g.M * g.P * row_chunks(g.N, g.Q, mode);
     // the reduction is split to fill the SMs whatever the tile count, so only the operand
     // traffic argues: assume many column tiles
     tc_pick_tile_rows(c, p, 64ll * p.tiles_n * p.nz, p.num_kb);
@@ -819,6 +842,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     return run_gemm(gc, stream);
   }
   const long long warps = g.sizeF();
+  count_fallback_launch();
   conv_update_simt<<<launch_1d(warps * 32, 256, c), 256, 0, stream>>>(
       g, static_cast<const __half*>(I), static_cast<const __half*>(E), gradF, out_f32, alpha);
   NG_CHECK_LAUNCH();

@@ -140,6 +140,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     s.az = g.az; s.bz = g.bz; s.cz = g.cz; s.loops = g.loops; s.alz = g.alz; s.blz = g.blz;
     s.out_f32 = g.out_f32; s.ea = ea;
     dim3 grid((g.n + 63) / 64, (g.m + 63) / 64, g.batch);
+    count_fallback_launch();
     gemm_simt_kernel<<<grid, 256, 0, stream>>>(s);
     NG_CHECK_LAUNCH();
     return NG_OK;
@@ -159,7 +160,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
   lay.kb_rows = kChunk;
   // an operand whose contiguous dimension is m (or n), a multiple of 64: the map gets the 64-wide
   // chunk number as a dimension of its own, and one box brings a 128-row half (a column tile)
-  static const bool merge_off = getenv("NG_MERGE_BOXES") && atoi(getenv("NG_MERGE_BOXES")) == 0;
+  const bool merge_off = tuning().merge_boxes == 0;
   lay.a_merge = !merge_off && g.a_t && g.m % kChunk == 0;
   lay.b_merge_static = !merge_off && !g.b_t && g.n % kChunk == 0 && p.block_n >= 2 * kChunk;
   tc_fill_mma(p, lay);

@@ -1,6 +1,7 @@
 // Host-side internals shared by the translation units of libnervana_b200.so.
 #pragma once
 #include <map>
+#include <vector>
 #include <cuda.h>
 #include <cuda_runtime.h>
 #include <stddef.h>
@@ -25,10 +26,27 @@ struct DeviceCtx {
   std::map<cudaStream_t, Scratch> scratch;
   float* ws = nullptr;
   size_t ws_bytes = 0;
+  // Recorded sequences (CUDA graphs) keep the scratch pointers of the calls they recorded: while
+  // any is alive, a scratch buffer that has to grow is retired (kept allocated), not freed.
+  int live_graphs = 0;
+  std::vector<void*> retired;
   bool smem_attr_set = false;
+  unsigned long long wait_limit_ns = 2000000000ull;   // bound of the kernels' waits (ng_set_wait_limit_ns)
   bool capturing = false;    // a stream capture is open: nothing may allocate or synchronise
   unsigned long long capture_launches0 = 0;
 };
+
+// Tuning aids, read from the environment once per process (none is needed in normal use):
+// NG_TILE_ROWS=128|256, NG_TILE_COLS=128|192|256, NG_KB_ROWS=16|32|48|64, NG_MERGE_BOXES=0,
+// NG_SPLIT_TAIL=0, NG_LEAN_KERNELS=0, NG_REDUCE_LANES=<power of two>, NG_UPDATE_GROUPS=<n>,
+// NG_UPDATE_STACK=<n>, NG_UPDATE_MIN_STAGES=<n>, NG_UPDATE_SWAP=0, NG_PAIR_MMA=0|1. A field is 0
+// (or -1 for the on/off switches) when its variable is not set.
+struct Tuning {
+  int tile_rows = 0, tile_cols = 0, kb_rows = 0, reduce_lanes = 0;
+  int update_groups = 0, update_stack = 0, update_min_stages = 0;
+  int merge_boxes = -1, split_tail = -1, lean_kernels = -1, update_swap = -1, pair_mma = -1;
+};
+const Tuning& tuning();
 
 // Error reporting: returns `code` after storing a printf-style message for ng_last_error().
 int fail(int code, const char* fmt, ...);
@@ -42,11 +60,17 @@ int cuda_fail(cudaError_t e, const char* what);
 
 // Count of kernels this library has launched (all devices, all streams); read by ng_launch_count.
 void count_launch();
+// Count of GEMM / convolution calls that ran on the plain CUDA-core fall-back kernels instead of
+// the tensor-core engine; read by ng_fallback_launch_count.
+void count_fallback_launch();
 #define NG_CHECK_LAUNCH()            \
   do {                               \
     NG_CUDA(cudaGetLastError());     \
     ::ngb::count_launch();           \
   } while (0)
+
+// Status word of ng_hgemm_static_scratch on device `dev`, read and cleared without allocating.
+int static_scratch_status(int dev, int* code);
 
 // Context of the current device (initialised on first use). Null + error set on failure.
 DeviceCtx* current_ctx();

@@ -96,18 +96,20 @@ struct TcParams {
   int sr_bits;                     // 0 = round to nearest even, else mantissa bits kept
   int out_f32;
   int vec_ok;                      // rows are 16-byte aligned for vector access
-  int tma_store;                   // 1: tiles leave through shared memory + bulk tensor stores
-  int c_box_cols;                  // columns per store box (128 bytes worth: 64 fp16 / 32 fp32)
+  int store_staged;                // 1: tiles leave through swizzled shared memory, written out in
+                                   // whole 128-byte rows; 0: stored straight from registers
+  int c_box_cols;                  // columns per staged box (128 bytes worth: 64 fp16 / 32 fp32)
+  // Convolution outputs over a flattened (x, n) pixel space whose image rows are not a multiple
+  // of 64 elements: the column space is padded to c_row_chunks chunks per image row, of which
+  // the first c_row_len elements exist in memory (row r starts at column r * c_row_len of C).
+  // 0 = columns are stored as they are numbered.
+  int c_row_chunks, c_row_len;
   uint32_t seed_lo, seed_hi, rng_offset;
   float* ws;                       // split-K partials [split][z][M][N] when splits > 1
   int* status;                     // device status word
   // divisors of the tile / chunk / tap decodes, filled in by the launch code
-  FastDiv fd_tiles_m, fd_tiles_n, fd_nz, fd_cpi, fd_q, fd_p, fd_RS, fd_S, fd_red;
-  // Development builds (-DNG_TC_TIMELINE) only: %globaltimer stamps of the first CTAs' roles,
-  // [cta][tile][slot]; null otherwise.
-  unsigned long long* timeline;
+  FastDiv fd_tiles_m, fd_tiles_n, fd_nz, fd_cpi, fd_q, fd_p, fd_RS, fd_S, fd_red, fd_crow;
+  unsigned long long wait_limit_ns;   // bound of every wait inside the kernel
 };
-
-constexpr int kTimelineCtas = 4, kTimelineTiles = 24, kTimelineSlots = 20;
 
 }  // namespace ngb

@@ -28,43 +28,6 @@
 #include "common.cuh"
 #include "epilogue.cuh"
 
-// Development aid, compiled out unless -DNG_TC_TIMELINE: the first CTAs stamp %globaltimer at the
-// hand-offs between their roles (slots: 0/1 first/last copy of a tile issued, 2 accumulator free,
-// 3 first operands landed, 4 last MMA issued, 5 epilogue starts, 6 epilogue done).
-#ifdef NG_TC_TIMELINE
-#define NG_STAMP(tile, slot)                                                                      \
-  do {                                                                                            \
-    if (p.timeline && blockIdx.x < kTimelineCtas && (tile) < kTimelineTiles)                      \
-      p.timeline[(blockIdx.x * kTimelineTiles + (tile)) * kTimelineSlots + (slot)] = global_timer_ns(); \
-  } while (0)
-// cycle counters of the staged epilogue (warp 2): NG_CLK(k) adds the cycles since the previous
-// NG_CLK to bucket k (1: TMEM load, 2: convert + stage, 3: write-out, 0: everything else)
-#define NG_CLK(k)                                   \
-  do {                                              \
-    const long long now_ = clock64();               \
-    clk_acc[k] += now_ - clk_last;                  \
-    clk_last = now_;                                \
-  } while (0)
-// cycle buckets of the MMA issuer (slots 12: wait for operands, 13: issue, 14: commit) and of the
-// producer (slots 15: wait for a free slot, 16: coordinates + issue), summed over a tile
-#define NG_ROLE_CLK(acc)                            \
-  do {                                              \
-    const long long now_ = clock64();               \
-    (acc) += now_ - role_last;                      \
-    role_last = now_;                               \
-  } while (0)
-#define NG_ROLE_PUT(tile, slot, v)                                                                \
-  do {                                                                                            \
-    if (p.timeline && blockIdx.x < kTimelineCtas && (tile) < kTimelineTiles)                      \
-      p.timeline[(blockIdx.x * kTimelineTiles + (tile)) * kTimelineSlots + (slot)] = (v);          \
-  } while (0)
-#else
-#define NG_STAMP(tile, slot) do {} while (0)
-#define NG_CLK(k) do {} while (0)
-#define NG_ROLE_CLK(acc) do {} while (0)
-#define NG_ROLE_PUT(tile, slot, v) do {} while (0)
-#endif
-
 namespace ngb {
 
 namespace {
@@ -168,17 +131,16 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 template <int kMode, bool kLean>
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
-                const __grid_constant__ CUtensorMap mapC, const __grid_constant__ CUtensorMap mapBm,
-                const __grid_constant__ TcParams p) {
+                const __grid_constant__ CUtensorMap mapBm, const __grid_constant__ TcParams p) {
   extern __shared__ uint8_t smem_raw[];
   // ring buffer must be 1024-byte aligned for the 128-byte swizzle pattern
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   uint8_t* smem_gen = smem_raw + (smem_base - smem_u32(smem_raw));
   const uint32_t ring_bytes = static_cast<uint32_t>(p.stages) * p.stage_bytes;
-  // output staging (bulk-store epilogue only), then the control block
+  // output staging (staged epilogue only), then the control block
   const uint32_t epi_base = smem_base + ring_bytes;
-  const int store_mode = kLean ? 2 : p.tma_store;
-  const uint32_t epi_bytes = store_mode ? kEpiStageBytes : 0u;
+  const bool staged = kLean || p.store_staged != 0;
+  const uint32_t epi_bytes = staged ? kEpiStageBytes : 0u;
 
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem_gen + ring_bytes + epi_bytes);
   const uint32_t bar_base = smem_base + ring_bytes + epi_bytes;
@@ -209,7 +171,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (warp == 0 && lane == 0) {
     tma_prefetch_desc(&mapA);
     tma_prefetch_desc(&mapB);
-    if (store_mode == 1) tma_prefetch_desc(&mapC);
     if (p.b_merge == 1 || p.b_merge == 2) tma_prefetch_desc(&mapBm);
   }
   if (warp == 1) {
@@ -233,8 +194,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    int ptile = 0;
-    (void)ptile;
     for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
       const WorkItem it = decode_work(p, w);
       if (it.live == 0) continue;
@@ -375,45 +334,23 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       };
       // (Asking the L2 for the boxes of later k-blocks with prefetch copies was tried and was
       // slower everywhere: a prefetch costs the copy engine as much as the load it precedes.)
-#ifdef NG_TC_TIMELINE
-      long long role_last = clock64(), c_pwait = 0, c_pissue = 0, c_psync = 0, c_ptma = 0, c_padv = 0;
-#endif
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
         if (act) coords(wk, c0, c1, c2, c3, c4);
-        NG_ROLE_CLK(c_pissue);
-        const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER);
-        NG_ROLE_CLK(c_pwait);
+        const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER, p.wait_limit_ns);
         if (lane == 0 && got) mbar_expect_tx(full_bar(stage), tx_item);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
-        NG_ROLE_CLK(c_psync);
         if (act) {
           tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
-        NG_ROLE_CLK(c_ptma);
-        if (lane == 0) {
-          if (kb == it.kb0) NG_STAMP(ptile, 0);       // first copy of the tile issued
-          if (kb == it.kb1 - 1) NG_STAMP(ptile, 1);   // last copy of the tile issued
-        }
         advance(wk);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-        NG_ROLE_CLK(c_padv);
       }
-#ifdef NG_TC_TIMELINE
-      if (lane == 0) {
-        NG_ROLE_PUT(ptile, 15, c_pwait);
-        NG_ROLE_PUT(ptile, 16, c_pissue);
-        NG_ROLE_PUT(ptile, 17, c_psync);
-        NG_ROLE_PUT(ptile, 18, c_ptma);
-        NG_ROLE_PUT(ptile, 19, c_padv);
-      }
-#endif
-      ++ptile;
     }
   } else if (warp == 1) {
     // =========================== MMA issuer ===========================
@@ -441,20 +378,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           halves = min(p.acc_groups, (taps_here + p.acc_taps - 1) / p.acc_taps);
         }
         if (!wide) {
-          if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC)) break;
+          if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC, p.wait_limit_ns)) break;
           tc_fence_after();
         }
-        NG_STAMP(local, 2);                           // accumulator is free
-#ifdef NG_TC_TIMELINE
-        long long role_last = clock64(), c_mwait = 0, c_missue = 0, c_mcommit = 0;
-#endif
         for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA)) {
+          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA, p.wait_limit_ns)) {
             ok = false;
             break;
           }
-          NG_ROLE_CLK(c_mwait);
-          if (kb == it.kb0) NG_STAMP(local, 3);       // first operands have landed
           tc_fence_after();
           const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
           const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
@@ -462,7 +393,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           const uint32_t acc_first = kb > it.kb0 ? 1u : 0u;
           for (int h = 0; h < halves; ++h) {
             if (wide && kb == it.kb0) {   // half h of the previous tile must have been drained
-              ok = mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC);
+              ok = mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC, p.wait_limit_ns);
               if (!ok) break;
               tc_fence_after();
             }
@@ -477,16 +408,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             }
           }
           if (!ok) break;
-          NG_ROLE_CLK(c_missue);
           tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs have read it
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-          NG_ROLE_CLK(c_mcommit);
         }
-        NG_ROLE_PUT(local, 12, c_mwait);
-        NG_ROLE_PUT(local, 13, c_missue);
-        NG_ROLE_PUT(local, 14, c_mcommit);
         if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
-        NG_STAMP(local, 4);                           // last MMA of the tile issued
         ++local;
       }
     }
@@ -523,12 +448,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (it.live == 0) continue;
       const int acc = (wide || grouped) ? 0 : (local & 1);
       const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
-      if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE)) break;
-      if (warp == 2 && lane == 0) NG_STAMP(local, 5);   // accumulator complete, epilogue starts
-#ifdef NG_TC_TIMELINE
-      long long clk_acc[4] = {0, 0, 0, 0};
-      long long clk_last = clock64();
-#endif
+      if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE, p.wait_limit_ns)) break;
       tc_fence_after();
       const int n0 = it.tile_n * p.block_n;
       for (int h = 0; h < n_acc; ++h) {
@@ -575,11 +495,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           oldrow = p.Cold ? static_cast<const uint8_t*>(p.Cold) + off * esz : nullptr;
           lin_row = (static_cast<unsigned long long>(zt) * p.M + row) * static_cast<unsigned long long>(p.N);
         }
-        if (store_mode) {
+        if (staged) {
           // Staged path: 32 rows x 128 bytes per box, written to shared memory in the 128-byte
           // swizzle pattern (16-byte chunk j of row t lands at chunk j ^ (t & 7): conflict-free
-          // for the per-row writes below), then one bulk tensor store per box. The store clips
-          // rows >= M and columns >= N itself.
+          // for the per-row writes below), then written out by the warp in whole 128-byte rows.
           const int epi_warp = warp - 2;
           const int zc = partial ? it.split * p.nz_out + zt_warp : zt_warp;
           const int subs = p.c_box_cols / 32;            // tcgen05.ld groups per box: 2 (fp16) or 1 (fp32)
@@ -591,23 +510,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             const int colb = n0 + cb * p.c_box_cols;
             for (int sub = 0; sub < subs; ++sub) {
               uint32_t r[32];
-              NG_CLK(0);
               tc_ld_32x32(taddr + static_cast<uint32_t>(cb * p.c_box_cols + sub * 32), r);
               tc_wait_ld();
-#ifdef NG_TC_TIMELINE
-              {   // touch every loaded register so that the load's real latency lands in bucket 1
-                uint32_t x = 0;
-#pragma unroll
-                for (int i = 0; i < 32; ++i) x ^= r[i];
-                if (x == 0x9e3779b9u) clk_acc[0] += 1;
-              }
-#endif
-              NG_CLK(1);
-              if (sub == 0 && store_mode == 1) {
-                // the previous store from this warp's buffer must have read it before we overwrite
-                if (lane == 0) tma_store_wait_read<0>();
-                __syncwarp();
-              }
               const uint32_t rowb = buf + static_cast<uint32_t>(lane) * 128u;
               const uint32_t swz = static_cast<uint32_t>(lane & 7);
               // (no "memory" clobber on the staging stores: they are ordered with the loads of the
@@ -672,19 +576,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 }
               }
             }
-            NG_CLK(2);
-            if (store_mode == 1) {
-              fence_async_smem();
-              __syncwarp();
-              if (lane == 0) {
-                if (colb < p.N && row0 < p.M && zt_warp < p.nz_out) tma_store_5d(&mapC, buf, colb, row0, zc, 0, 0);
-                tma_store_commit();
-              }
-            } else {
+            {
               // Write-out by the warp itself: each instruction stores four whole 128-byte rows
-              // (lane = row within the group of four, 16-byte chunk). A bulk tensor store would
-              // queue behind the operand loads of the copy engine, and the wait for it to release
-              // the staging buffer then costs ~2 us per box.
+              // (lane = row within the group of four, 16-byte chunk). (A bulk tensor store would
+              // queue behind the operand loads of the copy engine; the wait for it to release the
+              // staging buffer then cost ~2 us per box.)
               __syncwarp();
               const int esz = f32 ? 4 : 2;
               uint8_t* gbase;
@@ -697,8 +593,18 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 gstride = p.ldc * esz;
               }
               const int j = lane & 7;
-              const int gcol = colb + j * (16 / esz);
-              const bool col_live = gcol < p.N && zt_warp < p.nz_out;
+              int gcol = colb + j * (16 / esz);
+              bool col_live = gcol < p.N && zt_warp < p.nz_out;
+              if (kConvOut && p.c_row_chunks) {
+                // Flattened pixel space whose image rows are padded to whole 64-element chunks:
+                // this box is chunk `ch` of the padded space; it holds elements [cq * 64, +64) of
+                // image row r, of which only those below c_row_len exist in memory.
+                const int ch = colb >> 6;
+                const int r = fast_div(ch, p.fd_crow);
+                const int cq = ch - r * p.c_row_chunks;
+                gcol = r * p.c_row_len + cq * kChunk + j * 8;
+                col_live = col_live && cq * kChunk + j * 8 < p.c_row_len;
+              }
               uint8_t* gp = gbase + (row0 + (lane >> 3)) * gstride + static_cast<long long>(gcol) * esz;
               uint4 v[8];
 #pragma unroll
@@ -714,14 +620,14 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                 gp += 4 * gstride;
               }
               __syncwarp();   // the buffer is free for the next box
-              NG_CLK(3);
             }
           }
         }
         const int n_chunks = p.block_n / 32;
         const int c_begin = col_group == 0 ? 0 : (n_chunks + 1) / 2;
         const int c_end = col_group == 0 ? (n_chunks + 1) / 2 : n_chunks;
-        for (int c = c_begin; !store_mode && half_live && c < c_end; ++c) {
+        const bool from_regs = !kLean && !staged;   // (lean instances always stage)
+        for (int c = c_begin; from_regs && half_live && c < c_end; ++c) {
           uint32_t r[32];
           tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
           tc_wait_ld();
@@ -750,7 +656,6 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           tc_fence_before();
           __syncwarp();
           if (lane == 0) mbar_arrive(acce_bar(h));
-          if (warp == 2 && lane == 0 && h == 0) NG_STAMP(local, 7);   // first half handed back
         }
       }
       if (!wide) {
@@ -758,16 +663,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(acce_bar(acc));
       }
-      if (warp == 2 && lane == 0) NG_STAMP(local, 6);   // this warp's share of the tile is stored
-#ifdef NG_TC_TIMELINE
-      if (warp == 2 && lane == 0 && p.timeline && blockIdx.x < kTimelineCtas && local < kTimelineTiles)
-        for (int k = 0; k < 4; ++k)
-          p.timeline[(blockIdx.x * kTimelineTiles + local) * kTimelineSlots + 8 + k] = clk_acc[k];
-#endif
       ++local;
     }
-    // outstanding bulk stores must be complete before the CTA (and its shared memory) goes away
-    if (store_mode == 1 && lane == 0) tma_store_wait_all();
   }
 
   // =========================== teardown ===========================

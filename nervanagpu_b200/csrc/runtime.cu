@@ -29,8 +29,34 @@ int cuda_fail(cudaError_t e, const char* what) {
   return fail(NG_ERR_CUDA, "CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
 }
 
+const Tuning& tuning() {
+  static Tuning t;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    auto num = [](const char* name, int unset) {
+      const char* v = getenv(name);
+      return v && *v ? atoi(v) : unset;
+    };
+    t.tile_rows = num("NG_TILE_ROWS", 0);
+    t.tile_cols = num("NG_TILE_COLS", 0);
+    t.kb_rows = num("NG_KB_ROWS", 0);
+    t.reduce_lanes = num("NG_REDUCE_LANES", 0);
+    t.update_groups = num("NG_UPDATE_GROUPS", 0);
+    t.update_stack = num("NG_UPDATE_STACK", 0);
+    t.update_min_stages = num("NG_UPDATE_MIN_STAGES", 0);
+    t.merge_boxes = num("NG_MERGE_BOXES", -1);
+    t.split_tail = num("NG_SPLIT_TAIL", -1);
+    t.lean_kernels = num("NG_LEAN_KERNELS", -1);
+    t.update_swap = num("NG_UPDATE_SWAP", -1);
+    t.pair_mma = num("NG_PAIR_MMA", -1);
+  });
+  return t;
+}
+
 static std::atomic<unsigned long long> g_launches{0};
 void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+static std::atomic<unsigned long long> g_fallback_launches{0};
+void count_fallback_launch() { g_fallback_launches.fetch_add(1, std::memory_order_relaxed); }
 
 static std::mutex g_ctx_mutex;
 static DeviceCtx g_ctx[64];
@@ -79,9 +105,13 @@ int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes) {
       return fail(NG_ERR_UNSUPPORTED,
                   "the workspace would have to grow during a capture: run the sequence once before recording it");
     }
-    // growing: earlier launches may still read the old buffer
+    // growing: earlier launches may still read the old buffer, and so does every replay of a
+    // recorded sequence that was recorded with it
     NG_CUDA(cudaDeviceSynchronize());
-    if (s.ptr) NG_CUDA(cudaFree(s.ptr));
+    if (s.ptr) {
+      if (c->live_graphs > 0) c->retired.push_back(s.ptr);
+      else NG_CUDA(cudaFree(s.ptr));
+    }
     s.ptr = nullptr;
     s.bytes = 0;
     size_t want = bytes + (bytes >> 2);
@@ -306,16 +336,26 @@ int ng_device_status(int* code) {
   int v = 0;
   NG_CUDA(cudaMemcpy(&v, c->status, sizeof(int), cudaMemcpyDeviceToHost));
   if (code) *code = v;
-  if (v != 0) {
-    cudaMemset(c->status, 0, sizeof(int));
-    return fail(NG_ERR_TIMEOUT, "a kernel gave up a bounded wait (site %d)", v);
-  }
+  if (v != 0) cudaMemset(c->status, 0, sizeof(int));
+  // kernels launched by ng_hgemm_static_scratch report through a status word of their own
+  int vs = 0;
+  const int rc = static_scratch_status(c->device, &vs);
+  if (rc != NG_OK) return rc;
+  if (v == 0) v = vs;
+  if (code) *code = v;
+  if (v != 0) return fail(NG_ERR_TIMEOUT, "a kernel gave up a bounded wait (site %d)", v);
   return NG_OK;
 }
 
 int ng_launch_count(unsigned long long* count) {
   if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
   *count = g_launches.load(std::memory_order_relaxed);
+  return NG_OK;
+}
+
+int ng_fallback_launch_count(unsigned long long* count) {
+  if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
+  *count = g_fallback_launches.load(std::memory_order_relaxed);
   return NG_OK;
 }
 
@@ -330,6 +370,7 @@ int ng_sync(void) {
 // offsets of the calls; replaying it costs one launch on the host.
 struct NgGraph {
   cudaGraphExec_t exec = nullptr;
+  DeviceCtx* ctx = nullptr;
   unsigned long long kernels = 0;   // kernel launches one replay stands for
 };
 
@@ -364,6 +405,8 @@ int ng_graph_capture_end(void* stream, void** graph_out) {
   }
   const unsigned long long now = g_launches.load(std::memory_order_relaxed);
   g->kernels = now - c->capture_launches0;
+  g->ctx = c;
+  ++c->live_graphs;
   // the recorded launches did not run
   g_launches.fetch_sub(g->kernels, std::memory_order_relaxed);
   *graph_out = g;
@@ -382,6 +425,11 @@ int ng_graph_destroy(void* graph) {
   NgGraph* g = static_cast<NgGraph*>(graph);
   if (!g) return NG_OK;
   if (g->exec) NG_CUDA(cudaGraphExecDestroy(g->exec));
+  if (g->ctx && --g->ctx->live_graphs == 0) {
+    // scratch buffers that recordings were still pointing at
+    for (void* ptr : g->ctx->retired) cudaFree(ptr);
+    g->ctx->retired.clear();
+  }
   delete g;
   return NG_OK;
 }

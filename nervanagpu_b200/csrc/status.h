@@ -16,3 +16,4 @@
 #define NG_DEV_TIMEOUT_MMA 102
 #define NG_DEV_TIMEOUT_EPILOGUE 103
 #define NG_DEV_TIMEOUT_ACC 104
+#define NG_DEV_TIMEOUT_TEST 105

@@ -48,6 +48,7 @@ static void fill_fast_divs(TcParams& p) {
   p.fd_RS = make_fast_div(p.RS);
   p.fd_S = make_fast_div(p.S);
   p.fd_red = make_fast_div(p.red_chunks);
+  p.fd_crow = make_fast_div(p.c_row_chunks);
 }
 
 // Bytes a K-major A descriptor may read past its (short) slot; kept inside the allocation.
@@ -137,42 +138,29 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
                                                p.stage_bytes);
 }
 
-// How tiles leave the epilogue: 2 = staged through swizzled shared memory and written out by the
-// warps in whole 128-byte rows (default), 1 = staged and written by bulk tensor stores over a
-// (columns, rows, z) map of C or of the split-K workspace (NG_TMA_STORE=1: measured slower, the
-// stores queue behind the operand loads), 0 = straight from registers (output not 16-byte
-// addressable, or NG_TMA_STORE=0).
-static int pick_store_mode(CUtensorMap* map, TcParams& p) {
-  static const char* sel = getenv("NG_TMA_STORE");
-  if (sel && sel[0] == '0') return 0;
-  const bool bulk = sel && sel[0] == '1';
+// How tiles leave the epilogue: 1 = staged through swizzled shared memory and written out by the
+// warps in whole 128-byte rows, 0 = straight from registers (output not 16-byte addressable).
+static int pick_store_mode(TcParams& p) {
   if ((p.N & 7) != 0) return 0;
   // stacked taps: a warp's 32 rows must belong to one tap
   if (p.acc_taps > 1 && (p.pack_rows & 31) != 0) return 0;
   const bool partial = p.splits > 1;
   const int esz = (partial || p.out_f32) ? 4 : 2;
-  uint64_t dims[5] = {static_cast<uint64_t>(p.N), static_cast<uint64_t>(p.M), 1, 1, 1};
-  uint64_t str[4];
+  uint64_t row_bytes, z_bytes;
   const void* base;
   if (partial) {
     base = p.ws;
-    dims[2] = static_cast<uint64_t>(p.nz_out) * p.splits;
-    str[0] = static_cast<uint64_t>(p.N) * 4;
-    str[1] = str[0] * p.M;
+    row_bytes = static_cast<uint64_t>(p.N) * 4;
+    z_bytes = row_bytes * p.M;
   } else {
     if (!p.vec_ok) return 0;
     base = p.C;
-    dims[2] = p.nz_out;
-    str[0] = static_cast<uint64_t>(p.ldc) * esz;
-    str[1] = p.nz_out > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : str[0] * p.M;
-    if (str[1] == 0) return 0;
+    row_bytes = static_cast<uint64_t>(p.ldc) * esz;
+    z_bytes = p.nz_out > 1 ? static_cast<uint64_t>(p.c_zstride) * esz : row_bytes * p.M;
+    if (z_bytes == 0) return 0;
   }
-  str[2] = str[3] = std::max(str[1] * dims[2], str[0] * dims[1]);
-  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (str[0] & 15u) || (str[1] & 15u)) return 0;
+  if ((reinterpret_cast<uintptr_t>(base) & 15u) || (row_bytes & 15u) || (z_bytes & 15u)) return 0;
   p.c_box_cols = 128 / esz;
-  if (!bulk) return 2;
-  const uint32_t box[5] = {static_cast<uint32_t>(p.c_box_cols), 32, 1, 1, 1};
-  if (make_tensor_map(map, base, dims, str, box, esz) != NG_OK) return 0;
   return 1;
 }
 
@@ -190,9 +178,8 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
   long long cost2 = ((t2 + sm - 1) / sm) * (num_kb + 4ll) * (2 * kTileM + p.block_n);
   if (t2 % sm > 0 && 2 * (t2 % sm) <= sm)   // the last wave runs as 128-row halves (see tc_launch)
     cost2 -= (num_kb + 4ll) * (2 * kTileM + p.block_n) - (num_kb + 2ll) * (kTileM + p.block_n);
-  // NG_TILE_ROWS=128|256 overrides the choice (tuning aid)
-  static const char* force = getenv("NG_TILE_ROWS");
-  const bool wide = force ? (force[0] == '2') : (cost2 < cost1);
+  const int force = tuning().tile_rows;   // 128 | 256 overrides the choice
+  const bool wide = force ? force == 256 : (cost2 < cost1);
   if (wide) {
     p.m_halves = 2;
     p.tiles_m = static_cast<int>(tm2);
@@ -205,15 +192,14 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
 // per K=16 step); a 256-row tile pays for its epilogue (not overlapped), a 128-row tile does not.
 // 85 tiles of 256 columns on 148 SMs (the 13x13 AlexNet layers) lose to 113 tiles of 192.
 void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, int kb_rows) {
-  static const char* force_rows = getenv("NG_TILE_ROWS");
-  static const char* force_cols = getenv("NG_TILE_COLS");
+  const int force_rows = tuning().tile_rows, force_cols = tuning().tile_cols;
   double best = -1.0;
   int best_h = 1, best_bn = 256;
   for (int h = 1; h <= 2; ++h) {
     if (h == 2 && p.M <= kTileM) continue;
-    if (force_rows && (force_rows[0] == '2') != (h == 2) && p.M > kTileM) continue;
+    if (force_rows && (force_rows == 256) != (h == 2) && p.M > kTileM) continue;
     for (int bn = 256; bn >= 128; bn -= 64) {
-      if (force_cols && atoi(force_cols) != bn) continue;
+      if (force_cols && force_cols != bn) continue;
       const long long tm = (p.M + kTileM * h - 1) / (kTileM * h);
       const long long tn = (cols + bn - 1) / bn;
       const long long tiles = tm * tn;
@@ -267,8 +253,8 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
 // Threads that share one 8-column group of the split-K reduction: more when the output is small
 // and the partitions many, so that the device is filled and no thread walks a long chain.
 static int splitk_reduce_lanes(long long groups, int splits, int sm_count) {
-  static const char* force = getenv("NG_REDUCE_LANES");   // tuning aid: 1, 2, 4, ... 32
-  if (force && atoi(force) >= 1 && atoi(force) <= 32 && (atoi(force) & (atoi(force) - 1)) == 0) return atoi(force);
+  const int force = tuning().reduce_lanes;   // 1, 2, 4, ... 32
+  if (force >= 1 && force <= 32 && (force & (force - 1)) == 0) return force;
   int lanes = 1;
   // only as many as it takes to occupy the SMs: with more, every thread holds fewer loads in flight
   // and the launch becomes several waves of short threads (AlexNet conv5: 49 -> 38 us for update + sum)
@@ -320,7 +306,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   p.full_items = static_cast<int>(total);
   // 256-row tiles: when the last wave fills at most half of the SMs, its tiles are handed out as
   // 128-row halves, so that the wave takes about half a tile time on twice as many SMs
-  static const bool split_tail = !(getenv("NG_SPLIT_TAIL") && atoi(getenv("NG_SPLIT_TAIL")) == 0);
+  const bool split_tail = tuning().split_tail != 0;
   const long long rem = total % c->sm_count;
   if (split_tail && p.m_halves == 2 && rem > 0 && 2 * rem <= c->sm_count) {
     p.full_items = static_cast<int>(total - rem);
@@ -328,9 +314,11 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   }
   p.total_items = static_cast<int>(total);
   const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
-  CUtensorMap mapC = mapA;   // placeholder when the bulk-store epilogue is off
-  p.tma_store = pick_store_mode(&mapC, p);
-  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.tma_store ? kEpiStageBytes : 0u) +
+  p.store_staged = pick_store_mode(p);
+  if (p.c_row_chunks && !p.store_staged)
+    return fail(NG_ERR_UNSUPPORTED, "internal: padded image rows need the staged output stage");
+  if (!p.wait_limit_ns) p.wait_limit_ns = c->wait_limit_ns;
+  const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.store_staged ? kEpiStageBytes : 0u) +
                         a_overread(p);
   fill_fast_divs(p);
   TcParams launch = p;
@@ -339,26 +327,14 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   if (landed != p.tx_bytes || landed > p.stage_bytes) {
     return fail(NG_ERR_INVALID_ARG, "internal: stage layout and box sizes disagree");
   }
-  launch.timeline = nullptr;
-#ifdef NG_TC_TIMELINE
-  static unsigned long long* tl_dev = nullptr;
-  const size_t tl_count = static_cast<size_t>(kTimelineCtas) * kTimelineTiles * kTimelineSlots;
-  const char* tl_out = getenv("NG_TC_TIMELINE_OUT");
-  if (tl_out) {
-    if (!tl_dev) NG_CUDA(cudaMalloc(&tl_dev, tl_count * 8));
-    NG_CUDA(cudaMemsetAsync(tl_dev, 0, tl_count * 8, stream));
-    launch.timeline = tl_dev;
-  }
-#endif
   if (!mapBm && (launch.b_merge == 1 || launch.b_merge == 2)) launch.b_merge = 0;
   const CUtensorMap& mapB2 = mapBm ? *mapBm : mapB;
   // the lean instances: staged tiles, and either raw split-K partials or alpha 1 / no beta / round to nearest
-  static const bool lean_ok = !(getenv("NG_LEAN_KERNELS") && atoi(getenv("NG_LEAN_KERNELS")) == 0);
-  const bool lean = lean_ok && launch.tma_store == 2 &&
+  const bool lean = tuning().lean_kernels != 0 && launch.store_staged &&
                     (launch.splits > 1 || (launch.alpha == 1.0f && launch.beta == 0.0f && launch.sr_bits == 0));
 #define NG_TC_LAUNCH(mode)                                                                                      \
-  if (lean) igemm_tc_kernel<mode, true><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch);   \
-  else igemm_tc_kernel<mode, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapC, mapB2, launch)
+  if (lean) igemm_tc_kernel<mode, true><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch);   \
+  else igemm_tc_kernel<mode, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch)
   switch (launch.mode) {
     case TC_GEMM: NG_TC_LAUNCH(TC_GEMM); break;
     case TC_FPROP: NG_TC_LAUNCH(TC_FPROP); break;
@@ -368,35 +344,6 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   }
 #undef NG_TC_LAUNCH
   NG_CHECK_LAUNCH();
-#ifdef NG_TC_TIMELINE
-  if (tl_out) {
-    std::vector<unsigned long long> tl(tl_count);
-    NG_CUDA(cudaStreamSynchronize(stream));
-    NG_CUDA(cudaMemcpy(tl.data(), tl_dev, tl_count * 8, cudaMemcpyDeviceToHost));
-    if (FILE* f = fopen(tl_out, "a")) {
-      unsigned long long t0 = ~0ull;
-      for (size_t i = 0; i < tl.size(); ++i) if (i % kTimelineSlots < 8 && tl[i] && tl[i] < t0) t0 = tl[i];
-      fprintf(f, "launch mode=%d M=%d N=%d tiles=%dx%dx%d splits=%d num_kb=%d stages=%d block_n=%d halves=%d groups=%dx%d\n",
-              p.mode, p.M, p.N, p.tiles_m, p.tiles_n, p.nz, p.splits, p.num_kb, p.stages, p.block_n, p.m_halves,
-              p.acc_groups, p.acc_taps);
-      for (int c2 = 0; c2 < kTimelineCtas; ++c2)
-        for (int t = 0; t < kTimelineTiles; ++t) {
-          const unsigned long long* s = &tl[(static_cast<size_t>(c2) * kTimelineTiles + t) * kTimelineSlots];
-          if (!s[0] && !s[2]) continue;
-          fprintf(f, "cta %d tile %2d:", c2, t);
-          for (int k = 0; k < 8; ++k) fprintf(f, " %8lld", s[k] ? static_cast<long long>(s[k] - t0) : -1ll);
-          fprintf(f, "  epilogue cycles other/tmem/convert/write:");
-          for (int k = 8; k < 12; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
-          fprintf(f, "  mma wait/issue/commit:");
-          for (int k = 12; k < 15; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
-          fprintf(f, "  producer wait/coords/sync/copy/advance:");
-          for (int k = 15; k < 20; ++k) fprintf(f, " %lld", static_cast<long long>(s[k]));
-          fprintf(f, "\n");
-        }
-      fclose(f);
-    }
-  }
-#endif
   if (p.splits > 1) {
     EpiArgs ea;
     ea.alpha = p.alpha; ea.beta = p.beta; ea.relu = p.relu; ea.sr_bits = p.sr_bits;
@@ -467,9 +414,67 @@ int static_setup(int dev, StaticSlots** out) {
 }
 
 }  // namespace
+
+// Status word of the static-scratch entry point on device `dev`: read and cleared. Nothing is
+// allocated; returns NG_OK with *code = 0 when that entry point has never run on the device.
+int static_scratch_status(int dev, int* code) {
+  *code = 0;
+  if (dev < 0 || dev >= 64) return NG_OK;
+  int* status = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (!g_static_slots[dev].ready) return NG_OK;
+    status = g_static_slots[dev].status;
+  }
+  NG_CUDA(cudaMemcpy(code, status, sizeof(int), cudaMemcpyDeviceToHost));
+  if (*code != 0) NG_CUDA(cudaMemset(status, 0, sizeof(int)));
+  return NG_OK;
+}
+
+// One CTA, one thread: a bounded wait on an mbarrier that nothing ever arrives at. The wait runs
+// out after `limit_ns`, records the site in the status word and the kernel returns normally.
+__global__ void wait_expires_kernel(int* status, unsigned long long limit_ns, unsigned long long* waited_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  abort_flag = 0;
+  mbar_init(smem_u32(&bar), 1);
+  mbar_fence_init();
+  const uint64_t t0 = global_timer_ns();
+  const bool ok = mbar_wait(smem_u32(&bar), 0u, &abort_flag, status, NG_DEV_TIMEOUT_TEST, limit_ns);
+  if (waited_ns) *waited_ns = ok ? 0ull : global_timer_ns() - t0;
+}
+
 }  // namespace ngb
 
 using namespace ngb;
+
+extern "C" int ng_static_scratch_status(int* code) {
+  int dev = -1;
+  NG_CUDA(cudaGetDevice(&dev));
+  int v = 0;
+  const int rc = static_scratch_status(dev, &v);
+  if (rc != NG_OK) return rc;
+  if (code) *code = v;
+  if (v != 0) return fail(NG_ERR_TIMEOUT, "a static-scratch GEMM gave up a bounded wait (site %d)", v);
+  return NG_OK;
+}
+
+extern "C" int ng_set_wait_limit_ns(unsigned long long limit_ns) {
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  c->wait_limit_ns = limit_ns ? limit_ns : kWaitLimitNs;
+  return NG_OK;
+}
+
+extern "C" int ng_test_wait_expires(unsigned long long limit_ns, unsigned long long* waited_ns_device, void* stream) {
+  DeviceCtx* c = current_ctx();
+  if (!c) return NG_ERR_CUDA;
+  if (limit_ns == 0 || limit_ns > 100000000ull)
+    return fail(NG_ERR_INVALID_ARG, "the test wait is limited to 100 ms");
+  wait_expires_kernel<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(c->status, limit_ns, waited_ns_device);
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
 
 extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, int a_t, int b_t, int m, int n, int k,
                                        int lda, int ldb, int ldc, float alpha, float beta, int relu, int sr_bits,
@@ -550,11 +555,11 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
   const long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.splits;
   const int grid = static_cast<int>(std::min<long long>(total, slots->sm_count));
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes;
-  p.tma_store = 0;   // this variant stores straight from registers
-  p.timeline = nullptr;
+  p.store_staged = 0;   // this variant stores straight from registers
+  p.wait_limit_ns = kWaitLimitNs;
   p.full_items = p.total_items = static_cast<int>(total);
   ngb::fill_fast_divs(p);
-  igemm_tc_kernel<TC_GEMM, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapA, mapB, p);
+  igemm_tc_kernel<TC_GEMM, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB, p);
   NG_CHECK_LAUNCH();
   EpiArgs ea;
   ea.alpha = alpha; ea.beta = beta; ea.relu = relu; ea.sr_bits = sr_bits;

@@ -292,23 +292,25 @@ def conv_bprop_pixels(cd, F, E, positions, alpha=1.0, absolute=False):
     return out * np.float32(alpha)
 
 
-def conv_update_taps(cd, I, E, taps, alpha=1.0, absolute=False):
+def conv_update_taps(cd, I, E, taps, alpha=1.0, absolute=False, dtype=np.float32):
     """Weight gradient of the filter taps `taps`, a list of (t, r, s): the sum over all output
-    pixels of conv_test.py:166-167 restricted to those taps. Returns (len(taps), C, K)."""
+    pixels of conv_test.py:166-167 restricted to those taps. Returns (len(taps), C, K).
+    `dtype=np.float64` sums in double precision: over millions of terms the fp32 sum of the
+    reference's np.dot carries a rounding error of its own of about 1e-4 relative."""
     C, D, H, W, N = cd.dimI
     M, P, Q = cd.MPQ
     pad_d, pad_h, pad_w = cd.padding
     str_d, str_h, str_w = cd.strides
-    Ip = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
-    Ip[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] = np.asarray(I, dtype=np.float32).reshape(cd.dimI)
-    E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, -1)
+    Ip = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=dtype)
+    Ip[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] = np.asarray(I, dtype=dtype).reshape(cd.dimI)
+    E2 = np.asarray(E, dtype=dtype).reshape(cd.K, -1)
     if absolute:
         Ip, E2 = np.abs(Ip), np.abs(E2)
-    out = np.empty((len(taps), C, cd.K), dtype=np.float32)
+    out = np.empty((len(taps), C, cd.K), dtype=dtype)
     for i, (t, r, s) in enumerate(taps):
         sl = Ip[:, t:t + M * str_d:str_d, r:r + P * str_h:str_h, s:s + Q * str_w:str_w, :].reshape(C, -1)
         out[i] = np.dot(sl, E2.T)
-    return out * np.float32(alpha)
+    return (out * dtype(alpha)).astype(np.float32)
 
 
 # ---------------------------------------------------------------------------------------------

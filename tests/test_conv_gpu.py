@@ -89,6 +89,28 @@ CASES = {
 }
 
 
+# Per-GPU shapes of a minibatch that is split over 2 / 4 / 8 GPUs (AlexNet 128 -> 64/32/16, VGG model A
+# 64 -> 32/16/8): with fewer than 64 images a 64-element chunk is several pixels of one image row, and
+# rows that are not a multiple of 64 elements (13 x 32, 27 x 16, 14 x 8, ...) are padded to whole chunks.
+SHARDED = {
+    "alexnet_conv2_n32": (32, 64, 192, 1, 27, 27, 1, 5, 5, 0, 2, 2, 1, 1, 1),
+    "alexnet_conv2_n16": (16, 64, 192, 1, 27, 27, 1, 5, 5, 0, 2, 2, 1, 1, 1),
+    "alexnet_conv3_n32": (32, 192, 384, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "alexnet_conv3_n16": (16, 192, 384, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "alexnet_conv4_n16": (16, 384, 256, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "alexnet_conv5_n32": (32, 256, 256, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "vgg_64_128_n8_w20": (8, 64, 128, 1, 20, 20, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "vgg_256_512_28_n8": (8, 256, 512, 1, 28, 28, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "vgg_512_512_14_n8": (8, 512, 512, 1, 14, 14, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "vgg_512_512_14_n16": (16, 512, 512, 1, 14, 14, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    "vgg_512_512_14_n32": (32, 512, 512, 1, 14, 14, 1, 3, 3, 0, 1, 1, 1, 1, 1),
+    # no padding (Q < W): the tail of a row's last chunk reads real pixels of the next columns
+    "valid_conv_n24_q9": (24, 32, 64, 1, 11, 11, 1, 3, 3, 0, 0, 0, 1, 1, 1),
+    # 3-D, one image row shorter than a chunk
+    "c32_3d_n8_w5": (8, 32, 32, 3, 5, 5, 3, 3, 3, 1, 1, 1, 1, 1, 1),
+}
+
+
 def _inputs(cd, seed):
     rng = np.random.default_rng(seed)
     I = rng.uniform(0, 1, cd.dimI).astype(np.float16)
@@ -107,6 +129,34 @@ def test_tensor_core_path_matches_oracle(ng, name):
     got = _run_all(ng, _layer(ng, cfg, "tensor"), I, F, E, relu=True, alpha=0.5)
     _check(cd, got, I, F, E, ref, name)
     assert (got["O"] >= 0).all()
+
+
+@pytest.mark.parametrize("name", sorted(SHARDED))
+def test_sharded_minibatch_shapes_run_on_the_tensor_core_path(ng, name):
+    cfg = SHARDED[name]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 1004)
+    ref = {"O": rm.conv_fprop_fast(cd, I, F, relu=True), "gradI": rm.conv_bprop_fast(cd, F, E),
+           "gradF": rm.conv_update_fast(cd, I, E)}
+    # guard cells around the outputs: columns of the padded chunk space must not be stored anywhere
+    layer = _layer(ng, cfg, "tensor")
+    dI, dF, dE = ng.array(I), ng.array(F), ng.array(E)
+    pad = 4096
+    bufO = ng.empty((layer.sizeO + 2 * pad,))
+    bufB = ng.empty((layer.sizeI + 2 * pad,))
+    bufO.fill(7.0)
+    bufB.fill(7.0)
+    dO = bufO[pad:pad + layer.sizeO].reshape(layer.dimO)
+    dB = bufB[pad:pad + layer.sizeI].reshape(layer.dimI)
+    dU = ng.empty(layer.dimF, dtype=np.float32)
+    ng.fprop_conv(layer, dI, dF, dO, relu=True)
+    ng.bprop_conv(layer, dF, dE, dB)
+    ng.update_conv(layer, dI, dE, dU)
+    got = {"O": dO.get(), "gradI": dB.get(), "gradF": dU.get()}
+    _check(cd, got, I, F, E, ref, name)
+    for buf, size in ((bufO, layer.sizeO), (bufB, layer.sizeI)):
+        h = buf.get()
+        assert (h[:pad] == 7.0).all() and (h[pad + size:] == 7.0).all(), name + ": wrote outside the tensor"
 
 
 @pytest.mark.parametrize("name", ["c3_3x3_n64_first_layer", "c3_11x11_stride4_n64_alexnet1", "c64_3x3_n64"])

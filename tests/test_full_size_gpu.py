@@ -103,9 +103,12 @@ def _rms_rel(got, ref):
 
 
 # Besides the element-wise bounds, the error as a whole must look like rounding noise: one fp16
-# rounding is at most 2^-11 relative (rms about 2^-12 of the values), the fp32 weight gradients
-# differ by summation order only.
-RMS_FP16, RMS_FP32 = 2.0 ** -11, 2.0 ** -14
+# rounding is at most 2^-11 relative (rms about 2^-12 of the values). The fp32 weight gradients
+# differ from a double-precision sum by the accumulators' own rounding: the tensor cores add each
+# K=16 step into the fp32 accumulator with truncation, so a chain of several hundred steps ends
+# up to 2e-4 below the exact magnitude (measured on the 3-D layer, 1.6 million terms per output,
+# 6.4e-5 rms; the reference's own fp32 FFMA chains have a rounding error of the same order).
+RMS_FP16, RMS_FP32 = 2.0 ** -11, 2.0 ** -12
 
 
 def _update_tol(i_c, e_k):
@@ -168,7 +171,7 @@ def test_large_layers_at_sampled_positions(ng, name):
     all_taps = [(t, r, s) for t in range(T) for r in range(R) for s in range(S)]
     picks = sorted(set([0, len(all_taps) - 1] + [int(i) for i in rng.choice(len(all_taps), n_taps, replace=False)]))
     taps = [all_taps[i] for i in picks[:max(n_taps, 2)]]
-    ref = rm.conv_update_taps(cd, I, E, taps)
+    ref = rm.conv_update_taps(cd, I, E, taps, dtype=np.float64)   # millions of terms: sum in double
     i_c = np.sqrt((I.astype(np.float64) ** 2).sum(axis=(1, 2, 3, 4)))
     e_k = np.sqrt((E.astype(np.float64) ** 2).sum(axis=(1, 2, 3, 4)))
     got = np.stack([U[:, t, r, s, :] for t, r, s in taps])
