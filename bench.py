@@ -1,25 +1,38 @@
 #!/usr/bin/env python
-"""Benchmark of the hot path: the AlexNet convolution stack (BASELINE config 3) on B200.
+"""Benchmark of the hot path on B200: the convolution stack of a benchmark network, or the GEMMs.
 
-One step = one forward + backward + weight-update pass over one synthetic minibatch through the
-public API (NervanaGPU.fprop_conv / bprop_conv / update_conv / fprop_pool / bprop_pool and the
-generated element-wise kernels for the ReLU mask and the SGD step), N = 128 images per GPU.
-With --gpus N > 1 (launched by torchrun, one rank per GPU) every rank runs the same per-GPU
-minibatch (weak scaling) and the fp32 weight gradients are summed with one NCCL all-reduce.
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+                  [--net alexnet|vgg_a|gemm] [--scaling strong|weak]
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--net alexnet|vgg_a]
+alexnet (default) / vgg_a: one step = one forward + backward + weight-update pass over one
+synthetic minibatch through the public API (NervanaGPU.fprop_conv / bprop_conv / update_conv /
+fprop_pool / bprop_pool and the generated element-wise kernels for the ReLU mask and the SGD
+step). With --gpus N > 1 (launched by torchrun, one rank per GPU) the minibatch of the
+configuration (128 images for AlexNet, 64 for VGG model A) is split over the GPUs, N/g images
+each (`--scaling strong`, the default: the split the configurations name), or every GPU runs a
+whole minibatch of its own (`--scaling weak`); the fp32 weight gradients are summed over the GPUs
+with NCCL all-reduces that overlap the backward pass.
+gemm: `ng.dot` on the 2048^3 TN + ReLU product (the metric) and the fully-connected shapes.
 
 Prints ONE JSON line (rank 0). `value` is device-timed with the inputs resident in HBM; `e2e`
 repeats the measurement with the minibatch copied from pinned host memory and the last
 activation read back every step. `--impl reference` times the reference's numpy validation path
-(the oracle) on the host cores instead.
+(the oracle) of the same step on the host cores instead.
 """
+import os
+import sys
+
+if "--impl" in sys.argv and "reference" in sys.argv:
+    # The CPU arm uses every host core; launchers (torchrun) pin OMP_NUM_THREADS to 1 otherwise.
+    # Must happen before numpy loads its BLAS.
+    for _v in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[_v] = str(os.cpu_count() or 1)
+
 import argparse
 import ctypes
+import hashlib
 import json
-import os
 import subprocess
-import sys
 import threading
 import time
 
@@ -28,11 +41,12 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-METRIC = "alexnet_conv_stack_fprop_bprop_update_tflops"
 UNIT = "TFLOP/s"
-# dram__bytes_read.sum + dram__bytes_write.sum per igemm_tc_kernel launch, from the ncu capture summarised
-# in profiles/igemm_tc_kernel_alexnet_step_traffic.md (not measurable from inside this script)
-TRAFFIC_BYTES_PER_CONV_LAUNCH = {("alexnet", 128): 27.92e6}
+METRICS = {
+    "alexnet": ("alexnet_conv_stack_fprop_bprop_update_tflops", "BASELINE config 3"),
+    "vgg_a": ("vgg_a_conv_stack_fprop_bprop_update_tflops", "BASELINE config 4"),
+    "gemm": ("gemm_2048_tn_relu_tflops", "BASELINE config 1 (+ the shapes of config 2)"),
+}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 
 
@@ -42,33 +56,64 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--net", default="alexnet", choices=["alexnet", "vgg_a"])
+    ap.add_argument("--net", default="alexnet", choices=["alexnet", "vgg_a", "gemm"])
+    ap.add_argument("--scaling", default="strong", choices=["strong", "weak"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-replay", action="store_true",
-                    help="end-to-end arm launches every kernel from Python instead of replaying a recorded step")
+                    help="launch every kernel from Python instead of replaying a recorded step")
     return ap.parse_args()
 
 
 # ---------------------------------------------------------------------------------------------
-# host-side baseline: the oracle (numpy restatement of the reference's validation math)
+# host-side baseline: the oracle (numpy restatement of the reference's validation math) on the
+# same step: every convolution's three passes, the max-pools, the ReLU masks and the SGD step
 # ---------------------------------------------------------------------------------------------
-CPU_SAMPLE = ("AlexNet conv3 (N=128, 192->384, 13x13, 3x3 pad 1) fprop+bprop+update through the vectorised "
-              "numpy oracle (im2col + BLAS sgemm), one pass per step")
+class CpuStack(object):
+    def __init__(self, net, seed=1003):
+        from oracle import reference_math as rm
+        self.rm = rm
+        rm.keep_workspaces(True)      # the same shapes every step: allocate the big temporaries once
+        rng = np.random.default_rng(seed)
+        N, C, H, W = net["N"], net["C"], net["H"], net["W"]
+        self.layers = []
+        for kind, prm in net["layers"]:
+            if kind == "conv":
+                K, R, S, pad, stride = prm
+                d = rm.ConvDims(N, C, K, 1, H, W, 1, R, S, 0, pad, pad, 1, stride, stride)
+                w = rng.normal(0.0, 0.01, d.dimF).astype(np.float16).astype(np.float32)
+                self.layers.append(["conv", d, w])
+                C, (_, H, W) = K, d.MPQ
+            else:
+                R, S, stride = prm
+                d = rm.PoolDims(N, C, 1, H, W, 1, 1, R, S, 0, 0, 0, 0, 1, 1, stride, stride)
+                self.layers.append(["pool", d, None])
+                _, H, W = d.MPQ
+        first, last = self.layers[0][1], self.layers[-1][1]
+        self.input = rng.uniform(0.0, 1.0, first.dimI).astype(np.float16).astype(np.float32)
+        self.top = (rng.uniform(-1.0, 1.0, last.dimO) * 0.125).astype(np.float16).astype(np.float32)
+        convs = [l[1] for l in self.layers if l[0] == "conv"]
+        self.flops = 3 * sum(d.flops for d in convs) - convs[0].flops     # no input gradient for layer 1
 
-
-def cpu_sample_setup():
-    from oracle import reference_math as rm
-    cd = rm.ConvDims(128, 192, 384, 1, 13, 13, 1, 3, 3, 0, 1, 1, 1, 1, 1)
-    rng = np.random.default_rng(1003)
-    I = rng.uniform(0, 1, cd.dimI).astype(np.float16).astype(np.float32)
-    F = rng.normal(0, 0.01, cd.dimF).astype(np.float16).astype(np.float32)
-    E = (rng.uniform(-1, 1, cd.dimO) * 0.125).astype(np.float16).astype(np.float32)
-
-    def one_pass():
-        rm.conv_fprop_fast(cd, I, F, relu=True)
-        rm.conv_bprop_fast(cd, F, E)
-        rm.conv_update_fast(cd, I, E)
-    return one_pass, 3 * cd.flops
+    def step(self, lr=-1e-4):
+        rm = self.rm
+        x, acts = self.input, []
+        for kind, d, w in self.layers:
+            y = rm.conv_fprop_fast(d, x, w, relu=True) if kind == "conv" else rm.pool_max_fast(d, x)[0]
+            y = y.astype(np.float16).astype(np.float32)
+            acts.append(y)
+            x = y
+        grad = self.top
+        for i in range(len(self.layers) - 1, -1, -1):
+            kind, d, w = self.layers[i]
+            x = self.input if i == 0 else acts[i - 1]
+            if kind == "conv":
+                grad = grad * (acts[i] > 0)                                   # Layer.bprop_relu
+                dx = rm.conv_bprop_fast(d, w, grad).astype(np.float16).astype(np.float32) if i > 0 else None
+                dw = rm.conv_update_fast(d, x, grad)
+                self.layers[i][2] = (w + dw * np.float32(lr)).astype(np.float16).astype(np.float32)
+            else:
+                dx = rm.pool_max_fast(d, x, grad)[1].astype(np.float16).astype(np.float32)
+            grad = dx
 
 
 def host_threads():
@@ -80,29 +125,63 @@ def host_threads():
         return os.cpu_count() or 1
 
 
-def time_cpu(steps, warmup):
-    one_pass, flops = cpu_sample_setup()
+def time_cpu(net, steps, warmup):
+    stack = CpuStack(net)
     for _ in range(warmup):
-        one_pass()
+        stack.step()
     t0 = time.perf_counter()
     for _ in range(steps):
-        one_pass()
+        stack.step()
     dt = (time.perf_counter() - t0) / steps
-    return flops / dt / 1e12, dt * 1e3
+    return stack.flops / dt / 1e12, dt * 1e3
 
 
-def run_reference_arm(args, rank):
+def cpu_gemm(steps, warmup):
+    from oracle import reference_math as rm
+    rng = np.random.default_rng(1001)
+    A = rng.standard_normal((2048, 2048)).astype(np.float16).astype(np.float32)
+    B = rng.standard_normal((2048, 2048)).astype(np.float16).astype(np.float32)
+    for _ in range(warmup):
+        rm.gemm(A, B, a_t=True, relu=True)
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        rm.gemm(A, B, a_t=True, relu=True)
+    dt = (time.perf_counter() - t0) / steps
+    return 2.0 * 2048 ** 3 / dt / 1e12, dt * 1e3
+
+
+def workload_text(args, net, per_gpu, world):
+    metric, cfg = METRICS[args.net]
+    if args.net == "gemm":
+        return "ng.dot 2048x2048x2048, A stored k x m (TN), ReLU, fp16 round to nearest (%s)" % cfg
+    split = ("minibatch of %d split over %d GPUs, %d images each" % (net["N"], world, per_gpu)
+             if per_gpu != net["N"] else "minibatch of %d per GPU" % per_gpu)
+    return ("%s, %s, fp16 CHWN, fprop+bprop+update, relu fused, max-pools, SGD step (%s)"
+            % (net["name"], split, cfg))
+
+
+def run_reference_arm(args, rank, world):
     if rank != 0:
         return
-    tflops, ms = time_cpu(max(1, args.steps), max(0, args.warmup))
+    from nervanagpu_b200.convnet import NETWORKS
+    metric, _ = METRICS[args.net]
     cores = host_threads()
+    if args.net == "gemm":
+        tflops, ms = cpu_gemm(max(1, args.steps), max(0, args.warmup))
+        net, sample = None, "the whole 2048^3 product per step (numpy fp32 sgemm + ReLU)"
+    else:
+        net = NETWORKS[args.net]
+        tflops, ms = time_cpu(net, max(1, args.steps), max(0, args.warmup))
+        sample = ("one whole step per step: every convolution's fprop / bprop / update, the max-pools, ReLU masks and "
+                  "SGD of the %s minibatch of %d through the vectorised numpy oracle" % (net["name"], net["N"]))
+    per_gpu = net["N"] // world if (net and args.scaling == "strong") else (net["N"] if net else 0)
     line = {
-        "impl": "reference", "metric": METRIC, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
+        "impl": "reference", "metric": metric, "value": tflops, "unit": UNIT, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "alexnet conv stack N=128 fprop+bprop+update (BASELINE config 3)",
-                   "sample": CPU_SAMPLE},
-        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": CPU_SAMPLE},
+        "scaling": args.scaling, "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": workload_text(args, net, per_gpu, world), "sample": sample},
+        "cpu_baseline": {"value": tflops, "unit": UNIT, "cores": cores, "kind": "port", "sample": sample,
+                         "blas_threads_env": os.environ.get("OMP_NUM_THREADS")},
         "e2e": {"value": tflops, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
@@ -171,6 +250,43 @@ def load_peaks():
     return dict(FALLBACK_PEAKS), "fallback"
 
 
+def pick_peak(peaks, clocks):
+    """The burst figure applies while the SM clock stays at its maximum with no power cap (a short
+    timed region), the sustained one otherwise. Returns (peak, name)."""
+    burst = float(peaks.get("bf16_tflops", FALLBACK_PEAKS["bf16_tflops"]))
+    sustained = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
+    at_max = (clocks and clocks.get("sm_mhz") and clocks.get("sm_max_mhz") and
+              clocks["sm_mhz"] >= 0.97 * clocks["sm_max_mhz"] and "sw_power_cap" not in clocks.get("reasons", []))
+    return (burst, "bf16_tflops (burst)", sustained) if at_max else (sustained, "bf16_tflops_sustained", burst)
+
+
+def kernel_sources_hash():
+    """sha256 over the CUDA sources of the library: a recorded ncu figure is only quoted while the
+    kernels it was captured from are unchanged."""
+    h = hashlib.sha256()
+    csrc = os.path.join(ROOT, "nervanagpu_b200", "csrc")
+    for name in sorted(os.listdir(csrc)):
+        if name.endswith((".cu", ".cuh", ".h")):
+            with open(os.path.join(csrc, name), "rb") as f:
+                h.update(name.encode() + b"\0" + f.read())
+    return h.hexdigest()
+
+
+def recorded_traffic(key):
+    """DRAM bytes (read + write) per launch of the dominant kernel from the ncu capture recorded in
+    profiles/dram_traffic.json, or None when the kernels have changed since it was taken."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            rec = json.load(f)
+        entry = rec[key]
+        if entry.get("kernel_sources_sha256") != kernel_sources_hash():
+            return None
+        return entry["dram_bytes_per_launch"]
+    except Exception:
+        return None
+
+
 class LaunchProbe(object):
     """Times every launch of one pass with its own CUDA event pair on the launching stream."""
 
@@ -209,106 +325,302 @@ class LaunchProbe(object):
             self.records.append((name, layer, ms.value))
 
 
+class Ranks(object):
+    """Rendezvous, barrier and reductions over the ranks (torch.distributed with gloo: plumbing)."""
+
+    def __init__(self):
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            dist.init_process_group("gloo", rank=self.rank, world_size=self.world)
+            self.dist = dist
+
+    def _reduce(self, x, op):
+        if self.dist is None:
+            return x
+        import torch
+        t = torch.tensor([x], dtype=torch.float64)
+        self.dist.all_reduce(t, op=getattr(self.dist.ReduceOp, op))
+        return float(t[0])
+
+    def max(self, x): return self._reduce(x, "MAX")
+    def min(self, x): return self._reduce(x, "MIN")
+    def sum(self, x): return self._reduce(x, "SUM")
+
+    def barrier(self):
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def close(self):
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+
+
+def make_comm(lib, ranks):
+    from nervanagpu_b200 import _lib
+    if ranks.world == 1:
+        return None
+    nbytes = lib.ng_comm_unique_id_bytes()
+    ident = ctypes.create_string_buffer(nbytes)
+    if ranks.rank == 0:
+        _lib.check(lib.ng_comm_unique_id(ident))
+    box = [ident.raw]
+    ranks.dist.broadcast_object_list(box, src=0)
+    ident = ctypes.create_string_buffer(box[0], nbytes)
+    comm = ctypes.c_void_p()
+    _lib.check(lib.ng_comm_init(ctypes.byref(comm), ranks.world, ranks.rank, ident))
+    return comm
+
+
+def counter(lib, fn):
+    from nervanagpu_b200 import _lib
+    c = ctypes.c_ulonglong()
+    _lib.check(fn(ctypes.byref(c)))
+    return c.value
+
+
+def check_allreduce(stack, ranks):
+    """One step's weight gradients, summed over the ranks by the library (NCCL), against the sum of
+    the ranks' own gradients formed on the host side (gloo); and the weights after the step must
+    be the same bits on every rank. Returns (sum is right, weights agree)."""
+    ng = stack.ng
+    comm, stack.comm = stack.comm, None
+    w0 = stack.weights_flat.get()
+    stack.fprop()
+    lr, stack.lr = stack.lr, 0.0          # gradients only: leave the weights alone
+    stack.bprop()
+    ng.synchronize()
+    local = stack.grads_flat.get().astype(np.float64)
+    stack.lr, stack.comm = lr, comm
+    import torch
+    t = torch.from_numpy(local.copy())
+    ranks.dist.all_reduce(t)              # sum over ranks, in double
+    want = t.numpy()
+    stack.weights_flat.set(w0)
+    stack.lr = 0.0
+    stack.step()                          # the same gradients, this time summed by the library
+    ng.synchronize()
+    stack.lr = lr
+    got = stack.grads_flat.get().astype(np.float64)
+    scale = np.abs(want).max() + 1e-30
+    sum_ok = bool(np.abs(got - want).max() <= 1e-5 * scale * ranks.world)
+    stack.weights_flat.set(w0)
+    stack.step()
+    ng.synchronize()
+    w = stack.weights_flat.get().view(np.uint16).astype(np.float64)
+    digest = float((w * (1 + np.arange(w.size) % 8191)).sum())
+    same = ranks.max(digest) == ranks.min(digest)
+    moved = bool((stack.weights_flat.get() != w0).any())
+    return sum_ok, bool(same and moved)
+
+
+def bench_gemm(args, ranks):
+    from nervanagpu_b200 import NervanaGPU, _lib
+    from nervanagpu_b200.convnet import StepTimer
+    metric, cfg = METRICS["gemm"]
+    ng = NervanaGPU(stochastic_round=False, bench=False, device=ranks.local_rank)
+    lib = ng.lib
+    ng.stream = ng.new_stream()
+    timer = StepTimer(ng)
+    rng = np.random.default_rng(1001)
+    sampler = ClockSampler(ranks.local_rank) if ranks.rank == 0 else None
+
+    def operands(op, m, n, k, std):
+        A = rng.normal(0, std, (k, m) if op[0] == "t" else (m, k)).astype(np.float16)
+        B = rng.normal(0, std, (n, k) if op[1] == "t" else (k, n)).astype(np.float16)
+        return A, B
+
+    # several operand sets, rotated, so that consecutive calls do not find their inputs in the L2
+    def timed(op, m, n, k, relu, steps, std=1.0, sets=None):
+        nbytes = 2 * (m * k + k * n + m * n)
+        sets = sets or max(2, int(np.ceil(300e6 / nbytes)))
+        ops = []
+        for _ in range(sets):
+            A, B = operands(op, m, n, k, std)
+            dA, dB = ng.array(A), ng.array(B)
+            ops.append((dA.T if op[0] == "t" else dA, dB.T if op[1] == "t" else dB, ng.empty((m, n))))
+        i = [0]
+
+        def call():
+            a, b, c = ops[i[0] % sets]
+            i[0] += 1
+            ng.dot(a, b, c, relu=relu)
+        for _ in range(max(args.warmup, 3)):
+            call()
+        ng.synchronize()
+        ms = timer.time_ms(call, steps) / steps
+        return ms, 2.0 * m * n * k / (ms * 1e-3) / 1e12, nbytes / (ms * 1e-3) / 1e9, sets
+
+    ranks.barrier()
+    l0 = counter(lib, lib.ng_launch_count)
+    t0 = time.time()
+    ms, tflops, _, sets = timed("tn", 2048, 2048, 2048, True, args.steps)
+    ng.synchronize()
+    t1 = time.time()
+    launches = counter(lib, lib.ng_launch_count) - l0 - max(args.warmup, 3)
+    ms = ranks.max(ms)
+    tflops = 2.0 * 2048 ** 3 / (ms * 1e-3) / 1e12
+
+    # end to end: operands from pinned host memory every call, result read back
+    A, B = operands("tn", 2048, 2048, 2048, 1.0)
+    nb = A.nbytes
+    pins = []
+    for src in (A, B):
+        p = ctypes.c_void_p()
+        _lib.check(lib.ng_host_alloc(ctypes.byref(p), nb))
+        ctypes.memmove(p.value, src.ctypes.data, nb)
+        pins.append(p)
+    pin_c = ctypes.c_void_p()
+    _lib.check(lib.ng_host_alloc(ctypes.byref(pin_c), nb))
+    dA, dB, dC = ng.empty((2048, 2048)), ng.empty((2048, 2048)), ng.empty((2048, 2048))
+
+    def e2e_call():
+        _lib.check(lib.ng_memcpy_h2d_async(dA.ptr, pins[0], nb, ng.stream))
+        _lib.check(lib.ng_memcpy_h2d_async(dB.ptr, pins[1], nb, ng.stream))
+        ng.dot(dA.T, dB, dC, relu=True)
+        _lib.check(lib.ng_memcpy_d2h_async(pin_c, dC.ptr, nb, ng.stream))
+    for _ in range(3):
+        e2e_call()
+    ng.synchronize()
+    w0 = time.perf_counter()
+    e2e_dev = timer.time_ms(e2e_call, args.steps)
+    ng.synchronize()
+    e2e_ms = ranks.max(max(e2e_dev, (time.perf_counter() - w0) * 1e3)) / args.steps
+    if sampler is not None:
+        sampler.stop()
+
+    others = {}
+    for name, (op, m, n, k) in {"3072_nn": ("nn", 3072, 3072, 3072), "3072_nt": ("nt", 3072, 3072, 3072),
+                                "3072_tn": ("tn", 3072, 3072, 3072), "fc_4096x128x9216": ("nn", 4096, 128, 9216),
+                                "fc_4096x128x4096": ("nn", 4096, 128, 4096), "fc_1000x128x4096": ("nn", 1000, 128, 4096),
+                                "fc_9216x4096x128": ("nn", 9216, 4096, 128)}.items():
+        o_ms, o_tf, o_gbs, _ = timed(op, m, n, k, False, min(args.steps, 50), std=0.1)
+        others[name] = {"us": o_ms * 1e3, "tflops": o_tf, "gbs": o_gbs}
+    if ranks.rank != 0:
+        return
+    clocks = sampler.summary(t0, t1) if sampler is not None else None
+    peaks, peak_src = load_peaks()
+    peak, peak_name, other_peak = pick_peak(peaks, clocks)
+    line = {
+        "metric": metric, "value": tflops * ranks.world, "unit": UNIT, "n_gpus": ranks.world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": workload_text(args, None, 0, ranks.world),
+                   "l2": "%d operand sets rotated (%d MB): consecutive calls read operands that left the L2"
+                         % (sets, sets * 25),
+                   "other_shapes": others},
+        "e2e": {"value": 2.0 * 2048 ** 3 / (e2e_ms * 1e-3) / 1e12 * ranks.world, "unit": UNIT,
+                "h2d_bytes_per_step": 2 * nb, "d2h_bytes_per_step": nb, "ms_per_step": e2e_ms},
+        "gpu_launches": int(launches), "clocks": clocks,
+        "roofline": {"bound": "tensor", "achieved": tflops, "peak": peak, "unit": "TFLOP/s", "frac": tflops / peak,
+                     "frac_of_other_peak": tflops / other_peak, "peak_source": "%s %s" % (peak_src, peak_name),
+                     "traffic": recorded_traffic("gemm_2048_tn"), "kernel": "igemm_tc_kernel<gemm>"},
+        "fallback_launches": int(counter(lib, lib.ng_fallback_launch_count)),
+    }
+    if ranks.world == 1 and not args.no_cpu_baseline:
+        c_tf, _ = cpu_gemm(5, 1)
+        line["cpu_baseline"] = {"value": c_tf, "unit": UNIT, "cores": host_threads(), "kind": "port",
+                                "sample": "the whole 2048^3 product (numpy fp32 sgemm + ReLU), 5 repeats"}
+    print(json.dumps(line))
+
+
 def main():
     args = parse_args()
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-
     if args.impl == "reference":
-        run_reference_arm(args, rank)
+        run_reference_arm(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
 
     # keep stdout to the one JSON line: NCCL's version banner goes to stderr
     os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-    dist = None
-    if world > 1:
-        import torch.distributed as dist   # plumbing only: rendezvous, barrier, max over ranks
-        dist.init_process_group("gloo", rank=rank, world_size=world)
+    ranks = Ranks()
+    rank, world = ranks.rank, ranks.world
+    if args.net == "gemm":
+        bench_gemm(args, ranks)
+        ranks.close()
+        return
 
     from nervanagpu_b200 import NervanaGPU, _lib
     from nervanagpu_b200.convnet import ConvStack, NETWORKS, StepTimer
 
-    ng = NervanaGPU(stochastic_round=False, bench=False, device=local_rank)
+    ng = NervanaGPU(stochastic_round=False, bench=False, device=ranks.local_rank)
     lib = ng.lib
     ng.stream = ng.new_stream()      # a stream of its own: recorded sequences cannot use the default one
-
-    comm = None
-    if world > 1:
-        nbytes = lib.ng_comm_unique_id_bytes()
-        ident = ctypes.create_string_buffer(nbytes)
-        if rank == 0:
-            _lib.check(lib.ng_comm_unique_id(ident))
-        box = [ident.raw]
-        dist.broadcast_object_list(box, src=0)
-        ident = ctypes.create_string_buffer(box[0], nbytes)
-        comm = ctypes.c_void_p()
-        _lib.check(lib.ng_comm_init(ctypes.byref(comm), world, rank, ident))
+    comm = make_comm(lib, ranks)
 
     net = NETWORKS[args.net]
-    stack = ConvStack(ng, net, seed=1003 + rank, comm=comm)
+    metric, cfg_name = METRICS[args.net]
+    strong = args.scaling == "strong"
+    if strong:
+        stack = ConvStack(ng, net, seed=1003, comm=comm, shard=(rank, world))
+    else:
+        stack = ConvStack(ng, net, seed=1003, data_seed=2003 + rank, comm=comm)
     timer = StepTimer(ng)
 
     def barrier():
         ng.synchronize()
-        if dist is not None:
-            dist.barrier()
+        ranks.barrier()
 
-    def max_over_ranks(x):
-        if dist is None:
-            return x
-        import torch
-        t = torch.tensor([x], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t[0])
+    sampler = ClockSampler(ranks.local_rank) if rank == 0 else None
 
-    def min_over_ranks(x):
-        if dist is None:
-            return x
-        import torch
-        t = torch.tensor([x], dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MIN)
-        return float(t[0])
-
-    def launches():
-        c = ctypes.c_ulonglong()
-        _lib.check(lib.ng_launch_count(ctypes.byref(c)))
-        return c.value
-
-    sampler = ClockSampler(local_rank) if rank == 0 else None
+    # ---- one live step: which kernels serve it ---------------------------------------------
+    f0 = counter(lib, lib.ng_fallback_launch_count)
+    stack.step()
+    ng.synchronize()
+    fallback = counter(lib, lib.ng_fallback_launch_count) - f0
+    allreduce_ok = weights_in_step = None
+    if world > 1:
+        allreduce_ok, weights_in_step = check_allreduce(stack, ranks)
 
     # ---- device-resident measurement ------------------------------------------------------
     # The step is recorded once per input buffer and replayed (one host call per step instead of
-    # ~33 launches); with several GPUs the per-layer NCCL all-reduces are part of the recording.
-    replay = not args.no_replay
-    for _ in range(max(args.warmup, 3)):
-        stack.step()
-    step_fn = stack.step
-    if replay:
-        ok = 1
-        try:
-            stack.record_steps()
-        except _lib.NervanaError as exc:
-            sys.stderr.write("recording the step failed (%s): launching kernel by kernel\n" % exc)
-            ok = 0
-        # every rank must take the same route
-        replay = min_over_ranks(ok) == 1
-        if not replay:
-            stack._recorded = None
-    if replay:
-        step_fn = stack.step_prefetched          # nothing prefetched yet: replays on the resident input
-        step_fn()
-    barrier()
-    l0 = launches()
+    # ~33 launches); with several GPUs the NCCL all-reduces are part of the recording.
+    def prepare(with_replay):
+        for _ in range(max(args.warmup, 3)):
+            stack.step()
+        stack._recorded = None
+        fn = stack.step
+        if with_replay:
+            ok = 1
+            try:
+                stack.record_steps()
+            except _lib.NervanaError as exc:
+                sys.stderr.write("recording the step failed (%s): launching kernel by kernel\n" % exc)
+                ok = 0
+            with_replay = ranks.min(ok) == 1      # every rank must take the same route
+            if not with_replay:
+                stack._recorded = None
+        if with_replay:
+            fn = stack.step_prefetched            # nothing prefetched yet: replays on the resident input
+            fn()
+        return fn, with_replay
+
+    def timed_steps(fn):
+        barrier()
+        ms = timer.time_ms(fn, args.steps)
+        ng.synchronize()
+        barrier()
+        return ranks.max(ms) / args.steps
+
+    step_fn, replay = prepare(not args.no_replay)
+    l0 = counter(lib, lib.ng_launch_count)
     t0 = time.time()
-    ms_total = timer.time_ms(step_fn, args.steps)
-    ng.synchronize()
+    ms_step = timed_steps(step_fn)
     t1 = time.time()
-    gpu_launches = launches() - l0
-    barrier()
-    ms_total = max_over_ranks(ms_total)
-    ms_step = ms_total / args.steps
-    value = world * stack.flops / (ms_step * 1e-3) / 1e12
+    gpu_launches = counter(lib, lib.ng_launch_count) - l0
+    units = stack.flops * world              # flops of all ranks per step (strong: one minibatch)
+    value = units / (ms_step * 1e-3) / 1e12
+
+    # the same step without the gradient exchange: what the all-reduces add to the step
+    exposed_comm_ms = None
+    if world > 1:
+        stack.comm = None
+        fn_nc, _ = prepare(replay)
+        exposed_comm_ms = ms_step - timed_steps(fn_nc)
+        stack.comm = comm
+        step_fn, replay = prepare(replay)
 
     # ---- end to end: pinned host minibatch in, last activation out, every step ---------------
     in_bytes = stack.input.nbytes
@@ -364,14 +676,15 @@ def main():
     ng.synchronize()                                 # includes the last prefetch: K steps, K copies
     e2e_wall = (time.perf_counter() - w0) * 1e3
     barrier()
-    e2e_ms = max_over_ranks(max(e2e_ms_dev, e2e_wall)) / args.steps
-    e2e_value = world * stack.flops / (e2e_ms * 1e-3) / 1e12
+    e2e_ms = ranks.max(max(e2e_ms_dev, e2e_wall)) / args.steps
+    e2e_value = units / (e2e_ms * 1e-3) / 1e12
     if sampler is not None:
         sampler.stop()
 
     # ---- per-launch timing of the tensor-core engine (roofline) --------------------------------
     # (launch by launch on one stream: the weight updates do not overlap the backward chain here, so
     # the sum of this breakdown is larger than the step time above)
+    stack._recorded = None
     stack.overlap_update = False
     stack.step()                      # sizes the main stream's scratch memory outside the timed passes
     ng.synchronize()
@@ -392,47 +705,55 @@ def main():
             conv_ms += ms
             conv_flops += layer.flops
     n_conv = sum(per_kind[k][1] for k in ("fprop_conv", "bprop_conv", "update_conv"))
-    peaks, peak_src = load_peaks()
-    peak = float(peaks.get("bf16_tflops_sustained", FALLBACK_PEAKS["bf16_tflops_sustained"]))
     achieved = conv_flops / (conv_ms * 1e-3) / 1e12 if conv_ms > 0 else 0.0
+    barrier()
 
     if rank != 0:
-        if dist is not None:
-            dist.destroy_process_group()
+        ranks.close()
         return
 
     clocks = sampler.summary(t0, t1) if sampler is not None else None
+    peaks, peak_src = load_peaks()
+    peak, peak_name, other_peak = pick_peak(peaks, clocks)
     line = {
-        "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
-        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "metric": metric, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms_step, "higher_is_better": True,
+        "scaling": args.scaling if world > 1 else "strong",
         "vs_baseline": None, "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "%s N=%d per GPU, fp16 CHWN, fprop+bprop+update, relu fused, max-pools, SGD step "
-                               "(BASELINE config 3)" % (net["name"], stack.N),
+        "config": {"workload": workload_text(args, net, stack.N, world),
                    "global_batch": stack.N * world, "parallelism": "dp%d" % world,
                    "gflop_per_step_per_gpu": stack.flops / 1e9,
-                   "l2": "no flush: activations+deltas of one step (~%d MB) exceed the 126 MB L2"
-                         % int(sum(a.nbytes for a in stack.acts) * 2 / 1e6),
+                   "l2": "no flush: activations+deltas of one step (~%d MB per GPU) %s the 126 MB L2"
+                         % (int(sum(a.nbytes for a in stack.acts) * 2 / 1e6),
+                            "exceed" if sum(a.nbytes for a in stack.acts) * 2 > 126e6 else "DO NOT exceed"),
                    "launch": "recorded step replayed (CUDA graph)" if replay else "one call per kernel"},
-        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes, "d2h_bytes_per_step": out_bytes,
-                "ms_per_step": e2e_ms, "launch": "recorded step replayed" if replay else "one call per kernel"},
+        "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": in_bytes * world,
+                "d2h_bytes_per_step": out_bytes * world, "ms_per_step": e2e_ms,
+                "h2d_gbs_all_gpus": in_bytes * world / (e2e_ms * 1e-3) / 1e9,
+                "launch": "recorded step replayed" if replay else "one call per kernel"},
         "gpu_launches": int(gpu_launches),
+        "fallback_launches_per_step": int(fallback),
         "clocks": clocks,
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": achieved / peak if peak else None,
-                     "traffic": TRAFFIC_BYTES_PER_CONV_LAUNCH.get((args.net, stack.N)),
-                     "traffic_unit": "bytes of DRAM read+write per conv launch (ncu, mean of the 14 launches of a step)",
-                     "peak_source": "%s bf16_tflops_sustained" % peak_src,
+                     "frac_of_other_peak": achieved / other_peak if other_peak else None,
+                     "traffic": recorded_traffic("%s_step_n%d" % (args.net, stack.N)),
+                     "traffic_unit": "bytes of DRAM read+write per conv launch (ncu, mean over the launches of a step)",
+                     "peak_source": "%s %s" % (peak_src, peak_name),
                      "kernel": "igemm_tc_kernel (+ its split-K reduction / im2col satellites)",
                      "launches_timed": n_conv, "avg_launch_ms": conv_ms / n_conv if n_conv else None},
         "breakdown_ms_per_step": {k: v[0] / 5.0 for k, v in sorted(per_kind.items())},
     }
+    if world > 1:
+        line["allreduce_ok"] = allreduce_ok
+        line["weights_identical_across_ranks"] = weights_in_step
+        line["allreduce_exposed_ms_per_step"] = exposed_comm_ms
     if world == 1 and not args.no_cpu_baseline:
-        tflops, _ = time_cpu(2, 1)
+        tflops, cpu_ms = time_cpu(net, 1, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": UNIT, "cores": host_threads(), "kind": "port",
-                                "sample": CPU_SAMPLE}
+                                "sample": "one whole step of the same stack through the numpy oracle (%.0f ms)" % cpu_ms}
     print(json.dumps(line))
-    if dist is not None:
-        dist.destroy_process_group()
+    ranks.close()
 
 
 if __name__ == "__main__":

@@ -58,9 +58,16 @@ def bucket_layout(sizes, align=8):
 class ConvStack(object):
     """A chain of ConvLayer / PoolLayer objects with their activations, deltas and weights."""
 
-    def __init__(self, ng, net, N=None, seed=1003, learning_rate=-1e-4, comm=None):
+    def __init__(self, ng, net, N=None, seed=1003, learning_rate=-1e-4, comm=None, shard=None, data_seed=None):
+        """`shard=(rank, world)`: the minibatch of net["N"] images is generated whole (same seed on
+        every rank) and this rank keeps its slice of N/world images (a minibatch split over GPUs).
+        Weights always come from `seed`, so ranks that share it start from identical weights; the
+        data of an unsharded stack comes from `data_seed` (default: `seed`)."""
         self.ng = ng
         self.net = net
+        self.shard = shard
+        if shard is not None:
+            N = net["N"] // shard[1]
         self.N = N = net["N"] if N is None else N
         self.comm = comm                      # ng_comm handle or None (single GPU)
         self.lr = learning_rate
@@ -95,9 +102,17 @@ class ConvStack(object):
         self.acts = [ng.empty(l.dimO, dtype=np.float16) for l in self.layers]
         self.deltas = [None] + [ng.empty(l.dimI, dtype=np.float16) for l in self.layers[1:]]
         self.top_delta = ng.empty(self.layers[-1].dimO, dtype=np.float16)
-        self.host_input = rng.uniform(0.0, 1.0, self.layers[0].dimI).astype(np.float16)
+        drng = rng if data_seed is None else np.random.default_rng(data_seed)
+        if shard is None:
+            self.host_input = drng.uniform(0.0, 1.0, self.layers[0].dimI).astype(np.float16)
+            top = (drng.uniform(-1.0, 1.0, self.layers[-1].dimO) * 0.125).astype(np.float16)
+        else:
+            rank, world = shard
+            whole_in = self.layers[0].dimI[:-1] + (net["N"],)
+            whole_top = self.layers[-1].dimO[:-1] + (net["N"],)
+            self.host_input = shard_minibatch(drng.uniform(0.0, 1.0, whole_in).astype(np.float16), rank, world)
+            top = shard_minibatch((drng.uniform(-1.0, 1.0, whole_top) * 0.125).astype(np.float16), rank, world)
         self.input.set(self.host_input)
-        top = (rng.uniform(-1.0, 1.0, self.layers[-1].dimO) * 0.125).astype(np.float16)
         self.top_delta.set(top)
         # pooling layers keep their windows' argmax between the forward and the backward pass
         self.argmax = [None] * len(self.layers)
@@ -113,6 +128,18 @@ class ConvStack(object):
         self.overlap_update = ng.stream is not None
         self._side, self._side_busy = None, False
         self._comm_stream, self._comm_busy = None, False
+        # Gradient buckets of the multi-GPU step, as ranges of the flat buffers: the upper layers
+        # (most of the parameters) are summed over the GPUs as soon as the lowest of them has its
+        # gradient, while the layers below still compute; the small remainder goes last. Each
+        # bucket's SGD step runs on the communication stream right behind its sum.
+        sizes = [l.sizeF for l in self.convs]
+        split = 1
+        while split + 1 < len(sizes) and sum(sizes[:split + 1]) <= 0.15 * sum(sizes):
+            split += 1
+        self._conv_offsets = offsets
+        self._flat_elems = total_f
+        # (first conv index, one past the last conv index) per bucket, in the order they complete
+        self.comm_buckets = [(split, len(sizes)), (0, split)] if len(sizes) > 1 else [(0, 1)]
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)
@@ -163,10 +190,14 @@ class ConvStack(object):
                         ng.update_conv(l, x, grad, l.updat_out)
                     finally:
                         ng.stream = main
-                    if self.comm is not None:
-                        # this layer's gradient is summed over the GPUs while the layers below
-                        # are still computing (a third stream: the sum must not hold up the updates)
-                        self._allreduce_behind(side, l.updat_out)
+                    ci = self.convs.index(l)
+                    bucket = [b for b in self.comm_buckets if b[0] == ci]
+                    if self.comm is not None and bucket:
+                        # This layer is the lowest of its bucket: the bucket's gradients are summed
+                        # over the GPUs and applied while the layers below are still computing (a
+                        # third stream: the sum must not hold up the updates). The weights of the
+                        # bucket are free once this layer's bprop_conv, queued above, has read them.
+                        self._allreduce_behind(side, bucket[0])
                 else:
                     self._run("update_conv", l, lambda l=l, x=x, grad=grad: ng.update_conv(l, x, grad, l.updat_out))
             else:
@@ -177,22 +208,39 @@ class ConvStack(object):
                           ng.bprop_pool(l, x, grad, dx, relu_mask=fuse, argmax=a))
                 masked = fuse
             grad = dx
-        summed = self._comm_busy          # per-layer sums were queued behind the updates
+        summed = self._comm_busy          # the buckets were summed and applied behind the updates
         self._join_side()
-        if self.comm is not None and not summed:
+        if summed:
+            return
+        if self.comm is not None:
             self._run("allreduce_dW", None, self.allreduce_grads)
         self._run("grad_descent", None, self.grad_descent)
 
-    def _allreduce_behind(self, after_stream, grad):
-        lib = self.ng.lib
+    def _bucket_range(self, bucket):
+        first, last = bucket
+        start = self._conv_offsets[first]
+        end = self._conv_offsets[last] if last < len(self.convs) else self._flat_elems
+        return start, end
+
+    def _allreduce_behind(self, after_stream, bucket):
+        ng, lib = self.ng, self.ng.lib
         if self._comm_stream is None:
-            self._comm_stream = self.ng.new_stream()
-            self._comm_ev, self._comm_done = ctypes.c_void_p(), ctypes.c_void_p()
-            _lib.check(lib.ng_event_create(ctypes.byref(self._comm_ev)))
-            _lib.check(lib.ng_event_create(ctypes.byref(self._comm_done)))
-        _lib.check(lib.ng_event_record(self._comm_ev, after_stream))
+            self._comm_stream = ng.new_stream()
+            self._comm_ev, self._comm_done, self._w_free = ctypes.c_void_p(), ctypes.c_void_p(), ctypes.c_void_p()
+            for ev in (self._comm_ev, self._comm_done, self._w_free):
+                _lib.check(lib.ng_event_create(ctypes.byref(ev)))
+        start, end = self._bucket_range(bucket)
+        g, w = self.grads_flat[start:end], self.weights_flat[start:end]
+        _lib.check(lib.ng_event_record(self._comm_ev, after_stream))      # the bucket's last update
+        _lib.check(lib.ng_event_record(self._w_free, ng.stream))          # its last reader of the weights
         _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._comm_ev))
-        _lib.check(lib.ng_comm_allreduce_f32(self.comm, grad.ptr, grad.size, self._comm_stream))
+        _lib.check(lib.ng_comm_allreduce_f32(self.comm, g.ptr, g.size, self._comm_stream))
+        _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._w_free))
+        main, ng.stream = ng.stream, self._comm_stream
+        try:
+            w[:] = w + g * self.lr
+        finally:
+            ng.stream = main
         self._comm_busy = True
 
     def _fork_side(self):

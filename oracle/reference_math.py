@@ -165,6 +165,29 @@ def conv_update(cd, I, E, alpha=1.0):
     return (U * np.float32(alpha)).reshape(cd.dimF)
 
 
+# Large temporaries of the vectorised variants. A timing loop that repeats the same shapes may
+# switch the cache on (keep_workspaces(True)) so that the buffers are allocated, and their pages
+# touched, once instead of on every call; the arithmetic is the same either way.
+_WORKSPACES = None
+
+
+def keep_workspaces(on):
+    global _WORKSPACES
+    _WORKSPACES = {} if on else None
+
+
+def _workspace(tag, shape, zero=False):
+    if _WORKSPACES is None:
+        return np.zeros(shape, dtype=np.float32) if zero else np.empty(shape, dtype=np.float32)
+    key = (tag,) + tuple(shape)
+    buf = _WORKSPACES.get(key)
+    if buf is None:
+        buf = _WORKSPACES[key] = np.zeros(shape, dtype=np.float32)
+    elif zero:
+        buf.fill(0)
+    return buf
+
+
 def _im2col(cd, I):
     """All pixels at once: (C*T*R*S, M*P*Q*N) patch matrix, zero outside the image."""
     C, D, H, W, N = cd.dimI
@@ -172,9 +195,9 @@ def _im2col(cd, I):
     M, P, Q = cd.MPQ
     pad_d, pad_h, pad_w = cd.padding
     str_d, str_h, str_w = cd.strides
-    Ip = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
+    Ip = _workspace("padded", (C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), zero=True)
     Ip[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] = np.asarray(I, dtype=np.float32).reshape(cd.dimI)
-    col = np.empty((C, T, R, S, M, P, Q, N), dtype=np.float32)
+    col = _workspace("col", (C, T, R, S, M, P, Q, N))
     for t in range(T):
         for r in range(R):
             for s in range(S):
@@ -207,13 +230,13 @@ def conv_bprop_fast(cd, F, E, alpha=1.0):
     str_d, str_h, str_w = cd.strides
     F2 = np.asarray(F, dtype=np.float32).reshape(_slicable(cd.dimF))
     E2 = np.asarray(E, dtype=np.float32).reshape(cd.K, -1)
-    colg = np.dot(F2, E2).reshape(C, T, R, S, M, P, Q, N)
-    Bp = np.zeros((C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), dtype=np.float32)
+    colg = np.dot(F2, E2, out=_workspace("col", (C * T * R * S, M * P * Q * N))).reshape(C, T, R, S, M, P, Q, N)
+    Bp = _workspace("padded", (C, D + 2 * pad_d + str_d, H + 2 * pad_h + str_h, W + 2 * pad_w + str_w, N), zero=True)
     for t in range(T):
         for r in range(R):
             for s in range(S):
                 Bp[:, t:t + M * str_d:str_d, r:r + P * str_h:str_h, s:s + Q * str_w:str_w, :] += colg[:, t, r, s]
-    return Bp[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] * np.float32(alpha)
+    return Bp[:, pad_d:pad_d + D, pad_h:pad_h + H, pad_w:pad_w + W, :] * np.float32(alpha)   # (a copy)
 
 
 # ---------------------------------------------------------------------------------------------
