@@ -708,6 +708,8 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   if (rc != NG_OK) return rc;
   if (mode == CH_PIXEL && g.str_w == 1)
     p.b_merge = act_map_merged(&mapBm, I, g.C, g.D, g.H, g.W, g.N, lay.kb_rows, p.block_n / kChunk);
+  // few tiles (a small minibatch, e.g. the shard of one GPU): the reduction is split over the SMs too
+  p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n, p.num_kb, 1ll * g.K * cols, true);
   return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 
@@ -760,6 +762,7 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   // the error pixels of a column tile inside one image row as one box
   if (mode == CH_PIXEL && g.str_w == 1)
     p.b_merge = act_map_merged(&mapBm, E, g.K, g.M, g.P, g.Q, g.N, kChunk, p.block_n / kChunk);
+  p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n, p.num_kb, 1ll * g.C * cols, true);
   return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 

@@ -39,11 +39,12 @@ struct DeviceCtx {
 // Tuning aids, read from the environment once per process (none is needed in normal use):
 // NG_TILE_ROWS=128|256, NG_TILE_COLS=128|192|256, NG_KB_ROWS=16|32|48|64, NG_MERGE_BOXES=0,
 // NG_SPLIT_TAIL=0, NG_LEAN_KERNELS=0, NG_REDUCE_LANES=<power of two>, NG_UPDATE_GROUPS=<n>,
-// NG_UPDATE_STACK=<n>, NG_UPDATE_MIN_STAGES=<n>, NG_UPDATE_SWAP=0, NG_PAIR_MMA=0|1. A field is 0
+// NG_UPDATE_STACK=<n>, NG_UPDATE_MIN_STAGES=<n>, NG_UPDATE_SWAP=0, NG_PAIR_MMA=0|1, NG_MAX_CTAS=<n>,
+// NG_CONV_SPLITS=<n> (partitions of the forward / backward reduction; 1 = never split). A field is 0
 // (or -1 for the on/off switches) when its variable is not set.
 struct Tuning {
   int tile_rows = 0, tile_cols = 0, kb_rows = 0, reduce_lanes = 0;
-  int update_groups = 0, update_stack = 0, update_min_stages = 0;
+  int update_groups = 0, update_stack = 0, update_min_stages = 0, max_ctas = 0, conv_splits = -1;
   int merge_boxes = -1, split_tail = -1, lean_kernels = -1, update_swap = -1, pair_mma = -1;
 };
 const Tuning& tuning();
@@ -113,7 +114,7 @@ void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, i
 
 // Picks the number of split-K partitions for `tiles` output tiles and `num_kb` k-blocks.
 constexpr int kMaxSplits = 160;
-int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems);
+int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems, bool charge_reduction = false);
 
 // One GEMM request: C[m x n] = epilogue(op(A) * op(B)); see ng_hgemm for the conventions.
 struct GemmCall {

@@ -426,8 +426,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     // update never rounds stochastically: their instances leave those paths out.)
     constexpr bool kConvOut = kMode == TC_FPROP || kMode == TC_BPROP;
     constexpr bool kNoBetaSr = kMode != TC_GEMM;
-    const bool partial = !kConvOut && p.splits > 1;
-    const bool f32 = !kConvOut && (partial || p.out_f32 != 0);
+    const bool partial = p.splits > 1;
+    const bool f32 = partial || (!kConvOut && p.out_f32 != 0);
     EpiArgs ea;
     ea.alpha = partial ? 1.0f : p.alpha;
     ea.beta = (partial || kNoBetaSr) ? 0.0f : p.beta;
@@ -595,7 +595,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               const int j = lane & 7;
               int gcol = colb + j * (16 / esz);
               bool col_live = gcol < p.N && zt_warp < p.nz_out;
-              if (kConvOut && p.c_row_chunks) {
+              if (kConvOut && !partial && p.c_row_chunks) {
                 // Flattened pixel space whose image rows are padded to whole 64-element chunks:
                 // this box is chunk `ch` of the padded space; it holds elements [cq * 64, +64) of
                 // image row r, of which only those below c_row_len exist in memory.
@@ -693,7 +693,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 // ------------------------------------------------------------------------------------------
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int lanes, int nz, int M, int N,
                                      void* C, const void* Cold, long long ldc, long long c_zstride, int out_f32,
-                                     int vec_ok, EpiArgs ea) {
+                                     int vec_ok, EpiArgs ea, int c_row_chunks, int c_row_len) {
   const int groups_per_row = (N + 7) / 8;
   const long long total = static_cast<long long>(nz) * M * groups_per_row;
   const long long slice = static_cast<long long>(nz) * M * N;
@@ -747,15 +747,25 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, i
     for (int j = 0; j < 8; ++j) v[j] += __shfl_xor_sync(0xffffffffu, v[j], d);
   }
   if (!live || sub != 0) return;
+  int gcol = col;
+  if (c_row_chunks) {
+    // padded image rows (see TcParams::c_row_chunks): the partials are laid out in the padded
+    // column space, the output is not
+    const int ch = col >> 6;
+    const int r = ch / c_row_chunks;
+    const int within = (ch - r * c_row_chunks) * kChunk + (col & 63);
+    if (within >= c_row_len) return;
+    gcol = r * c_row_len + within;
+  }
   const long long off = z * c_zstride + static_cast<long long>(row) * ldc;
   const int esz = out_f32 ? 4 : 2;
   uint8_t* crow = static_cast<uint8_t*>(C) + off * esz;
   const uint8_t* oldrow = Cold ? static_cast<const uint8_t*>(Cold) + off * esz : nullptr;
   const unsigned long long lin = (static_cast<unsigned long long>(z) * M + row) * static_cast<unsigned long long>(N) + col;
   if (out_f32)
-    epi_store8<true>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
+    epi_store8<true>(ea, v, crow, oldrow, gcol, lin, nvalid, vec_ok != 0);
   else
-    epi_store8<false>(ea, v, crow, oldrow, col, lin, nvalid, vec_ok != 0);
+    epi_store8<false>(ea, v, crow, oldrow, gcol, lin, nvalid, vec_ok != 0);
 }
 
 }  // namespace ngb

@@ -49,6 +49,8 @@ const Tuning& tuning() {
     t.lean_kernels = num("NG_LEAN_KERNELS", -1);
     t.update_swap = num("NG_UPDATE_SWAP", -1);
     t.pair_mma = num("NG_PAIR_MMA", -1);
+    t.max_ctas = num("NG_MAX_CTAS", 0);
+    t.conv_splits = num("NG_CONV_SPLITS", -1);
   });
   return t;
 }

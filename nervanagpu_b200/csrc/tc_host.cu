@@ -227,7 +227,8 @@ void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, i
   p.tiles_n = static_cast<int>((cols + best_bn - 1) / best_bn);
 }
 
-int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems) {
+int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out_elems, bool charge_reduction) {
+  if (charge_reduction && tuning().conv_splits > 0) return std::min(tuning().conv_splits, std::max(1, num_kb / 2));
   if (tiles >= c->sm_count || num_kb < 8) return 1;
   // Makespan model: items run in waves of one per SM; an item costs its k-blocks plus a fixed
   // start-up/drain charge. 17 splits of 9 tiles (153 items on 148 SMs) would take two waves;
@@ -241,7 +242,10 @@ int choose_splits(const DeviceCtx* c, long long tiles, int num_kb, long long out
     if (s > 32 && s * out_elems * 4 > (16ll << 20)) break;
     const long long items = tiles * s;
     const long long waves = (items + sm - 1) / sm;
-    const long long cost = waves * ((num_kb + s - 1) / s + 6);
+    long long cost = waves * ((num_kb + s - 1) / s + 6);
+    // (forward / backward passes: the output is large, so the second stage is not free: a launch
+    // plus (s + 1) passes over the fp32 output at ~5 TB/s, in units of a k-block's ~0.5 us)
+    if (charge_reduction && s > 1) cost += 8 + out_elems * 4 * (s + 1) / 2500000;
     if (best_cost < 0 || cost < best_cost) {
       best = s;
       best_cost = cost;
@@ -313,7 +317,8 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     total += rem;
   }
   p.total_items = static_cast<int>(total);
-  const int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
+  int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
+  if (tuning().max_ctas > 0) grid = std::min(grid, tuning().max_ctas);
   p.store_staged = pick_store_mode(p);
   if (p.c_row_chunks && !p.store_staged)
     return fail(NG_ERR_UNSUPPORTED, "internal: padded image rows need the staged output stage");
@@ -354,7 +359,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     if (blocks > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "output too large for the split-K reduction");
     splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p.ws, p.splits, lanes, p.nz_out, p.M, p.N, p.C,
                                                                         p.Cold, p.ldc, p.c_zstride, p.out_f32,
-                                                                        p.vec_ok, ea);
+                                                                        p.vec_ok, ea, p.c_row_chunks, p.c_row_len);
     NG_CHECK_LAUNCH();
   }
   return NG_OK;
@@ -569,7 +574,7 @@ extern "C" int ng_hgemm_static_scratch(const void* A, const void* B, void* C, in
     const int lanes = ngb::splitk_reduce_lanes(groups, p.splits, slots->sm_count);
     const int blocks = static_cast<int>((groups * lanes + 255) / 256);
     splitk_reduce_kernel<<<blocks, 256, 0, stream>>>(p.ws, p.splits, lanes, 1, m, n, C, p.Cold, ldc, 0, 0, p.vec_ok,
-                                                     ea);
+                                                     ea, 0, 0);
     NG_CHECK_LAUNCH();
   }
   return NG_OK;
