@@ -75,6 +75,11 @@ int ng_test_wait_expires(unsigned long long limit_ns, unsigned long long* waited
 /* Number of kernels this library has launched so far in this process (its own kernels and the
  * generated element-wise ones; memcpy / memset / NCCL calls are not counted). */
 int ng_launch_count(unsigned long long* count);
+/* Tuning aids of the tensor-core engine (tile shape, partitions, CTA pairs ...), as the NG_*
+ * environment variables set them at start-up; `name` is the variable's name without the NG_
+ * prefix, in lower case ("pair_mma", "tile_rows", ...). For tests and measurements: results do
+ * not depend on them beyond fp32 summation order. No counterpart in the reference. */
+int ng_tune(const char* name, int value);
 /* Number of GEMM / convolution calls so far that ran on the plain CUDA-core fall-back kernels
  * (operands TMA cannot address, strided layers with fewer than 64 images) instead of the
  * tensor-core engine. A benchmark that claims the tensor-core path checks that this stays 0. */

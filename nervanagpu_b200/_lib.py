@@ -70,6 +70,7 @@ SIGNATURES = {
     "ng_static_scratch_status": (c_int, [ctypes.POINTER(c_int)]),
     "ng_launch_count": (c_int, [ctypes.POINTER(c_ulonglong)]),
     "ng_fallback_launch_count": (c_int, [ctypes.POINTER(c_ulonglong)]),
+    "ng_tune": (c_int, [c_char_p, c_int]),
     "ng_graph_capture_begin": (c_int, [c_void_p]),
     "ng_graph_capture_end": (c_int, [c_void_p, ctypes.POINTER(c_void_p)]),
     "ng_graph_launch": (c_int, [c_void_p, c_void_p]),

@@ -154,6 +154,14 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
   p.nz = g.batch;
   p.num_kb = (g.k + kChunk - 1) / kChunk;
   tc_pick_tile_rows(c, p, static_cast<long long>(p.tiles_n) * p.nz, p.num_kb);
+  // Two or more row tiles and 128 or 256 columns: CTA pairs (a 256-row tile over two SMs, each of
+  // which loads half of the B columns).
+  if (tuning().pair_mma == 1 && g.m > kTileM && p.block_n >= 128) {
+    p.pair = 1;
+    p.m_halves = 1;
+    p.tiles_m = (g.m + 2 * kTileM - 1) / (2 * kTileM);
+  }
+  const int bn_cta = p.pair ? p.block_n / 2 : p.block_n;
   TcOperandLayout lay;
   lay.a_mn_major = g.a_t ? 1 : 0;   // stored k x m: m contiguous
   lay.b_mn_major = g.b_t ? 0 : 1;   // stored k x n: n contiguous
@@ -162,7 +170,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
   // chunk number as a dimension of its own, and one box brings a 128-row half (a column tile)
   const bool merge_off = tuning().merge_boxes == 0;
   lay.a_merge = !merge_off && g.a_t && g.m % kChunk == 0;
-  lay.b_merge_static = !merge_off && !g.b_t && g.n % kChunk == 0 && p.block_n >= 2 * kChunk;
+  lay.b_merge_static = !merge_off && !g.b_t && g.n % kChunk == 0 && bn_cta >= 2 * kChunk;
   tc_fill_mma(p, lay);
   p.a_zmul = g.az != 0; p.b_zmul = g.bz != 0;
   p.C = g.C; p.Cold = g.beta != 0.0f ? g.C : nullptr;
@@ -202,7 +210,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
     uint64_t dims[5] = {1, 1, 1, 1, 1};
     uint64_t str[4] = {16, 16, 16, 16};
     uint32_t box[5] = {kChunk, 1, 1, 1, 1};
-    if (g.b_t) { dims[0] = g.k; dims[1] = g.n; box[1] = p.block_n; }
+    if (g.b_t) { dims[0] = g.k; dims[1] = g.n; box[1] = bn_cta; }
     else       { dims[0] = g.n; dims[1] = g.k; box[1] = kChunk; }
     dims[2] = g.bz != 0 ? g.batch : 1;
     str[0] = static_cast<uint64_t>(g.ldb) * 2;
@@ -214,7 +222,7 @@ int run_gemm(const GemmCall& g, cudaStream_t stream) {
       str[0] = static_cast<uint64_t>(g.ldb) * 2; str[1] = 128;
       str[2] = g.bz != 0 ? static_cast<uint64_t>(g.bz) * 2 : str[0] * dims[1];
       str[3] = str[2] * dims[3];
-      box[1] = kChunk; box[2] = p.block_n / kChunk;
+      box[1] = kChunk; box[2] = bn_cta / kChunk;
     }
     int rc = make_tensor_map(&mapB, g.B, dims, str, box);
     if (rc != NG_OK) return rc;

@@ -33,6 +33,9 @@ struct TcParams {
   int block_n;         // UMMA N: 64, 128 or 256
   int m_halves;        // 1: 128-row tiles, accumulator double-buffered across tiles
                        // 2: 256-row tiles, two accumulators that share every B operand
+  int pair;            // 1: CTA pairs (cta_group::2): a work item is 256 rows x block_n columns, each CTA
+                       // of the pair holds 128 rows of A and block_n / 2 columns of B; needs m_halves == 1
+                       // and tiles_m counted in 256-row tiles
   int acc_groups;      // weight update only: accumulators per work item (taps z*g .. z*g+g-1 share
                        // every B operand); 1 otherwise. Needs m_halves == 1, g * block_n <= 512.
   int acc_taps;        // weight update only: taps stacked along the rows of one accumulator (each
@@ -110,6 +113,7 @@ struct TcParams {
   // divisors of the tile / chunk / tap decodes, filled in by the launch code
   FastDiv fd_tiles_m, fd_tiles_n, fd_nz, fd_cpi, fd_q, fd_p, fd_RS, fd_S, fd_red, fd_crow;
   unsigned long long wait_limit_ns;   // bound of every wait inside the kernel
+  int debug_noload;                   // measurement aid: the producer signals full slots without loading anything
 };
 
 }  // namespace ngb

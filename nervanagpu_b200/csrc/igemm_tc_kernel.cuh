@@ -128,7 +128,13 @@ __device__ __forceinline__ WorkItem decode_work(const TcParams& p, int w) {
 // code, which keeps the single-warp roles' loops short in the instruction cache.
 // kLean instances serve the common output stage only (tiles staged through shared memory,
 // alpha 1, no beta term, round to nearest, or raw split-K partials) and carry no other.
-template <int kMode, bool kLean>
+// kPair instances run as clusters of two CTAs on the two SMs of a pair (tcgen05 cta_group::2):
+// a work item is a tile of 256 rows, 128 in the tensor memory of each CTA; each CTA loads its own
+// 128 rows of A and its own half of the columns of B (plain TMA loads, no multicast) and the MMA,
+// issued by one thread of the first CTA, reads both halves of B from the two shared memories. Per
+// flop each SM takes in a third fewer operand bytes than with a 128-row tile of its own, and the
+// accumulators stay double-buffered across tiles.
+template <int kMode, bool kLean, bool kPair = false>
 __global__ void __launch_bounds__(kTcThreads, 1)
 igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB,
                 const __grid_constant__ CUtensorMap mapBm, const __grid_constant__ TcParams p) {
@@ -155,6 +161,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   const int lane = threadIdx.x & 31;
   const int total_work = p.total_items;   // tiles_m * tiles_n * nz * splits, plus the halves of a cut last wave
   const uint32_t tmem_cols = 512;  // 2 accumulators of up to 256 columns
+  // CTA pairs: rank of this CTA in its pair; both walk the pair's work items
+  const uint32_t rank = kPair ? cluster_cta_rank() : 0u;
+  const int w_first = kPair ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int w_step = kPair ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int row_shift = kPair ? static_cast<int>(rank) * kTileM : 0;              // this CTA's rows of the tile
+  const int col_shift = kPair ? static_cast<int>(rank) * (p.block_n >> 1) : 0;    // its columns of B
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.stages; ++s) {
@@ -163,7 +175,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(accf_bar(a), 1);
-      mbar_init(acce_bar(a), kEpiWarps);
+      mbar_init(acce_bar(a), kPair ? 2 * kEpiWarps : kEpiWarps);   // (pairs: both CTAs' epilogues report to the first)
     }
     *abort_flag = 0;
     mbar_fence_init();
@@ -174,11 +186,17 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     if (p.b_merge == 1 || p.b_merge == 2) tma_prefetch_desc(&mapBm);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), tmem_cols);
-    tmem_relinquish();
+    if (kPair) {
+      tmem_alloc_pair(smem_u32(tmem_slot), tmem_cols);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(tmem_slot), tmem_cols);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
+  if (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
@@ -194,11 +212,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+    for (int w = w_first; w < total_work && ok; w += w_step) {
       const WorkItem it = decode_work(p, w);
       if (it.live == 0) continue;
-      const int m0 = it.m0;
-      const int n0 = it.tile_n * p.block_n;
+      const int m0 = it.m0 * (kPair ? 2 : 1) + row_shift;
+      const int n0 = it.tile_n * p.block_n + col_shift;
       // an item that computes one half of a 256-row tile needs only that half's A boxes when they
       // are separate boxes (MN-major A); a K-major A box always carries all its rows
       const int a_live = (p.m_halves == 2 && it.live == 1 && p.a_mn_major) ? (p.a_boxes >> 1) : p.a_boxes;
@@ -340,13 +358,24 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
         if (act) coords(wk, c0, c1, c2, c3, c4);
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER, p.wait_limit_ns);
-        if (lane == 0 && got) mbar_expect_tx(full_bar(stage), tx_item);
+        // (pairs: the operands of both CTAs are counted on the first CTA's barrier)
+        if (p.debug_noload) {
+          if (lane == 0 && got && rank == 0) mbar_arrive(full_bar(stage));
+          advance(wk);
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          continue;
+        }
+        if (lane == 0 && got && rank == 0) mbar_expect_tx(full_bar(stage), kPair ? 2u * tx_item : tx_item);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
           break;
         }
         if (act) {
-          tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
+          if (kPair)
+            tma_load_5d_pair(smem_base + stage * p.stage_bytes + box_off, map, map_to_cta(full_bar(stage), 0u), c0, c1,
+                             c2, c3, c4);
+          else
+            tma_load_5d(smem_base + stage * p.stage_bytes + box_off, map, full_bar(stage), c0, c1, c2, c3, c4);
         }
         advance(wk);
         if (++stage == p.stages) { stage = 0; phase ^= 1u; }
@@ -357,7 +386,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     // m_halves == 1: accumulator `local & 1` (double-buffered across tiles), barriers accf/acce[acc].
     // m_halves == 2: both accumulators belong to one 256-row tile; acce[h] says half h was drained,
     //                accf[0] says both halves are complete.
-    if (lane == 0) {
+    if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -366,7 +395,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
       // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
       const bool grouped = kMode == TC_UPDATE && (p.acc_groups > 1 || p.acc_taps > 1);
-      for (int w = blockIdx.x; w < total_work && ok; w += gridDim.x) {
+      for (int w = w_first; w < total_work && ok; w += w_step) {
         const WorkItem it = decode_work(p, w);
         if (it.live == 0) continue;     // `local` counts the items this CTA works on, in every role alike
         const int acc = (wide || grouped) ? 0 : (local & 1);
@@ -404,14 +433,28 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
                                      (p.a_desc_lo | ((sah + k * p.a_kstep) & 0x3fffu));
               const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
                                      (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
-              tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
+              if (kPair) tc_mma_f16_pair(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
+              else tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
             }
           }
           if (!ok) break;
-          tc_commit(empty_bar(stage));  // frees the smem slot once these MMAs have read it
+          // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
+          if (kPair) {
+            tc_commit_pair(map_to_cta(empty_bar(stage), 0u));
+            tc_commit_pair(map_to_cta(empty_bar(stage), 1u));
+          } else {
+            tc_commit(empty_bar(stage));
+          }
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
-        if (ok) tc_commit(accf_bar(acc));  // accumulator(s) complete
+        if (ok) {   // accumulator(s) complete
+          if (kPair) {
+            tc_commit_pair(map_to_cta(accf_bar(acc), 0u));
+            tc_commit_pair(map_to_cta(accf_bar(acc), 1u));
+          } else {
+            tc_commit(accf_bar(acc));
+          }
+        }
         ++local;
       }
     }
@@ -443,9 +486,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     const bool grouped = kMode == TC_UPDATE && (p.acc_groups > 1 || p.acc_taps > 1);
     const int n_acc = wide ? 2 : p.acc_groups;   // accumulators of one work item
     int local = 0;
-    for (int w = blockIdx.x; w < total_work; w += gridDim.x) {
-      const WorkItem it = decode_work(p, w);
+    for (int w = w_first; w < total_work; w += w_step) {
+      WorkItem it = decode_work(p, w);
       if (it.live == 0) continue;
+      if (kPair) it.m0 = it.m0 * 2 + row_shift;
       const int acc = (wide || grouped) ? 0 : (local & 1);
       const uint32_t acc_phase = (wide || grouped) ? (local & 1u) : ((local >> 1) & 1u);
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE, p.wait_limit_ns)) break;
@@ -626,8 +670,9 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         const int n_chunks = p.block_n / 32;
         const int c_begin = col_group == 0 ? 0 : (n_chunks + 1) / 2;
         const int c_end = col_group == 0 ? (n_chunks + 1) / 2 : n_chunks;
-        const bool from_regs = !kLean && !staged;   // (lean instances always stage)
-        for (int c = c_begin; from_regs && half_live && c < c_end; ++c) {
+        // (lean instances always stage: the loop bound is 0 for them)
+        const int c_stop = (kLean || staged || !half_live) ? c_begin : c_end;
+        for (int c = c_begin; c < c_stop; ++c) {
           uint32_t r[32];
           tc_ld_32x32(taddr + static_cast<uint32_t>(c * 32), r);
           tc_wait_ld();
@@ -661,7 +706,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!wide) {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(acce_bar(acc));
+        if (lane == 0) {
+          if (kPair) mbar_arrive_cluster(map_to_cta(acce_bar(acc), 0u));
+          else mbar_arrive(acce_bar(acc));
+        }
       }
       ++local;
     }
@@ -677,9 +725,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     while (global_timer_ns() - t0 < 200000ull) __nanosleep(1000);
     __syncthreads();
   }
+  if (kPair) cluster_sync_all();   // neither CTA leaves while the other may still read its shared memory
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, tmem_cols);
+    if (kPair) tmem_dealloc_pair(tmem_base, tmem_cols);
+    else tmem_dealloc(tmem_base, tmem_cols);
   }
 }
 

@@ -29,10 +29,14 @@ int cuda_fail(cudaError_t e, const char* what) {
   return fail(NG_ERR_CUDA, "CUDA error %d (%s) in %s", static_cast<int>(e), cudaGetErrorString(e), what);
 }
 
+static Tuning g_tuning;
+Tuning& tuning_mutable() { return const_cast<Tuning&>(tuning()); }
+
 const Tuning& tuning() {
-  static Tuning t;
+  Tuning& t = g_tuning;
   static std::once_flag once;
   std::call_once(once, [] {
+    Tuning& t = g_tuning;
     auto num = [](const char* name, int unset) {
       const char* v = getenv(name);
       return v && *v ? atoi(v) : unset;
@@ -51,6 +55,7 @@ const Tuning& tuning() {
     t.pair_mma = num("NG_PAIR_MMA", -1);
     t.max_ctas = num("NG_MAX_CTAS", 0);
     t.conv_splits = num("NG_CONV_SPLITS", -1);
+    t.max_stages = num("NG_MAX_STAGES", 0);
   });
   return t;
 }
@@ -353,6 +358,24 @@ int ng_launch_count(unsigned long long* count) {
   if (!count) return fail(NG_ERR_INVALID_ARG, "count is null");
   *count = g_launches.load(std::memory_order_relaxed);
   return NG_OK;
+}
+
+int ng_tune(const char* name, int value) {
+  if (!name) return fail(NG_ERR_INVALID_ARG, "name is null");
+  Tuning& t = tuning_mutable();
+  struct Field { const char* name; int* slot; };
+  const Field fields[] = {
+      {"tile_rows", &t.tile_rows}, {"tile_cols", &t.tile_cols}, {"kb_rows", &t.kb_rows},
+      {"reduce_lanes", &t.reduce_lanes}, {"update_groups", &t.update_groups}, {"update_stack", &t.update_stack},
+      {"update_min_stages", &t.update_min_stages}, {"max_ctas", &t.max_ctas}, {"conv_splits", &t.conv_splits},
+      {"max_stages", &t.max_stages}, {"merge_boxes", &t.merge_boxes}, {"split_tail", &t.split_tail},
+      {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}};
+  for (const Field& f : fields)
+    if (strcmp(f.name, name) == 0) {
+      *f.slot = value;
+      return NG_OK;
+    }
+  return fail(NG_ERR_INVALID_ARG, "unknown tuning field '%s'", name);
 }
 
 int ng_fallback_launch_count(unsigned long long* count) {

@@ -68,9 +68,11 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   p.mma_per_kb = lay.kb_rows / 16;
   // Instruction descriptor (kind::f16): D fp32 [4,6)=1, A/B fp16 (format 0), major-ness bits
   // 15/16 (1 = MN-major), N>>3 in [17,23), M>>4 in [24,29).
+  // (CTA pairs: M = 256, 128 rows in each CTA; N = block_n, half of the columns from each CTA)
   p.idesc = (1u << 4) | (static_cast<uint32_t>(lay.a_mn_major) << 15) |
             (static_cast<uint32_t>(lay.b_mn_major) << 16) | (static_cast<uint32_t>(p.block_n >> 3) << 17) |
-            (static_cast<uint32_t>(kTileM >> 4) << 24);
+            (static_cast<uint32_t>((p.pair ? 2 * kTileM : kTileM) >> 4) << 24);
+  const int bn_cta = p.pair ? p.block_n / 2 : p.block_n;   // columns of B this CTA holds
   // K-major operand: one box of [rows][64 k] 128-byte rows; 8-row groups 1024 B apart; a K=16
   // step moves the start address 32 B inside the swizzled row.
   // MN-major operand: boxes of [kb_rows][64 mn]; 8 reduction rows = 1024 B (stride offset),
@@ -112,8 +114,8 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   if (lay.b_mn_major) {
     // one box per 64-column chunk, or (b_merge_static) one box for the whole column tile
     // (b_pair: one box per pixel, its two image groups)
-    const int per_box = lay.b_merge_static ? p.block_n / kChunk : (lay.b_pair ? 2 : 1);
-    p.b_boxes = p.block_n / kChunk / per_box;
+    const int per_box = lay.b_merge_static ? bn_cta / kChunk : (lay.b_pair ? 2 : 1);
+    p.b_boxes = bn_cta / kChunk / per_box;
     p.b_box_bytes = per_box * mn_box;
     if (lay.b_merge_static) p.b_merge = 3;
     if (lay.b_pair) p.b_merge = 4;
@@ -123,7 +125,7 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
     // one box of block_n rows, or several shorter ones stacked (rows past the last box keep stale
     // data: their products are columns that the caller never reads)
     p.b_boxes = lay.b_box_count > 0 ? lay.b_box_count : 1;
-    p.b_box_bytes = static_cast<uint32_t>(lay.b_box_count > 0 ? lay.b_box_rows : p.block_n) * 128u;
+    p.b_box_bytes = static_cast<uint32_t>(lay.b_box_count > 0 ? lay.b_box_rows : bn_cta) * 128u;
     p.b_desc_lo = desc_lo(16);
     p.b_kstep = 32u >> 4;
   }
@@ -131,11 +133,12 @@ void tc_fill_mma(TcParams& p, const TcOperandLayout& lay) {
   // every box must start on a 1024-byte boundary for the 128-byte swizzle
   p.a_bytes = (p.a_bytes + 1023u) & ~1023u;
   uint32_t b_bytes = (p.b_boxes * p.b_box_bytes + 1023u) & ~1023u;
-  if (!lay.b_mn_major) b_bytes = std::max(b_bytes, static_cast<uint32_t>(p.block_n) * 128u);
+  if (!lay.b_mn_major) b_bytes = std::max(b_bytes, static_cast<uint32_t>(bn_cta) * 128u);
   p.stage_bytes = p.a_bytes + b_bytes;
   p.tx_bytes = p.a_boxes * p.a_box_bytes + p.b_boxes * p.b_box_bytes;
   p.stages = std::min<uint32_t>(kMaxStages, (kSmemLimit - 1024u - kCtrlBytes - kEpiStageBytes - a_overread(p)) /
                                                p.stage_bytes);
+  if (tuning().max_stages > 0) p.stages = std::min<int>(p.stages, tuning().max_stages);
 }
 
 // How tiles leave the epilogue: 1 = staged through swizzled shared memory and written out by the
@@ -303,6 +306,14 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     NG_TC_SMEM_ATTR(TC_BPROP);
     NG_TC_SMEM_ATTR(TC_UPDATE);
 #undef NG_TC_SMEM_ATTR
+#define NG_TC_SMEM_ATTR_PAIR(mode)                                                                                 \
+  NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<mode, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                               kSmemLimit));                                                                       \
+  NG_CUDA(cudaFuncSetAttribute(igemm_tc_kernel<mode, true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit))
+    NG_TC_SMEM_ATTR_PAIR(TC_GEMM);
+    NG_TC_SMEM_ATTR_PAIR(TC_FPROP);
+    NG_TC_SMEM_ATTR_PAIR(TC_BPROP);
+#undef NG_TC_SMEM_ATTR_PAIR
     c->smem_attr_set = true;
   }
   long long total = static_cast<long long>(p.tiles_m) * p.tiles_n * p.nz * p.splits;
@@ -319,10 +330,16 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   p.total_items = static_cast<int>(total);
   int grid = static_cast<int>(std::min<long long>(total, c->sm_count));
   if (tuning().max_ctas > 0) grid = std::min(grid, tuning().max_ctas);
+  if (p.pair) {
+    if (p.m_halves != 1 || p.acc_groups > 1 || p.acc_taps > 1 || p.mode == TC_UPDATE || (p.block_n & 127))
+      return fail(NG_ERR_INVALID_ARG, "internal: this tiling cannot run on CTA pairs");
+    grid = 2 * static_cast<int>(std::min<long long>(total, c->sm_count / 2));   // one pair per work item in flight
+  }
   p.store_staged = pick_store_mode(p);
   if (p.c_row_chunks && !p.store_staged)
     return fail(NG_ERR_UNSUPPORTED, "internal: padded image rows need the staged output stage");
   if (!p.wait_limit_ns) p.wait_limit_ns = c->wait_limit_ns;
+  p.debug_noload = getenv("NG_DEBUG_NOLOAD") ? 1 : 0;
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.store_staged ? kEpiStageBytes : 0u) +
                         a_overread(p);
   fill_fast_divs(p);
@@ -337,6 +354,31 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   // the lean instances: staged tiles, and either raw split-K partials or alpha 1 / no beta / round to nearest
   const bool lean = tuning().lean_kernels != 0 && launch.store_staged &&
                     (launch.splits > 1 || (launch.alpha == 1.0f && launch.beta == 0.0f && launch.sr_bits == 0));
+  if (launch.pair) {
+    // clusters of two CTAs
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kTcThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+#define NG_TC_LAUNCH_PAIR(mode)                                                                              \
+  if (lean) NG_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<mode, true, true>, mapA, mapB, mapB2, launch));  \
+  else NG_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<mode, false, true>, mapA, mapB, mapB2, launch))
+    switch (launch.mode) {
+      case TC_GEMM: NG_TC_LAUNCH_PAIR(TC_GEMM); break;
+      case TC_FPROP: NG_TC_LAUNCH_PAIR(TC_FPROP); break;
+      case TC_BPROP: NG_TC_LAUNCH_PAIR(TC_BPROP); break;
+      default: return fail(NG_ERR_INVALID_ARG, "internal: no CTA-pair instance of this mode");
+    }
+#undef NG_TC_LAUNCH_PAIR
+  } else
 #define NG_TC_LAUNCH(mode)                                                                                      \
   if (lean) igemm_tc_kernel<mode, true><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch);   \
   else igemm_tc_kernel<mode, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch)

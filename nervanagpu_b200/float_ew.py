@@ -475,6 +475,20 @@ class _Emitter(object):
                 expr = "((int)p%d[col] == row ? 1.0f : 0.0f)" % node.slot
             else:
                 expr = "((int)p%d[row] == col ? 1.0f : 0.0f)" % node.slot
+        elif (node.name == "div" and len(node.children) == 2 and node.children[1].scalar
+              and not node.children[0].scalar):
+            # x / s with s fixed for the whole row (a reduction result, a constant): the reciprocal
+            # is taken once per row and every element multiplies by it. An IEEE division per
+            # element made the batch-norm kernel issue-bound; the product differs from the
+            # quotient by at most one fp32 ulp.
+            num = self.emit(node.children[0], loop_names, loop_lines)
+            den = self.emit_row(node.children[1])
+            inv_key = ("recip", node.children[1].key)
+            if inv_key not in self.row_names:
+                inv = self.fresh("s")
+                self.row_lines.append("const float %s = 1.0f / %s;" % (inv, den))
+                self.row_names[inv_key] = inv
+            expr = "(%s * %s)" % (num, self.row_names[inv_key])
         else:
             names = [self.emit(c, loop_names, loop_lines) for c in node.children]
             expr = _float_ops[node.name][1].format(*names)

@@ -251,3 +251,46 @@ def test_stochastic_rounding_gemm(ng):
     sr.dot(dA, dB, C3, stochastic_round=0)
     assert np.array_equal(C3.get(), ref.astype(np.float16)) or \
         (np.abs(C3.get().astype(np.float32) - ref) <= 2.0 ** -10 * np.abs(ref) + eps).all()
+
+
+def _kahan_model(s, c, a, cmp_scale, add_scale):
+    """numpy restatement of the reference's compensated_sum kernel (nervanagpu/float_ew.py:1430-1482):
+    every intermediate in fp32, the new sum and the new compensation rounded to the storage type."""
+    f32 = np.float32
+    s32, c32, a32 = s.astype(f32), c.astype(f32), a.astype(f32)
+    y = a32 * f32(add_scale) - c32 * f32(cmp_scale)
+    t = (s32 + y).astype(s.dtype)
+    c_new = ((t.astype(f32) - s32) - y).astype(s.dtype)
+    return t, c_new
+
+
+@pytest.mark.parametrize("dtype", [np.float16, np.float32])
+def test_compensated_sum_matches_the_kahan_model_and_keeps_small_updates(ng, dtype):
+    rng = np.random.default_rng(17)
+    shape = (96, 200)
+    s = rng.normal(0, 1, shape).astype(dtype)
+    c = np.zeros(shape, dtype)
+    dS, dC = ng.array(s, dtype=dtype), ng.array(c, dtype=dtype)
+    naive = s.copy()
+    exact = s.astype(np.float64)
+    for i in range(40):
+        a = (rng.normal(0, 1, shape) * 2.0 ** -9).astype(dtype)      # far below one ulp of most sums (fp16)
+        ng.compensated_sum(dS, dC, ng.array(a, dtype=dtype), cmp_scale=1.0, add_scale=0.5)
+        s, c = _kahan_model(s, c, a, 1.0, 0.5)
+        naive = (naive.astype(np.float32) + a.astype(np.float32) * np.float32(0.5)).astype(dtype)
+        exact += a.astype(np.float64) * 0.5
+        assert np.array_equal(dS.get(), s), "sum after %d steps" % (i + 1)
+        assert np.array_equal(dC.get(), c), "compensation after %d steps" % (i + 1)
+    assert dC.kahan_count == 40
+    if dtype is np.float16:
+        # the point of the compensation: the fp16 running sum stays close to the exact one
+        err_kahan = np.abs(s.astype(np.float64) - exact).mean()
+        err_naive = np.abs(naive.astype(np.float64) - exact).mean()
+        assert err_kahan < 0.25 * err_naive
+    # kahan_reset: after that many steps the old compensation is dropped (cmp_scale = 0)
+    dC.kahan_reset = 2
+    dC.kahan_count = 3
+    a = (rng.normal(0, 1, shape) * 2.0 ** -9).astype(dtype)
+    ng.compensated_sum(dS, dC, ng.array(a, dtype=dtype))
+    s2, c2 = _kahan_model(s, c, a, 0.0, 1.0)
+    assert np.array_equal(dS.get(), s2) and np.array_equal(dC.get(), c2) and dC.kahan_count == 1

@@ -154,3 +154,26 @@ def test_dot_argument_errors(ng):
                ng.empty((4, 4), dtype=np.float32))
     with pytest.raises(TypeError):
         ng.dot(ng.empty((4, 4), dtype=np.int8), ng.empty((4, 4), dtype=np.int8), ng.empty((4, 4), dtype=np.int8))
+
+
+@pytest.mark.parametrize("op", ["nn", "nt", "tn"])
+def test_cta_pair_instances_match_the_oracle(ng, lib, op):
+    """The two-SM form of the tensor-core kernel (tcgen05 cta_group::2, switched on with the
+    "pair_mma" tuning field): a 256-row tile is shared by the two CTAs of a cluster, each of which
+    loads its own half of the B columns. Same results as the one-CTA kernel up to summation order."""
+    rng = np.random.default_rng(31)
+    try:
+        assert lib.ng_tune(b"pair_mma", 1) == 0
+        for (m, n, k) in [(512, 512, 256), (384, 256, 1024), (1000, 136, 520), (256, 128, 64)]:
+            A, B = _operands(rng, m, n, k, op, std=0.1)
+            C0 = rng.standard_normal((m, n)).astype(np.float16)
+            got = _dot(ng, A, B, op, C0=C0, alpha=0.5, beta=0.25, relu=True)
+            ref = rm.gemm(A, B, op[0] == "t", op[1] == "t", alpha=0.5, beta=0.25, relu=True, C=C0)
+            tol = rn16_tol(ref, rm.gemm_abs(A, B, op[0] == "t", op[1] == "t"), k) + 2.0 ** -11 * np.abs(C0.astype(np.float32))
+            assert_close(got, ref, tol, "pair %s %s" % (op, (m, n, k)))
+            plain = _dot(ng, A, B, op)
+            ref = rm.gemm(A, B, op[0] == "t", op[1] == "t")
+            assert_close(plain, ref, rn16_tol(ref, rm.gemm_abs(A, B, op[0] == "t", op[1] == "t"), k), "pair plain")
+    finally:
+        assert lib.ng_tune(b"pair_mma", -1) == 0
+    assert lib.ng_sync() == 0
