@@ -214,6 +214,73 @@ __device__ __forceinline__ void tc_mma_f16(uint32_t d_tmem, uint64_t adesc, uint
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same with the descriptors given as (low, high) words, so that the issuing thread steps the
+// start-address field with one 32-bit add per operand and K step. kPair: the two-SM form below.
+template <bool kPair>
+__device__ __forceinline__ void tc_mma_f16_words(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                                 uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (kPair) {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " .reg .b64 da, db;\n"
+        " setp.ne.b32 p, %6, 0;\n"
+        " mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n"
+        " .reg .pred p;\n"
+        " .reg .b64 da, db;\n"
+        " setp.ne.b32 p, %6, 0;\n"
+        " mov.b64 da, {%1, %2};\n"
+        " mov.b64 db, {%3, %4};\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+        : "memory");
+  }
+}
+// kCount (1..4) MMAs of one k-block into one accumulator as a single block of PTX: the first takes
+// `accumulate`, the others add; the start-address fields step by a_kstep / b_kstep (16-byte units)
+// from one to the next. One statement, so that no control flow of the surrounding loop ends up
+// between the MMAs: the issuing thread has to get each of them out in well under the 128 cycles
+// the tensor pipe spends on it.
+template <bool kPair, int kCount>
+__device__ __forceinline__ void tc_mma_f16_run(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                               uint32_t b_hi, uint32_t idesc, uint32_t accumulate, uint32_t a_kstep,
+                                               uint32_t b_kstep) {
+#define NG_MMA_OP(group) " tcgen05.mma.cta_group::" group ".kind::f16 [%0], da, db, %5, "
+#define NG_MMA_STEP(group)                                       \
+  " add.u32 al, al, %7;\n add.u32 bl, bl, %8;\n"                \
+  " mov.b64 da, {al, %2};\n mov.b64 db, {bl, %4};\n" NG_MMA_OP(group) "q;\n"
+#define NG_MMA_RUN(group, more)                                                                            \
+  asm volatile(                                                                                            \
+      "{\n .reg .pred p, q;\n .reg .b64 da, db;\n .reg .b32 al, bl;\n"                                    \
+      " setp.ne.b32 p, %6, 0;\n setp.eq.b32 q, %6, %6;\n mov.b32 al, %1;\n mov.b32 bl, %3;\n"            \
+      " mov.b64 da, {al, %2};\n mov.b64 db, {bl, %4};\n" NG_MMA_OP(group) "p;\n" more "}\n"               \
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(a_kstep), \
+      "r"(b_kstep)                                                                                         \
+      : "memory")
+  if (kPair) {
+    if (kCount == 1) NG_MMA_RUN("2", "");
+    else if (kCount == 2) NG_MMA_RUN("2", NG_MMA_STEP("2"));
+    else if (kCount == 3) NG_MMA_RUN("2", NG_MMA_STEP("2") NG_MMA_STEP("2"));
+    else NG_MMA_RUN("2", NG_MMA_STEP("2") NG_MMA_STEP("2") NG_MMA_STEP("2"));
+  } else {
+    if (kCount == 1) NG_MMA_RUN("1", "");
+    else if (kCount == 2) NG_MMA_RUN("1", NG_MMA_STEP("1"));
+    else if (kCount == 3) NG_MMA_RUN("1", NG_MMA_STEP("1") NG_MMA_STEP("1"));
+    else NG_MMA_RUN("1", NG_MMA_STEP("1") NG_MMA_STEP("1") NG_MMA_STEP("1"));
+  }
+#undef NG_MMA_RUN
+#undef NG_MMA_STEP
+#undef NG_MMA_OP
+}
 // The two-SM form: D is 256 rows (128 in the tensor memory of each CTA of the pair), A comes from
 // both CTAs' shared memory (128 rows each), B likewise (half of the columns each), all at the
 // same offsets; issued by one thread of the pair's first CTA.

@@ -286,16 +286,19 @@ __global__ void conv_update_simt(Geo g, const __half* __restrict__ I, const __ha
 // ------------------------------------------------------------------------------------------
 // im2col: col[crst][pixel * N + n] = I[c, z, y, x, n] (zero outside the image); 8 images per thread
 // ------------------------------------------------------------------------------------------
-// grid: x covers (q, 8-image lane) of one output row, y = (m, p) row, z = (c, t, r, s) patch row,
-// so the only per-thread division is by the lane count.
+// grid: x covers the (m, p, q, 8-image lane) positions of one patch row, y = (c, t, r, s) patch row
+// (whole blocks of live threads whatever N is: with 16 images an output row is only 110 lanes wide)
 __global__ void __launch_bounds__(256) im2col_kernel(Geo g, const __half* __restrict__ I, __half* __restrict__ col) {
   const int n8 = g.N / 8;
-  const int t0 = blockIdx.x * blockDim.x + threadIdx.x;
-  const int q = t0 / n8;
-  if (q >= g.Q) return;
-  const int nv = t0 - q * n8;
-  const int p = blockIdx.y % g.P, m = blockIdx.y / g.P;
-  int r = blockIdx.z;
+  const long long per_row = 1ll * g.M * g.P * g.Q * n8;
+  const long long t0 = blockIdx.x * 256ll + threadIdx.x;
+  if (t0 >= per_row) return;
+  const int nv = static_cast<int>(t0 % n8);
+  long long pix = t0 / n8;
+  const int q = static_cast<int>(pix % g.Q); pix /= g.Q;
+  const int p = static_cast<int>(pix % g.P);
+  const int m = static_cast<int>(pix / g.P);
+  int r = blockIdx.y;
   const int s = r % g.S; r /= g.S;
   const int rr = r % g.R; r /= g.R;
   const int t = r % g.T;
@@ -304,12 +307,12 @@ __global__ void __launch_bounds__(256) im2col_kernel(Geo g, const __half* __rest
   uint4 v = make_uint4(0, 0, 0, 0);
   if (z >= 0 && z < g.D && y >= 0 && y < g.H && x >= 0 && x < g.W)
     v = *reinterpret_cast<const uint4*>(I + (((1ll * c * g.D + z) * g.H + y) * g.W + x) * g.N + nv * 8);
-  const long long row = blockIdx.z, pix = (1ll * m * g.P + p) * g.Q + q;
-  reinterpret_cast<uint4*>(col)[(row * g.M * g.P * g.Q + pix) * n8 + nv] = v;
+  reinterpret_cast<uint4*>(col)[blockIdx.y * per_row + t0] = v;
 }
 
 dim3 im2col_grid(const Geo& g) {
-  return dim3((g.Q * (g.N / 8) + 255) / 256, g.M * g.P, g.C * g.T * g.R * g.S);
+  const long long per_row = 1ll * g.M * g.P * g.Q * (g.N / 8);
+  return dim3(static_cast<unsigned>((per_row + 255) / 256), g.C * g.T * g.R * g.S, 1);
 }
 
 int launch_1d(long long total, int threads, const DeviceCtx* c) {
@@ -651,7 +654,7 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
     const long long span = 1ll * g.M * g.P * g.Q * g.N;
     const bool small_c = g.C < 16 && path == NG_PATH_AUTO;
     const bool im2col = (small_c || path == NG_PATH_IM2COL) && al && span <= 0x7fffffffll &&
-                        1ll * g.C * RST * span * 2 <= (6ll << 30) && g.M * g.P <= 65535 && g.C * RST <= 65535;
+                        1ll * g.C * RST * span * 2 <= (6ll << 30) && g.C * RST <= 65535;
     if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
     if (im2col) {
       const size_t col_bytes = static_cast<size_t>(g.C) * RST * span * 2;
@@ -782,7 +785,7 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   const bool direct = path != NG_PATH_SIMT && path != NG_PATH_IM2COL && mode != CH_NONE && al &&
                       (g.C >= 16 || path == NG_PATH_TENSOR);
   const bool im2col = !direct && path != NG_PATH_SIMT && path != NG_PATH_TENSOR && al &&
-                      1ll * g.C * RST * span * 2 <= (6ll << 30) && g.M * g.P <= 65535 && g.C * RST <= 65535;
+                      1ll * g.C * RST * span * 2 <= (6ll << 30) && g.C * RST <= 65535;
   if (path == NG_PATH_TENSOR && !direct) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the tensor-core path");
   if (path == NG_PATH_IM2COL && !im2col) return fail(NG_ERR_UNSUPPORTED, "shape not addressable by the im2col path");
   if ((path == NG_PATH_AUTO || path == NG_PATH_TENSOR) && g.C < 16 && g.N % kChunk == 0 && al) {

@@ -356,12 +356,12 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
-        if (act) coords(wk, c0, c1, c2, c3, c4);
+        if (act && p.debug_noload != 2) coords(wk, c0, c1, c2, c3, c4);
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER, p.wait_limit_ns);
         // (pairs: the operands of both CTAs are counted on the first CTA's barrier)
         if (p.debug_noload) {
           if (lane == 0 && got && rank == 0) mbar_arrive(full_bar(stage));
-          advance(wk);
+          if (p.debug_noload != 2) advance(wk);
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
           continue;
         }
@@ -386,7 +386,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     // m_halves == 1: accumulator `local & 1` (double-buffered across tiles), barriers accf/acce[acc].
     // m_halves == 2: both accumulators belong to one 256-row tile; acce[h] says half h was drained,
     //                accf[0] says both halves are complete.
-    if (lane == 0 && rank == 0) {
+    // The whole warp walks the loop (every lane waits on the barriers) and lane 0 alone issues the
+    // MMAs and commits: a warp that stays converged gets through an iteration in fewer cycles than
+    // a single lane running inside a divergent branch does.
+    if (rank == 0) {
+      const bool issuer = lane == 0;
       int stage = 0;
       uint32_t phase = 0;
       int local = 0;
@@ -395,6 +399,21 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // acc_groups > 1 (weight update): one item accumulates several taps at once, accumulator g
       // for tap z*groups+g, all fed by the same B operand; TMEM is then one set, not two.
       const bool grouped = kMode == TC_UPDATE && (p.acc_groups > 1 || p.acc_taps > 1);
+      // Everything the issue loop needs sits in registers, and the loop does as little as it can:
+      // this one thread's instruction stream is serial, and every cycle it spends between two
+      // MMAs beyond the 128 the tensor pipe needs for one is a cycle the pipe idles. Descriptors
+      // are kept as (low, high) words whose start-address field is stepped by 32-bit adds (the
+      // ring lies below 256 KB, so the 14-bit field never carries), barrier addresses and the
+      // stage base are stepped, not recomputed, and a wait first tries the barrier once inline.
+      const uint32_t a_lo0 = p.a_desc_lo, a_hi = p.a_desc_hi, b_lo0 = p.b_desc_lo, b_hi = p.b_desc_hi;
+      const uint32_t a_kstep = p.a_kstep, b_kstep = p.b_kstep, a_half = p.a_half_step, idesc = p.idesc;
+      const int mma_per_kb = p.mma_per_kb, stages = p.stages;
+      const uint32_t ring0 = (smem_base >> 4) & 0x3fffu, stage_step = p.stage_bytes >> 4, b_off = p.a_bytes >> 4;
+      const uint32_t block_n = static_cast<uint32_t>(p.block_n);
+      const uint32_t full0 = full_bar(0);
+      const uint32_t empty0 = kPair ? map_to_cta(empty_bar(0), 0u) : empty_bar(0);
+      const uint32_t empty0_peer = kPair ? map_to_cta(empty_bar(0), 1u) : 0u;
+      uint32_t sa = ring0, fbar = full0, ebar = empty0, ebar_peer = empty0_peer;
       for (int w = w_first; w < total_work && ok; w += w_step) {
         const WorkItem it = decode_work(p, w);
         if (it.live == 0) continue;     // `local` counts the items this CTA works on, in every role alike
@@ -410,44 +429,94 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           if (!mbar_wait(acce_bar(acc), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC, p.wait_limit_ns)) break;
           tc_fence_after();
         }
-        for (int kb = it.kb0; kb < it.kb1 && ok; ++kb) {
-          if (!mbar_wait(full_bar(stage), phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA, p.wait_limit_ns)) {
-            ok = false;
-            break;
-          }
+        const uint32_t d_base = tmem_base + ((wide || grouped) ? 0u : static_cast<uint32_t>(acc) * block_n);
+        // One k-block: wait for its operands, issue its MMAs accumulator by accumulator (measured
+        // faster than interleaving them k-step by k-step), release the slot, step the ring.
+        auto wait_operands = [&]() -> bool {
+          if (!mbar_try_wait(fbar, phase) &&
+              !mbar_wait(fbar, phase, abort_flag, p.status, NG_DEV_TIMEOUT_MMA, p.wait_limit_ns))
+            return false;
           tc_fence_after();
-          const uint32_t sa = (smem_base + stage * p.stage_bytes) >> 4;
-          const uint32_t sb = (smem_base + stage * p.stage_bytes + p.a_bytes) >> 4;
-          // accumulator by accumulator (measured faster than interleaving them k-step by k-step)
-          const uint32_t acc_first = kb > it.kb0 ? 1u : 0u;
-          for (int h = 0; h < halves; ++h) {
-            if (wide && kb == it.kb0) {   // half h of the previous tile must have been drained
-              ok = mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC, p.wait_limit_ns);
-              if (!ok) break;
+          return true;
+        };
+        auto release_and_step = [&]() {
+          // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
+          if (issuer) {
+            if (kPair) {
+              tc_commit_pair(ebar);
+              tc_commit_pair(ebar_peer);
+            } else {
+              tc_commit(ebar);
+            }
+          }
+          sa += stage_step; fbar += 8u; ebar += 8u; ebar_peer += 8u;
+          if (++stage == stages) {
+            stage = 0; phase ^= 1u;
+            sa = ring0; fbar = full0; ebar = empty0; ebar_peer = empty0_peer;
+          }
+        };
+        auto run_any = [&](uint32_t d_tmem, uint32_t alo, uint32_t blo, uint32_t accumulate) {
+          switch (mma_per_kb) {   // (one block of PTX per accumulator and k-block: see tc_mma_f16_run)
+            case 4: tc_mma_f16_run<kPair, 4>(d_tmem, alo, a_hi, blo, b_hi, idesc, accumulate, a_kstep, b_kstep); break;
+            case 3: tc_mma_f16_run<kPair, 3>(d_tmem, alo, a_hi, blo, b_hi, idesc, accumulate, a_kstep, b_kstep); break;
+            case 2: tc_mma_f16_run<kPair, 2>(d_tmem, alo, a_hi, blo, b_hi, idesc, accumulate, a_kstep, b_kstep); break;
+            default: tc_mma_f16_run<kPair, 1>(d_tmem, alo, a_hi, blo, b_hi, idesc, accumulate, a_kstep, b_kstep); break;
+          }
+        };
+        // general form: any number of accumulators, the first k-block of an item included (it
+        // overwrites the accumulators, and with 256-row tiles waits for each half to be drained)
+        auto general_kb = [&](uint32_t accumulate) -> bool {
+          if (!wait_operands()) return false;
+          const uint32_t blo0 = b_lo0 | (sa + b_off);
+          uint32_t alo_h = a_lo0 | sa, d_tmem = d_base;
+          for (int h = 0; h < halves; ++h, alo_h += a_half, d_tmem += block_n) {
+            if (wide && accumulate == 0u) {   // half h of the previous tile must have been drained
+              if (!mbar_wait(acce_bar(h), acc_phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_ACC, p.wait_limit_ns))
+                return false;
               tc_fence_after();
             }
-            const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(((wide || grouped) ? h : acc) * p.block_n);
-            const uint32_t sah = sa + h * p.a_half_step;
-            for (int k = 0; k < p.mma_per_kb; ++k) {
-              const uint64_t adesc = (static_cast<uint64_t>(p.a_desc_hi) << 32) |
-                                     (p.a_desc_lo | ((sah + k * p.a_kstep) & 0x3fffu));
-              const uint64_t bdesc = (static_cast<uint64_t>(p.b_desc_hi) << 32) |
-                                     (p.b_desc_lo | ((sb + k * p.b_kstep) & 0x3fffu));
-              if (kPair) tc_mma_f16_pair(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
-              else tc_mma_f16(d_tmem, adesc, bdesc, p.idesc, k > 0 ? 1u : acc_first);
-            }
+            if (issuer) run_any(d_tmem, alo_h, blo0, accumulate);
           }
-          if (!ok) break;
-          // frees the smem slot (in both CTAs of a pair) once these MMAs have read it
-          if (kPair) {
-            tc_commit_pair(map_to_cta(empty_bar(stage), 0u));
-            tc_commit_pair(map_to_cta(empty_bar(stage), 1u));
-          } else {
-            tc_commit(empty_bar(stage));
+          release_and_step();
+          return true;
+        };
+        int kb = it.kb0;
+        ok = general_kb(0u);
+        ++kb;
+        // The steady state of the common tilings (one or two accumulators) runs in loops that hold
+        // nothing but the wait, the MMAs of a fixed count and the commit: with the accumulator
+        // loop, the count switch and the first-k-block test inside, the same work took the issuing
+        // warp ~900 cycles per k-block of four MMAs instead of ~570 (the tensor pipe needs 512).
+#define NG_STEADY_LOOP(count, two)                                                                                  \
+  for (; ok && kb < it.kb1; ++kb) {                                                                                 \
+    if (!wait_operands()) { ok = false; break; }                                                                    \
+    if (issuer) {                                                                                                   \
+      tc_mma_f16_run<kPair, count>(d_base, a_lo0 | sa, a_hi, b_lo0 | (sa + b_off), b_hi, idesc, 1u, a_kstep, b_kstep); \
+      if (two)                                                                                                      \
+        tc_mma_f16_run<kPair, count>(d_base + block_n, (a_lo0 | sa) + a_half, a_hi, b_lo0 | (sa + b_off), b_hi, idesc, \
+                                     1u, a_kstep, b_kstep);                                                         \
+    }                                                                                                               \
+    release_and_step();                                                                                             \
+  }
+        if (halves == 1) {
+          switch (mma_per_kb) {
+            case 4: NG_STEADY_LOOP(4, false) break;
+            case 3: NG_STEADY_LOOP(3, false) break;
+            case 2: NG_STEADY_LOOP(2, false) break;
+            default: NG_STEADY_LOOP(1, false) break;
           }
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        } else if (halves == 2) {
+          switch (mma_per_kb) {
+            case 4: NG_STEADY_LOOP(4, true) break;
+            case 3: NG_STEADY_LOOP(3, true) break;
+            case 2: NG_STEADY_LOOP(2, true) break;
+            default: NG_STEADY_LOOP(1, true) break;
+          }
+        } else {
+          for (; ok && kb < it.kb1; ++kb) ok = general_kb(1u);
         }
-        if (ok) {   // accumulator(s) complete
+#undef NG_STEADY_LOOP
+        if (ok && issuer) {   // accumulator(s) complete
           if (kPair) {
             tc_commit_pair(map_to_cta(accf_bar(acc), 0u));
             tc_commit_pair(map_to_cta(accf_bar(acc), 1u));
@@ -495,7 +564,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE, p.wait_limit_ns)) break;
       tc_fence_after();
       const int n0 = it.tile_n * p.block_n;
-      for (int h = 0; h < n_acc; ++h) {
+      for (int h = 0; h < (p.debug_noload >= 4 ? 0 : n_acc); ++h) {
         // accumulator h holds rows of row-tile `rt` of output slice `zt`; with stacked taps
         // (weight update, few rows per tap) every `pack_rows` lanes belong to the next slice
         const int rt = it.m0 / kTileM + (wide ? h : 0);

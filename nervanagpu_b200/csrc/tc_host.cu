@@ -339,7 +339,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   if (p.c_row_chunks && !p.store_staged)
     return fail(NG_ERR_UNSUPPORTED, "internal: padded image rows need the staged output stage");
   if (!p.wait_limit_ns) p.wait_limit_ns = c->wait_limit_ns;
-  p.debug_noload = getenv("NG_DEBUG_NOLOAD") ? 1 : 0;
+  p.debug_noload = getenv("NG_DEBUG_NOLOAD") ? atoi(getenv("NG_DEBUG_NOLOAD")) : 0;
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.store_staged ? kEpiStageBytes : 0u) +
                         a_overread(p);
   fill_fast_divs(p);
