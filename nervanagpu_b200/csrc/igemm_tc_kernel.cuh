@@ -352,11 +352,48 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       };
       // (Asking the L2 for the boxes of later k-blocks with prefetch copies was tried and was
       // slower everywhere: a prefetch costs the copy engine as much as the load it precedes.)
+      // Forward pass, and backward pass with unit strides: inside one tile every coordinate of a
+      // box is linear in the tap (t, r, s) and the reduction chunk. The offsets and the four
+      // steps are taken once per tile, as differences of the general formula above, and a k-block
+      // costs this warp five multiply-adds per coordinate instead of a walk through that formula
+      // (which the A and the B lanes take one after the other): with it the producer took about
+      // as long per k-block as the MMAs themselves and, being one serial warp, set the pace.
+      const bool linear = (kMode == TC_FPROP || (kMode == TC_BPROP && p.str_w == 1 && p.str_h == 1 && p.str_d == 1));
+      int lb0 = 0, lb1 = 0, lb2 = 0, lb3 = 0, lb4 = 0;          // coordinates at tap (0, 0, 0), chunk 0
+      int ls[5] = {0, 0, 0, 0, 0}, lr[5] = {0, 0, 0, 0, 0}, lt[5] = {0, 0, 0, 0, 0}, lc[5] = {0, 0, 0, 0, 0};
+      if (linear && act) {
+        Walk o = wk;
+        o.tap = {0, 0, 0}; o.trs = 0; o.rc = 0;
+        coords(o, lb0, lb1, lb2, lb3, lb4);
+        int d0, d1, d2, d3, d4;
+        Walk q = o;
+        q.tap.s = 1; q.trs = 1;
+        coords(q, d0, d1, d2, d3, d4);
+        ls[0] = d0 - lb0; ls[1] = d1 - lb1; ls[2] = d2 - lb2; ls[3] = d3 - lb3; ls[4] = d4 - lb4;
+        q = o; q.tap.r = 1; q.trs = p.S;
+        coords(q, d0, d1, d2, d3, d4);
+        lr[0] = d0 - lb0; lr[1] = d1 - lb1; lr[2] = d2 - lb2; lr[3] = d3 - lb3; lr[4] = d4 - lb4;
+        q = o; q.tap.t = 1; q.trs = p.RS;
+        coords(q, d0, d1, d2, d3, d4);
+        lt[0] = d0 - lb0; lt[1] = d1 - lb1; lt[2] = d2 - lb2; lt[3] = d3 - lb3; lt[4] = d4 - lb4;
+        q = o; q.rc = 1;
+        coords(q, d0, d1, d2, d3, d4);
+        lc[0] = d0 - lb0; lc[1] = d1 - lb1; lc[2] = d2 - lb2; lc[3] = d3 - lb3; lc[4] = d4 - lb4;
+      }
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
         // (All lanes poll: one polling lane plus a broadcast measured the same or slower.)
         int c0 = 0, c1 = 0, c2 = 0, c3 = 0, c4 = 0;
-        if (act && p.debug_noload != 2) coords(wk, c0, c1, c2, c3, c4);
+        if (linear) {
+          const int ts = wk.tap.s, tr = wk.tap.r, tt = wk.tap.t, rc = wk.rc;
+          c0 = lb0 + ts * ls[0] + tr * lr[0] + tt * lt[0] + rc * lc[0];
+          c1 = lb1 + ts * ls[1] + tr * lr[1] + tt * lt[1] + rc * lc[1];
+          c2 = lb2 + ts * ls[2] + tr * lr[2] + tt * lt[2] + rc * lc[2];
+          c3 = lb3 + ts * ls[3] + tr * lr[3] + tt * lt[3] + rc * lc[3];
+          c4 = lb4 + ts * ls[4] + tr * lr[4] + tt * lt[4] + rc * lc[4];
+        } else if (act && p.debug_noload != 2) {
+          coords(wk, c0, c1, c2, c3, c4);
+        }
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER, p.wait_limit_ns);
         // (pairs: the operands of both CTAs are counted on the first CTA's barrier)
         if (p.debug_noload) {
