@@ -1,6 +1,9 @@
 """Small stand-alone workloads for profiling single kernels (ncu) or timing single calls.
 
-    python -m nervanagpu_b200.profile_cases <case> [--reps R] [--warm W]
+    python benchmarks/profile_cases.py <case> [--reps R] [--warm W]
+
+A case is a name from the tables below plus, for convolutions, the pass ("vgg4_fprop"), or a
+convolution spelled out: "conv:N,C,K,D,H,W,T,R,S,pad_d,pad_h,pad_w,str_d,str_h,str_w:fprop".
 
 Each case allocates its operands once (tensors larger than the 126 MB L2 in total, a few
 hundred MB at most), runs `warm` untimed calls, then `reps` calls timed with CUDA events, and
@@ -9,11 +12,13 @@ prints one JSON line with the time per call, the algorithmic work and the achiev
 import argparse
 import ctypes
 import json
+import os
 import sys
 
 import numpy as np
 
-from . import NervanaGPU, _lib
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+from nervanagpu_b200 import NervanaGPU, _lib   # noqa: E402
 
 CONV = {
     # name: (N, C, K, D, H, W, T, R, S, pad_d, pad_h, pad_w, str_d, str_h, str_w)
@@ -89,9 +94,14 @@ def _fill(ng, shape, dtype=np.float16, seed=0, lo=-1.0, hi=1.0):
 
 def run_case(name, warm=3, reps=10, sr=False):
     ng = NervanaGPU(stochastic_round=sr)
-    if "_" in name and name.rsplit("_", 1)[0] in CONV and name.rsplit("_", 1)[1] in ("fprop", "bprop", "update"):
-        layer_name, op = name.rsplit("_", 1)
-        cfg = CONV[layer_name]
+    if name.startswith("conv:") or ("_" in name and name.rsplit("_", 1)[0] in CONV and
+                                    name.rsplit("_", 1)[1] in ("fprop", "bprop", "update")):
+        if name.startswith("conv:"):
+            _, dims, op = name.split(":")
+            cfg = tuple(int(v) for v in dims.split(","))
+        else:
+            layer_name, op = name.rsplit("_", 1)
+            cfg = CONV[layer_name]
         layer = ng.conv_layer(np.float16, *cfg)
         I = _fill(ng, layer.dimI, seed=1, lo=0.0)
         F = _fill(ng, layer.dimF, seed=2, lo=-0.02, hi=0.02)

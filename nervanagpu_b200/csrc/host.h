@@ -44,7 +44,7 @@ struct DeviceCtx {
 // (or -1 for the on/off switches) when its variable is not set.
 struct Tuning {
   int tile_rows = 0, tile_cols = 0, kb_rows = 0, reduce_lanes = 0;
-  int update_groups = 0, update_stack = 0, update_min_stages = 0, max_ctas = 0, conv_splits = -1, max_stages = 0;
+  int update_groups = 0, update_stack = 0, update_min_stages = 0, max_ctas = 0, conv_splits = -1, max_stages = 0, feed_bytes_per_ns = 0;
   int merge_boxes = -1, split_tail = -1, lean_kernels = -1, update_swap = -1, pair_mma = -1;
 };
 const Tuning& tuning();

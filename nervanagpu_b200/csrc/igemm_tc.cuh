@@ -113,7 +113,6 @@ struct TcParams {
   // divisors of the tile / chunk / tap decodes, filled in by the launch code
   FastDiv fd_tiles_m, fd_tiles_n, fd_nz, fd_cpi, fd_q, fd_p, fd_RS, fd_S, fd_red, fd_crow;
   unsigned long long wait_limit_ns;   // bound of every wait inside the kernel
-  int debug_noload;                   // measurement aid: the producer signals full slots without loading anything
 };
 
 }  // namespace ngb

@@ -391,17 +391,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
           c2 = lb2 + ts * ls[2] + tr * lr[2] + tt * lt[2] + rc * lc[2];
           c3 = lb3 + ts * ls[3] + tr * lr[3] + tt * lt[3] + rc * lc[3];
           c4 = lb4 + ts * ls[4] + tr * lr[4] + tt * lt[4] + rc * lc[4];
-        } else if (act && p.debug_noload != 2) {
+        } else if (act) {
           coords(wk, c0, c1, c2, c3, c4);
         }
         const int got = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, p.status, NG_DEV_TIMEOUT_PRODUCER, p.wait_limit_ns);
         // (pairs: the operands of both CTAs are counted on the first CTA's barrier)
-        if (p.debug_noload) {
-          if (lane == 0 && got && rank == 0) mbar_arrive(full_bar(stage));
-          if (p.debug_noload != 2) advance(wk);
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
-          continue;
-        }
         if (lane == 0 && got && rank == 0) mbar_expect_tx(full_bar(stage), kPair ? 2u * tx_item : tx_item);
         if (!__all_sync(0xffffffffu, got)) {
           ok = false;
@@ -601,7 +595,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       if (!mbar_wait(accf_bar(acc), acc_phase, abort_flag, p.status, NG_DEV_TIMEOUT_EPILOGUE, p.wait_limit_ns)) break;
       tc_fence_after();
       const int n0 = it.tile_n * p.block_n;
-      for (int h = 0; h < (p.debug_noload >= 4 ? 0 : n_acc); ++h) {
+      for (int h = 0; h < n_acc; ++h) {
         // accumulator h holds rows of row-tile `rt` of output slice `zt`; with stacked taps
         // (weight update, few rows per tap) every `pack_rows` lanes belong to the next slice
         const int rt = it.m0 / kTileM + (wide ? h : 0);

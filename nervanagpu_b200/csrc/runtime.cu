@@ -56,6 +56,7 @@ const Tuning& tuning() {
     t.max_ctas = num("NG_MAX_CTAS", 0);
     t.conv_splits = num("NG_CONV_SPLITS", -1);
     t.max_stages = num("NG_MAX_STAGES", 0);
+    t.feed_bytes_per_ns = num("NG_FEED_BYTES_PER_NS", 0);
   });
   return t;
 }
@@ -368,7 +369,7 @@ int ng_tune(const char* name, int value) {
       {"tile_rows", &t.tile_rows}, {"tile_cols", &t.tile_cols}, {"kb_rows", &t.kb_rows},
       {"reduce_lanes", &t.reduce_lanes}, {"update_groups", &t.update_groups}, {"update_stack", &t.update_stack},
       {"update_min_stages", &t.update_min_stages}, {"max_ctas", &t.max_ctas}, {"conv_splits", &t.conv_splits},
-      {"max_stages", &t.max_stages}, {"merge_boxes", &t.merge_boxes}, {"split_tail", &t.split_tail},
+      {"max_stages", &t.max_stages}, {"feed_bytes_per_ns", &t.feed_bytes_per_ns}, {"merge_boxes", &t.merge_boxes}, {"split_tail", &t.split_tail},
       {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}};
   for (const Field& f : fields)
     if (strcmp(f.name, name) == 0) {

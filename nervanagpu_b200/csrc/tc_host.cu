@@ -194,6 +194,8 @@ void tc_pick_tile_rows(const DeviceCtx* c, TcParams& p, long long col_tiles, int
 // of its operand feed (copy engine: ~68 bytes/ns per SM) and its MMAs (~(rows + columns)/2 cycles
 // per K=16 step); a 256-row tile pays for its epilogue (not overlapped), a 128-row tile does not.
 // 85 tiles of 256 columns on 148 SMs (the 13x13 AlexNet layers) lose to 113 tiles of 192.
+static double tuning_or(int value, double fallback) { return value > 0 ? static_cast<double>(value) : fallback; }
+
 void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, int kb_rows) {
   const int force_rows = tuning().tile_rows, force_cols = tuning().tile_cols;
   double best = -1.0;
@@ -206,15 +208,17 @@ void tc_pick_tile(const DeviceCtx* c, TcParams& p, long long cols, int num_kb, i
       const long long tm = (p.M + kTileM * h - 1) / (kTileM * h);
       const long long tn = (cols + bn - 1) / bn;
       const long long tiles = tm * tn;
-      const double feed_ns = (kTileM * h + bn) * kb_rows * 2.0 / 68.0;
-      const double mma_ns = h * (kb_rows / 16) * (kTileM + bn) * 0.5 / 1.9;
+      // (an MMA takes the tensor pipe ~128 cycles whatever its width up to 256 columns, so narrower
+      // tiles only pay when they fill the last wave better; operands arrive at ~100 bytes/ns per SM)
+      const double feed_ns = (kTileM * h + bn) * kb_rows * 2.0 / tuning_or(tuning().feed_bytes_per_ns, 100);
+      const double mma_ns = h * (kb_rows / 16) * 66.0 + 30.0;
       const double epi_ns = h == 2 ? 5500.0 * bn / 256.0 : 600.0;
       const double tile_ns = num_kb * std::max(feed_ns, mma_ns) + epi_ns;
       double t = static_cast<double>((tiles + c->sm_count - 1) / c->sm_count) * tile_ns;
       const long long rem = tiles % c->sm_count;
       if (h == 2 && rem > 0 && 2 * rem <= c->sm_count) {
         // the last wave runs as 128-row halves (see tc_launch)
-        const double half_feed = (kTileM + bn) * kb_rows * 2.0 / 68.0;
+        const double half_feed = (kTileM + bn) * kb_rows * 2.0 / tuning_or(tuning().feed_bytes_per_ns, 100);
         t += num_kb * std::max(half_feed, mma_ns * 0.5) + epi_ns * 0.5 - tile_ns;
       }
       if (best < 0.0 || t < best) {
@@ -339,7 +343,6 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
   if (p.c_row_chunks && !p.store_staged)
     return fail(NG_ERR_UNSUPPORTED, "internal: padded image rows need the staged output stage");
   if (!p.wait_limit_ns) p.wait_limit_ns = c->wait_limit_ns;
-  p.debug_noload = getenv("NG_DEBUG_NOLOAD") ? atoi(getenv("NG_DEBUG_NOLOAD")) : 0;
   const uint32_t smem = p.stages * p.stage_bytes + 1024u + kCtrlBytes + (p.store_staged ? kEpiStageBytes : 0u) +
                         a_overread(p);
   fill_fast_divs(p);
