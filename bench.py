@@ -48,6 +48,7 @@ METRICS = {
     "gemm": ("gemm_2048_tn_relu_tflops", "BASELINE config 1 (+ the shapes of config 2)"),
 }
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
+JSON_OUT = sys.stdout
 
 
 def parse_args():
@@ -524,7 +525,8 @@ def bench_gemm(args, ranks):
         c_tf, _ = cpu_gemm(5, 1)
         line["cpu_baseline"] = {"value": c_tf, "unit": UNIT, "cores": host_threads(), "kind": "port",
                                 "sample": "the whole 2048^3 product (numpy fp32 sgemm + ReLU), 5 repeats"}
-    print(json.dumps(line))
+    JSON_OUT.write(json.dumps(line) + "\n")
+    JSON_OUT.flush()
 
 
 def main():
@@ -533,8 +535,13 @@ def main():
         run_reference_arm(args, int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1")))
         return
 
-    # keep stdout to the one JSON line: NCCL's version banner goes to stderr
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+    # Keep stdout to the one JSON line: the line is written to a private copy of the original
+    # stdout, and file descriptor 1 is pointed at stderr for everything else (NCCL prints its
+    # version banner on stdout from C).
+    sys.stdout.flush()
+    global JSON_OUT
+    JSON_OUT = os.fdopen(os.dup(1), "w")
+    os.dup2(2, 1)
     ranks = Ranks()
     rank, world = ranks.rank, ranks.world
     if args.net == "gemm":
@@ -752,7 +759,8 @@ def main():
         tflops, cpu_ms = time_cpu(net, 1, 1)
         line["cpu_baseline"] = {"value": tflops, "unit": UNIT, "cores": host_threads(), "kind": "port",
                                 "sample": "one whole step of the same stack through the numpy oracle (%.0f ms)" % cpu_ms}
-    print(json.dumps(line))
+    JSON_OUT.write(json.dumps(line) + "\n")
+    JSON_OUT.flush()
     ranks.close()
 
 
