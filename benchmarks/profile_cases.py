@@ -3,7 +3,8 @@
     python benchmarks/profile_cases.py <case> [--reps R] [--warm W]
 
 A case is a name from the tables below plus, for convolutions, the pass ("vgg4_fprop"), or a
-convolution spelled out: "conv:N,C,K,D,H,W,T,R,S,pad_d,pad_h,pad_w,str_d,str_h,str_w:fprop".
+convolution spelled out: "conv:N,C,K,D,H,W,T,R,S,pad_d,pad_h,pad_w,str_d,str_h,str_w:fprop";
+"step:alexnet:128" (or vgg_a, any minibatch) runs whole steps of the benchmark stack.
 
 Each case allocates its operands once (tensors larger than the 126 MB L2 in total, a few
 hundred MB at most), runs `warm` untimed calls, then `reps` calls timed with CUDA events, and
@@ -142,6 +143,16 @@ def run_case(name, warm=3, reps=10, sr=False):
         fn = lambda: ng.dot(a, b, C, relu=True)
         work, unit = 2.0 * m * n * k, "TFLOP/s"
         algo_bytes = 2 * (m * k + k * n + m * n)
+    elif name.startswith("step:"):
+        # "step:alexnet:128": whole steps of the benchmark stack, every kernel launched live on one stream
+        from nervanagpu_b200.convnet import ConvStack, NETWORKS
+        _, net, n = name.split(":")
+        ng.stream = ng.new_stream()
+        stack = ConvStack(ng, NETWORKS[net], N=int(n), seed=1003)
+        stack.overlap_update = False
+        fn = stack.step
+        work, unit = stack.flops, "TFLOP/s"
+        algo_bytes = 0
     elif name.startswith("bn_"):
         rows = int(name.split("_")[1])
         A = _fill(ng, (rows, 128), seed=5, lo=0.0)
