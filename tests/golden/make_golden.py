@@ -11,7 +11,7 @@ two scripts unmodified except for:
     fp16 device kernels can consume exactly the same inputs.
 The arrays the scripts compute on the CPU (cpuO / cpuB / cpuU) are stored with their inputs.
 
-Usage: python tests/golden/make_golden.py [/root/reference]
+Usage: python tests/golden/make_golden.py <path of a checkout of the reference>
 """
 import builtins
 import functools
@@ -182,7 +182,9 @@ def make_pool(ref_root, name, cfg, seed):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) != 2:
+        sys.exit(__doc__)
+    ref_root = sys.argv[1]
     for i, (name, cfg) in enumerate(sorted(CONV_CASES.items())):
         make_conv(ref_root, name, cfg, 100 + i)
     for i, (name, cfg) in enumerate(sorted(POOL_CASES.items())):
