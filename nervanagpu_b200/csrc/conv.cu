@@ -84,7 +84,9 @@ long long pixel_columns(TcParams& p, long long rows, int xdim, int N, ChunkMode 
 }
 
 // tensor map over an activation tensor (chan, z, y, x, n) seen as (n | x*n, x | 1, y, z, chan)
-int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, ChunkMode mode, uint32_t box_chan) {
+// (`blocked`: the tensor is the (z, y, chan, x, n) copy made by chan_block, see there)
+int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, ChunkMode mode, uint32_t box_chan,
+            bool blocked = false) {
   uint64_t dims[5], str[4];
   const uint64_t xn = 1ull * X * N * 2;
   if (mode == CH_PIXEL) {
@@ -93,9 +95,79 @@ int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int
     dims[0] = 1ull * X * N; dims[1] = 1; str[0] = xn;
   }
   dims[2] = Y; dims[3] = Z; dims[4] = chan;
-  str[1] = xn; str[2] = xn * Y; str[3] = xn * Y * Z;
+  if (blocked) {
+    str[1] = xn * chan; str[2] = xn * chan * Y; str[3] = xn;
+  } else {
+    str[1] = xn; str[2] = xn * Y; str[3] = xn * Y * Z;
+  }
   const uint32_t box[5] = {kChunk, 1, 1, 1, box_chan};
   return make_tensor_map(m, base, dims, str, box);
+}
+
+// ---- channel planes further apart than a page -------------------------------------------------
+// A TMA box of an activation tensor is [channels][64 elements]: one 128-byte row per channel, the
+// rows one channel plane (z * y * x * n elements) apart. When a plane is larger than a 2 MB page
+// every row of every box lies in another page, and the loads run at less than half their rate:
+// with planes of 1.8 MB the 3-D layer 64 -> 64, 3x3x3, 56x56, N = 32 runs at 620 TFLOP/s, with
+// planes of 2.0 MB at 390, of 3.2 MB at 280, whatever the tensor's total size, and with 16
+// instead of 64 filters (a quarter of the output) in the same time. The remedy is one pass over
+// the tensor before the product: a copy in (z, y, chan, x, n) order, whose channel rows are one
+// image row (x * n elements) apart, so that a box spans a few hundred KB. The product reads the
+// copy through a tensor map with the same dimensions and other strides; nothing in the kernel
+// changes. The copy costs one read and one write of the tensor; every tap of the filter reads
+// it again, so it pays from a few taps on.
+constexpr long long kPlaneBytesBlocked = 1900000;   // between the last fast (1.81 MB) and first slow (2.01 MB) plane
+bool wants_chan_block(int Z, int Y, int X, int N, int taps) {
+  if (tuning().chan_block == 0) return false;
+  const long long row = 2ll * X * N;
+  if (row % 16 != 0) return false;
+  if (tuning().chan_block == 2) return true;   // (tests: every shape)
+  return taps >= 4 && row * Y * Z > kPlaneBytesBlocked;
+}
+size_t chan_block_bytes(int chan, int Z, int Y, int X, int N) {
+  return (static_cast<size_t>(2) * chan * Z * Y * X * N + 255) & ~size_t(255);
+}
+// dst[(zy * chan + c)][row] = src[(c * zy_count + zy)][row], rows of `rowv` 16-byte vectors; one warp per row
+__global__ void chan_block_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int chan, long long zy_count,
+                                  int rowv) {
+  const long long r = blockIdx.x * static_cast<long long>(blockDim.y) + threadIdx.y;
+  if (r >= zy_count * chan) return;
+  const long long zy = r / chan;
+  const int c = static_cast<int>(r - zy * chan);
+  const uint4* s = src + (c * zy_count + zy) * rowv;
+  uint4* d = dst + r * rowv;
+  int v = threadIdx.x;
+  for (; v + 96 < rowv; v += 128) {   // four loads in flight per lane
+    const uint4 a = s[v], b = s[v + 32], e = s[v + 64], f = s[v + 96];
+    d[v] = a; d[v + 32] = b; d[v + 64] = e; d[v + 96] = f;
+  }
+  for (; v < rowv; v += 32) d[v] = s[v];
+}
+int chan_block(DeviceCtx* c, cudaStream_t stream, const void* src, void* dst, int chan, int Z, int Y, int X, int N) {
+  const long long rows = 1ll * chan * Z * Y;
+  const long long blocks = (rows + 7) / 8;
+  if (blocks > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "tensor too large for the channel-blocked copy");
+  (void)c;
+  chan_block_kernel<<<static_cast<unsigned>(blocks), dim3(32, 8), 0, stream>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst), chan, 1ll * Z * Y, X * N / 8);
+  NG_CHECK_LAUNCH();
+  return NG_OK;
+}
+// Room for the copies behind the split-K partials of the product `p` (whose tiling and number of
+// partitions are final): `n` copies of the given sizes, returned as pointers into the workspace.
+int chan_block_room(DeviceCtx* c, cudaStream_t stream, const TcParams& p, const size_t* bytes, void** ptrs, int n) {
+  const int nz_out = p.nz_out < 1 ? p.nz : p.nz_out;
+  size_t off = p.splits > 1 ? static_cast<size_t>(p.splits) * nz_out * p.M * p.N * sizeof(float) : 0;
+  off = (off + 255) & ~size_t(255);
+  size_t total = off;
+  for (int i = 0; i < n; ++i) total += bytes[i];
+  const int rc = ensure_workspace(c, stream, total);
+  if (rc != NG_OK) return rc;
+  for (int i = 0; i < n; ++i) {
+    ptrs[i] = reinterpret_cast<uint8_t*>(c->ws) + off;
+    off += bytes[i];
+  }
+  return NG_OK;
 }
 
 // Tensor map over an activation tensor whose box is a whole column tile of `nb` 64-wide chunks
@@ -103,21 +175,23 @@ int act_map(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int
 // (N = 64), else (n_lo, chan, n_hi, x, y) for 2-D data. The box lands in shared memory chunk by
 // chunk, each [box_chan rows][64], as the per-chunk boxes of act_map would. Returns the value for
 // TcParams::b_merge, 0 when the shape has no such map.
-int act_map_merged(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, uint32_t box_chan, int nb) {
+int act_map_merged(CUtensorMap* m, const void* base, int chan, int Z, int Y, int X, int N, uint32_t box_chan, int nb,
+                   bool blocked = false) {
   if (tuning().merge_boxes == 0 || N % kChunk != 0 || nb < 2) return 0;
   const int cpi = N / kChunk;
   const uint64_t xn = 1ull * X * N * 2;
+  const uint64_t chan_str = blocked ? xn : xn * Y * Z, y_str = blocked ? xn * chan : xn;
   uint64_t dims[5], str[4];
   uint32_t box[5];
   if (cpi == 1) {
     dims[0] = N; dims[1] = chan; dims[2] = X; dims[3] = Y; dims[4] = Z;
-    str[0] = xn * Y * Z; str[1] = 1ull * N * 2; str[2] = xn; str[3] = xn * Y;
+    str[0] = chan_str; str[1] = 1ull * N * 2; str[2] = y_str; str[3] = y_str * Y;
     box[0] = kChunk; box[1] = box_chan; box[2] = nb; box[3] = 1; box[4] = 1;
     return make_tensor_map(m, base, dims, str, box) == NG_OK ? 1 : 0;
   }
   if (Z != 1 || (nb % cpi != 0 && cpi % nb != 0)) return 0;
   dims[0] = kChunk; dims[1] = chan; dims[2] = cpi; dims[3] = X; dims[4] = Y;
-  str[0] = xn * Y; str[1] = 128; str[2] = 1ull * N * 2; str[3] = xn;
+  str[0] = chan_str; str[1] = 128; str[2] = 1ull * N * 2; str[3] = y_str;
   box[0] = kChunk; box[1] = box_chan; box[2] = std::min(cpi, nb); box[3] = std::max(1, nb / cpi); box[4] = 1;
   return make_tensor_map(m, base, dims, str, box) == NG_OK ? 2 : 0;
 }
@@ -707,12 +781,21 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
     rc = filter_map(&mapA, F, g, lay.kb_rows);
     if (rc != NG_OK) return rc;
   }
-  rc = act_map(&mapB, I, g.C, g.D, g.H, g.W, g.N, mode, lay.kb_rows);
-  if (rc != NG_OK) return rc;
-  if (mode == CH_PIXEL && g.str_w == 1)
-    p.b_merge = act_map_merged(&mapBm, I, g.C, g.D, g.H, g.W, g.N, lay.kb_rows, p.block_n / kChunk);
   // few tiles (a small minibatch, e.g. the shard of one GPU): the reduction is split over the SMs too
   p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n, p.num_kb, 1ll * g.K * cols, true);
+  const bool blocked = wants_chan_block(g.D, g.H, g.W, g.N, RST);
+  if (blocked) {   // large channel planes: the product reads a copy in (z, y, chan, x, n) order
+    const size_t bytes = chan_block_bytes(g.C, g.D, g.H, g.W, g.N);
+    void* copy = nullptr;
+    rc = chan_block_room(c, stream, p, &bytes, &copy, 1);
+    if (rc == NG_OK) rc = chan_block(c, stream, I, copy, g.C, g.D, g.H, g.W, g.N);
+    if (rc != NG_OK) return rc;
+    I = copy;
+  }
+  rc = act_map(&mapB, I, g.C, g.D, g.H, g.W, g.N, mode, lay.kb_rows, blocked);
+  if (rc != NG_OK) return rc;
+  if (mode == CH_PIXEL && g.str_w == 1)
+    p.b_merge = act_map_merged(&mapBm, I, g.C, g.D, g.H, g.W, g.N, lay.kb_rows, p.block_n / kChunk, blocked);
   return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 
@@ -760,12 +843,21 @@ int ng_conv_bprop(const ng_conv_desc* d, const void* F, const void* E, void* gra
   CUtensorMap mapA, mapB, mapBm;
   rc = filter_map(&mapA, F, g, a_rows);
   if (rc != NG_OK) return rc;
-  rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk);
+  p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n, p.num_kb, 1ll * g.C * cols, true);
+  const bool blocked = wants_chan_block(g.M, g.P, g.Q, g.N, RST);
+  if (blocked) {   // large channel planes: the product reads a copy in (z, y, chan, x, n) order
+    const size_t bytes = chan_block_bytes(g.K, g.M, g.P, g.Q, g.N);
+    void* copy = nullptr;
+    rc = chan_block_room(c, stream, p, &bytes, &copy, 1);
+    if (rc == NG_OK) rc = chan_block(c, stream, E, copy, g.K, g.M, g.P, g.Q, g.N);
+    if (rc != NG_OK) return rc;
+    E = copy;
+  }
+  rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, kChunk, blocked);
   if (rc != NG_OK) return rc;
   // the error pixels of a column tile inside one image row as one box
   if (mode == CH_PIXEL && g.str_w == 1)
-    p.b_merge = act_map_merged(&mapBm, E, g.K, g.M, g.P, g.Q, g.N, kChunk, p.block_n / kChunk);
-  p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n, p.num_kb, 1ll * g.C * cols, true);
+    p.b_merge = act_map_merged(&mapBm, E, g.K, g.M, g.P, g.Q, g.N, kChunk, p.block_n / kChunk, blocked);
   return tc_launch(c, mapA, mapB, p, stream, p.b_merge ? &mapBm : nullptr);
 }
 
@@ -821,9 +913,23 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
     p.alpha = alpha; p.beta = 0.0f; p.relu = 0; p.sr_bits = 0; p.out_f32 = out_f32; p.vec_ok = 1;
     p.splits = choose_splits(c, 1ll * p.tiles_m * p.tiles_n * p.nz, p.num_kb, 1ll * g.C * g.K * RST);
     CUtensorMap mapA, mapB;
-    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, a_rows);
+    // large channel planes: the product reads copies in (z, y, chan, x, n) order
+    const bool blocked_i = wants_chan_block(g.D, g.H, g.W, g.N, RST);
+    const bool blocked_e = wants_chan_block(g.M, g.P, g.Q, g.N, RST);
+    if (blocked_i || blocked_e) {
+      const size_t bytes[2] = {blocked_i ? chan_block_bytes(g.C, g.D, g.H, g.W, g.N) : 0,
+                               blocked_e ? chan_block_bytes(g.K, g.M, g.P, g.Q, g.N) : 0};
+      void* copies[2] = {nullptr, nullptr};
+      rc = chan_block_room(c, stream, p, bytes, copies, 2);
+      if (rc == NG_OK && blocked_i) rc = chan_block(c, stream, I, copies[0], g.C, g.D, g.H, g.W, g.N);
+      if (rc == NG_OK && blocked_e) rc = chan_block(c, stream, E, copies[1], g.K, g.M, g.P, g.Q, g.N);
+      if (rc != NG_OK) return rc;
+      if (blocked_i) I = copies[0];
+      if (blocked_e) E = copies[1];
+    }
+    rc = act_map(&mapA, I, g.C, g.D, g.H, g.W, g.N, mode, a_rows, blocked_i);
     if (rc != NG_OK) return rc;
-    rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, p.block_n);
+    rc = act_map(&mapB, E, g.K, g.M, g.P, g.Q, g.N, mode, p.block_n, blocked_e);
     if (rc != NG_OK) return rc;
     return tc_launch(c, mapA, mapB, p, stream);
   }

@@ -131,6 +131,33 @@ def test_tensor_core_path_matches_oracle(ng, name):
     assert (got["O"] >= 0).all()
 
 
+BLOCKED = ["c64_3x3_n64", "c96_3x3_n32_flattened", "c64_3d_n32", "c130_k200_ragged_channels", "stride_h_only",
+           "c48_k384_stacked_taps", "c64_k192_5x5_n128", "c64_k256_w6_merged_boxes"]
+
+
+@pytest.mark.parametrize("name", BLOCKED)
+def test_channel_blocked_copies_change_nothing(ng, lib, name):
+    """Activation tensors whose channel planes are larger than a page are read through a copy in
+    (z, y, channel, x, n) order (the "chan_block" tuning field: 2 = every shape, 0 = never). The
+    product reads the same values in the same order either way: results are equal bit for bit,
+    for every kind of tensor map (per pixel, flattened rows, merged boxes, strided rows)."""
+    cfg = CASES[name]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 1005)
+    try:
+        assert lib.ng_tune(b"chan_block", 0) == 0
+        plain = _run_all(ng, _layer(ng, cfg, "tensor"), I, F, E, relu=True, alpha=0.5)
+        assert lib.ng_tune(b"chan_block", 2) == 0
+        blocked = _run_all(ng, _layer(ng, cfg, "tensor"), I, F, E, relu=True, alpha=0.5)
+    finally:
+        assert lib.ng_tune(b"chan_block", -1) == 0
+    for key in ("O", "gradI", "gradF"):
+        np.testing.assert_array_equal(blocked[key], plain[key], err_msg="%s %s" % (name, key))
+    ref = {"O": rm.conv_fprop_fast(cd, I, F, alpha=0.5, relu=True), "gradI": rm.conv_bprop_fast(cd, F, E, alpha=0.5),
+           "gradF": rm.conv_update_fast(cd, I, E, alpha=0.5)}
+    _check(cd, blocked, I, F, E, ref, name + " (blocked)")
+
+
 @pytest.mark.parametrize("name", sorted(SHARDED))
 def test_sharded_minibatch_shapes_run_on_the_tensor_core_path(ng, name):
     cfg = SHARDED[name]
