@@ -144,6 +144,14 @@ __device__ __forceinline__ void tma_load_5d_pair(uint32_t dst, const CUtensorMap
 // ----------------------------------------------------------------------------------------
 // thread-block clusters (CTA pairs)
 // ----------------------------------------------------------------------------------------
+// Programmatic dependent launch. A kernel launched with the programmatic-serialization attribute
+// may start while the kernel before it in the stream still runs; grid_dependency_wait() returns
+// once that kernel has finished and its writes are visible (at once when the launch carried no
+// such attribute). grid_launch_dependents() lets the kernel after this one start being scheduled
+// (it waits in turn, so nothing of it that matters runs early).
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t cluster_cta_rank() {
   uint32_t r;
   asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));

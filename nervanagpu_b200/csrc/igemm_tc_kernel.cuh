@@ -199,6 +199,11 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
   if (kPair) cluster_sync_all();   // the peer's barriers exist before anything arrives on them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Everything above (barriers, tensor memory, descriptor prefetch) may run while the kernel
+  // before this one in the stream drains; its results are needed from here on. (Letting the next
+  // kernel in as soon as this one has started, griddepcontrol.launch_dependents here, made whole
+  // training steps 4 % slower: its blocks wait on the SMs this kernel's tail still needs.)
+  grid_dependency_wait();
 
   if (warp == 0) {
     // =========================== TMA producer ===========================
@@ -844,6 +849,8 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
 __global__ void splitk_reduce_kernel(const float* __restrict__ ws, int splits, int lanes, int nz, int M, int N,
                                      void* C, const void* Cold, long long ldc, long long c_zstride, int out_f32,
                                      int vec_ok, EpiArgs ea, int c_row_chunks, int c_row_len) {
+  grid_dependency_wait();     // (launched while the product that writes the partials drains)
+  grid_launch_dependents();
   const int groups_per_row = (N + 7) / 8;
   const long long total = static_cast<long long>(nz) * M * groups_per_row;
   const long long slice = static_cast<long long>(nz) * M * N;

@@ -54,6 +54,7 @@ const Tuning& tuning() {
     t.update_swap = num("NG_UPDATE_SWAP", -1);
     t.pair_mma = num("NG_PAIR_MMA", -1);
     t.chan_block = num("NG_CHAN_BLOCK", -1);
+    t.dependent_launch = num("NG_DEPENDENT_LAUNCH", -1);
     t.max_ctas = num("NG_MAX_CTAS", 0);
     t.conv_splits = num("NG_CONV_SPLITS", -1);
     t.max_stages = num("NG_MAX_STAGES", 0);
@@ -371,7 +372,7 @@ int ng_tune(const char* name, int value) {
       {"reduce_lanes", &t.reduce_lanes}, {"update_groups", &t.update_groups}, {"update_stack", &t.update_stack},
       {"update_min_stages", &t.update_min_stages}, {"max_ctas", &t.max_ctas}, {"conv_splits", &t.conv_splits},
       {"max_stages", &t.max_stages}, {"feed_bytes_per_ns", &t.feed_bytes_per_ns}, {"merge_boxes", &t.merge_boxes}, {"split_tail", &t.split_tail},
-      {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}, {"chan_block", &t.chan_block}};
+      {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}, {"chan_block", &t.chan_block}, {"dependent_launch", &t.dependent_launch}};
   for (const Field& f : fields)
     if (strcmp(f.name, name) == 0) {
       *f.slot = value;

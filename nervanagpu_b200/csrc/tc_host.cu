@@ -382,9 +382,21 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     }
 #undef NG_TC_LAUNCH_PAIR
   } else
+  {
+  // (may be set up while the kernel before it in the stream drains: see grid_dependency_wait)
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid);
+  cfg.blockDim = dim3(kTcThreads);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = tuning().dependent_launch != 0 ? 1 : 0;
 #define NG_TC_LAUNCH(mode)                                                                                      \
-  if (lean) igemm_tc_kernel<mode, true><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch);   \
-  else igemm_tc_kernel<mode, false><<<grid, kTcThreads, smem, stream>>>(mapA, mapB, mapB2, launch)
+  if (lean) NG_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<mode, true, false>, mapA, mapB, mapB2, launch));  \
+  else NG_CUDA(cudaLaunchKernelEx(&cfg, igemm_tc_kernel<mode, false, false>, mapA, mapB, mapB2, launch))
   switch (launch.mode) {
     case TC_GEMM: NG_TC_LAUNCH(TC_GEMM); break;
     case TC_FPROP: NG_TC_LAUNCH(TC_FPROP); break;
@@ -393,6 +405,7 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     default: return fail(NG_ERR_INVALID_ARG, "internal: unknown tensor-core mode");
   }
 #undef NG_TC_LAUNCH
+  }
   NG_CHECK_LAUNCH();
   if (p.splits > 1) {
     EpiArgs ea;
@@ -402,9 +415,18 @@ int tc_launch(DeviceCtx* c, const CUtensorMap& mapA, const CUtensorMap& mapB, Tc
     const int lanes = splitk_reduce_lanes(groups, p.splits, c->sm_count);
     const long long blocks = (groups * lanes + 255) / 256;
     if (blocks > 0x7fffffffll) return fail(NG_ERR_TOO_LARGE, "output too large for the split-K reduction");
-    splitk_reduce_kernel<<<static_cast<int>(blocks), 256, 0, stream>>>(p.ws, p.splits, lanes, p.nz_out, p.M, p.N, p.C,
-                                                                        p.Cold, p.ldc, p.c_zstride, p.out_f32,
-                                                                        p.vec_ok, ea, p.c_row_chunks, p.c_row_len);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>(blocks));
+    cfg.blockDim = dim3(256);
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = tuning().dependent_launch != 0 ? 1 : 0;
+    NG_CUDA(cudaLaunchKernelEx(&cfg, splitk_reduce_kernel, static_cast<const float*>(p.ws), p.splits, lanes, p.nz_out,
+                               p.M, p.N, p.C, p.Cold, p.ldc, p.c_zstride, p.out_f32, p.vec_ok, ea, p.c_row_chunks,
+                               p.c_row_len));
     NG_CHECK_LAUNCH();
   }
   return NG_OK;
