@@ -89,6 +89,10 @@ __device__ __forceinline__ bool div_exact(int num, int den, int& out) {
   return out * den == num;
 }
 
+// Row coordinate of a box that must read zeros (a chunk past the end of the pixel space): this far
+// beyond the last row, so that the per-tap steps added to it cannot bring it back inside.
+constexpr int kFarRows = 1 << 16;
+
 struct WorkItem {
   int tile_m, tile_n, z, split, kb0, kb1;
   int m0;     // first output row of the item
@@ -217,6 +221,10 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    // steps of the box coordinates per tap (s, r, t) and per reduction chunk, see below
+    const bool linear = (kMode == TC_FPROP || (kMode == TC_BPROP && p.str_w == 1 && p.str_h == 1 && p.str_d == 1));
+    int ls[5] = {0, 0, 0, 0, 0}, lr[5] = {0, 0, 0, 0, 0}, lt[5] = {0, 0, 0, 0, 0}, lc[5] = {0, 0, 0, 0, 0};
+    int steps_for = -1;   // form of the B box (0 per chunk, 1 merged) the steps were taken for; -1 = not yet
     for (int w = w_first; w < total_work && ok; w += w_step) {
       const WorkItem it = decode_work(p, w);
       if (it.live == 0) continue;
@@ -289,7 +297,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
             } else {     // input pixels of this chunk shifted by the tap
               c0 = cp.inner0 + (tap.s - p.pad_w) * p.inner_tap;
               c1 = (cp.q * p.str_w - p.pad_w + tap.s * p.tap_w) * p.x_tap;
-              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tap.r * p.tap_h : p.oob_y;
+              c2 = cp.valid ? cp.p * p.str_h - p.pad_h + tap.r * p.tap_h : p.oob_y + kFarRows;
               c3 = cp.m * p.str_d - p.pad_d + tap.t;
               c4 = rc * p.kb_rows;
             }
@@ -307,7 +315,7 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
               }
               v &= div_exact(cp.p + p.pad_h - tap.r, p.str_h, pp);
               v &= div_exact(cp.m + p.pad_d - tap.t, p.str_d, mm);
-              c1 = q; c2 = v ? pp : p.oob_y; c3 = mm; c4 = rc * kChunk;
+              c1 = q; c2 = v ? pp : p.oob_y + kFarRows; c3 = mm; c4 = rc * kChunk;
             }
           } else {  // TC_UPDATE: k-block = one 64-element chunk of the (m,p,q,n) space
             if (is_a != (p.swap_ab != 0)) {  // input pixels under tap z, 128 channels c
@@ -363,27 +371,35 @@ igemm_tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant_
       // costs this warp five multiply-adds per coordinate instead of a walk through that formula
       // (which the A and the B lanes take one after the other): with it the producer took about
       // as long per k-block as the MMAs themselves and, being one serial warp, set the pace.
-      const bool linear = (kMode == TC_FPROP || (kMode == TC_BPROP && p.str_w == 1 && p.str_h == 1 && p.str_d == 1));
+      // The steps depend on the tile only through the form of its B box (one merged box or one
+      // per chunk), so they are kept from tile to tile; a tile costs one walk through the formula
+      // for its offsets. (Tiles of a few k-blocks, e.g. a 3-channel first layer with one k-block
+      // per tile, spent most of their time in this set-up when it took five walks.)
       int lb0 = 0, lb1 = 0, lb2 = 0, lb3 = 0, lb4 = 0;          // coordinates at tap (0, 0, 0), chunk 0
-      int ls[5] = {0, 0, 0, 0, 0}, lr[5] = {0, 0, 0, 0, 0}, lt[5] = {0, 0, 0, 0, 0}, lc[5] = {0, 0, 0, 0, 0};
       if (linear && act) {
         Walk o = wk;
         o.tap = {0, 0, 0}; o.trs = 0; o.rc = 0;
         coords(o, lb0, lb1, lb2, lb3, lb4);
-        int d0, d1, d2, d3, d4;
-        Walk q = o;
-        q.tap.s = 1; q.trs = 1;
-        coords(q, d0, d1, d2, d3, d4);
-        ls[0] = d0 - lb0; ls[1] = d1 - lb1; ls[2] = d2 - lb2; ls[3] = d3 - lb3; ls[4] = d4 - lb4;
-        q = o; q.tap.r = 1; q.trs = p.S;
-        coords(q, d0, d1, d2, d3, d4);
-        lr[0] = d0 - lb0; lr[1] = d1 - lb1; lr[2] = d2 - lb2; lr[3] = d3 - lb3; lr[4] = d4 - lb4;
-        q = o; q.tap.t = 1; q.trs = p.RS;
-        coords(q, d0, d1, d2, d3, d4);
-        lt[0] = d0 - lb0; lt[1] = d1 - lb1; lt[2] = d2 - lb2; lt[3] = d3 - lb3; lt[4] = d4 - lb4;
-        q = o; q.rc = 1;
-        coords(q, d0, d1, d2, d3, d4);
-        lc[0] = d0 - lb0; lc[1] = d1 - lb1; lc[2] = d2 - lb2; lc[3] = d3 - lb3; lc[4] = d4 - lb4;
+        if (steps_for != static_cast<int>(merged)) {
+          steps_for = static_cast<int>(merged);
+          // (taken on a chunk that exists: a chunk past the end has a constant, far row coordinate)
+          o.cp.valid = true;
+          int b0, b1, b2, b3, b4, d0, d1, d2, d3, d4;
+          coords(o, b0, b1, b2, b3, b4);
+          Walk q = o;
+          q.tap.s = 1; q.trs = 1;
+          coords(q, d0, d1, d2, d3, d4);
+          ls[0] = d0 - b0; ls[1] = d1 - b1; ls[2] = d2 - b2; ls[3] = d3 - b3; ls[4] = d4 - b4;
+          q = o; q.tap.r = 1; q.trs = p.S;
+          coords(q, d0, d1, d2, d3, d4);
+          lr[0] = d0 - b0; lr[1] = d1 - b1; lr[2] = d2 - b2; lr[3] = d3 - b3; lr[4] = d4 - b4;
+          q = o; q.tap.t = 1; q.trs = p.RS;
+          coords(q, d0, d1, d2, d3, d4);
+          lt[0] = d0 - b0; lt[1] = d1 - b1; lt[2] = d2 - b2; lt[3] = d3 - b3; lt[4] = d4 - b4;
+          q = o; q.rc = 1;
+          coords(q, d0, d1, d2, d3, d4);
+          lc[0] = d0 - b0; lc[1] = d1 - b1; lc[2] = d2 - b2; lc[3] = d3 - b3; lc[4] = d4 - b4;
+        }
       }
       for (int kb = it.kb0; kb < it.kb1; ++kb) {
         // The coordinates are ready before the slot is, so the copy leaves as soon as it frees.
