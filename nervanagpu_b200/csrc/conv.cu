@@ -691,6 +691,95 @@ int update_tapblock(DeviceCtx* c, const Geo& g, const TapBlock& tb, const void* 
 
 using namespace ngb;
 
+// ------------------------------------------------------------------------------------------
+// Strided first layers of a small minibatch: space to depth.
+// With fewer than 64 images a chunk holds several pixels, which a strided layer does not read
+// from consecutive addresses, and with 3 channels a tap is no k-block. Such a layer (AlexNet
+// conv1 on the shard of one of 4 or 8 GPUs) is rewritten as a unit-stride layer over
+//   I2[(c, dy, dx)][Y][X][n] = I[c][st * Y + dy - pad_h][st * X + dx - pad_w][n]   (zero outside),
+//   F2[(c, dy, dx)][r2][s2][k] = F[c][st * r2 + dy][st * s2 + dx][k]               (zero outside),
+// O[k][p][q][n] = sum F2 * I2[..][p + r2][q + s2][n]: C * st * st channels (48 for 3 channels and
+// stride 4), ceil(R / st) x ceil(S / st) taps, no padding, which is a shape the flattened-row
+// tensor-core path handles at any minibatch. The copies cost a pass over the (small) input; the
+// im2col matrix this replaces was R * S / st^2 times larger.
+struct SpaceToDepth {
+  bool ok = false;
+  int st = 1, C2 = 0, H2 = 0, W2 = 0, R2 = 0, S2 = 0;
+};
+SpaceToDepth pick_space_to_depth(const Geo& g) {
+  SpaceToDepth z;
+  if (tuning().space_to_depth == 0) return z;
+  if (g.D != 1 || g.T != 1 || g.pad_d != 0 || g.str_d != 1 || g.str_h != g.str_w || g.str_w < 2) return z;
+  z.st = g.str_w;
+  z.C2 = g.C * z.st * z.st;
+  z.R2 = (g.R + z.st - 1) / z.st;
+  z.S2 = (g.S + z.st - 1) / z.st;
+  z.H2 = g.P + z.R2 - 1;
+  z.W2 = g.Q + z.S2 - 1;
+  z.ok = z.C2 >= 16 && z.C2 <= 4096;
+  return z;
+}
+ng_conv_desc space_to_depth_desc(const Geo& g, const SpaceToDepth& z) {
+  ng_conv_desc d = {};
+  d.N = g.N; d.C = z.C2; d.K = g.K;
+  d.D = 1; d.H = z.H2; d.W = z.W2;
+  d.T = 1; d.R = z.R2; d.S = z.S2;
+  d.pad_d = d.pad_h = d.pad_w = 0;
+  d.str_d = d.str_h = d.str_w = 1;
+  return d;
+}
+// one block row per (channel of I2, Y): the threads walk its X * N / 8 16-byte vectors
+__global__ void s2d_input_kernel(Geo g, SpaceToDepth z, const uint4* __restrict__ I, uint4* __restrict__ I2) {
+  const int nvec = g.N >> 3;
+  const int row = blockIdx.x;                 // c2 * H2 + Y
+  const int c2 = row / z.H2, Y = row - c2 * z.H2;
+  const int dx = c2 % z.st, dy = (c2 / z.st) % z.st, c = c2 / (z.st * z.st);
+  const int y = z.st * Y + dy - g.pad_h;
+  const bool row_in = y >= 0 && y < g.H;
+  const uint4* src = I + (1ll * c * g.H + (row_in ? y : 0)) * g.W * nvec;
+  uint4* dst = I2 + 1ll * row * z.W2 * nvec;
+  for (int i = threadIdx.x; i < z.W2 * nvec; i += blockDim.x) {
+    const int X = i / nvec, v = i - X * nvec;
+    const int x = z.st * X + dx - g.pad_w;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (row_in && x >= 0 && x < g.W) val = __ldg(src + x * nvec + v);
+    dst[i] = val;
+  }
+}
+// one 16-byte vector (8 filters) of F2 per thread
+__global__ void s2d_filter_kernel(Geo g, SpaceToDepth z, const uint4* __restrict__ F, uint4* __restrict__ F2) {
+  const int kvec = g.K >> 3;
+  const long long total = 1ll * z.C2 * z.R2 * z.S2 * kvec;
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int v = static_cast<int>(r % kvec); r /= kvec;
+    const int s2 = static_cast<int>(r % z.S2); r /= z.S2;
+    const int r2 = static_cast<int>(r % z.R2);
+    const int c2 = static_cast<int>(r / z.R2);
+    const int dx = c2 % z.st, dy = (c2 / z.st) % z.st, c = c2 / (z.st * z.st);
+    const int rr = z.st * r2 + dy, ss = z.st * s2 + dx;
+    uint4 val = make_uint4(0, 0, 0, 0);
+    if (rr < g.R && ss < g.S) val = __ldg(F + ((1ll * c * g.R + rr) * g.S + ss) * kvec + v);
+    F2[i] = val;
+  }
+}
+// gradF[c][r][s][k] = G2[(c, r % st, s % st)][r / st][s / st][k]
+__global__ void s2d_filter_grad_kernel(Geo g, SpaceToDepth z, const float* __restrict__ G2, void* gradF, int out_f32) {
+  const long long total = g.sizeF();
+  for (long long i = blockIdx.x * 1ll * blockDim.x + threadIdx.x; i < total; i += 1ll * gridDim.x * blockDim.x) {
+    long long r = i;
+    const int k = static_cast<int>(r % g.K); r /= g.K;
+    const int ss = static_cast<int>(r % g.S); r /= g.S;
+    const int rr = static_cast<int>(r % g.R);
+    const int c = static_cast<int>(r / g.R);
+    const int c2 = (c * z.st + rr % z.st) * z.st + ss % z.st;
+    const float v = G2[((1ll * c2 * z.R2 + rr / z.st) * z.S2 + ss / z.st) * g.K + k];
+    if (out_f32) static_cast<float*>(gradF)[i] = v;
+    else static_cast<__half*>(gradF)[i] = __float2half_rn(v);
+  }
+}
+size_t round256(size_t b) { return (b + 255) & ~size_t(255); }
+
 extern "C" {
 
 int ng_conv_output_dims(const ng_conv_desc* d, int* M, int* P, int* Q) {
@@ -719,6 +808,24 @@ int ng_conv_fprop(const ng_conv_desc* d, const void* I, const void* F, void* O, 
   if ((path == NG_PATH_AUTO || path == NG_PATH_TENSOR) && g.C < 16 && g.N % kChunk == 0 && al) {
     const TapBlock tb = pick_tap_block(g);
     if (tb.ok) return fprop_tapblock(c, g, tb, I, F, O, alpha, relu, stream);
+  }
+  if (path == NG_PATH_AUTO && g.C < 16 && g.N % kChunk != 0 && al) {
+    const SpaceToDepth z = pick_space_to_depth(g);
+    if (z.ok) {
+      const size_t i2_bytes = round256(2ull * z.C2 * z.H2 * z.W2 * g.N), f2_bytes = round256(2ull * z.C2 * z.R2 * z.S2 * g.K);
+      void* aux = nullptr;
+      rc = ensure_aux(c, stream, i2_bytes + f2_bytes, &aux);
+      if (rc != NG_OK) return rc;
+      uint4* I2 = static_cast<uint4*>(aux);
+      uint4* F2 = reinterpret_cast<uint4*>(static_cast<uint8_t*>(aux) + i2_bytes);
+      s2d_input_kernel<<<z.C2 * z.H2, 256, 0, stream>>>(g, z, static_cast<const uint4*>(I), I2);
+      NG_CHECK_LAUNCH();
+      s2d_filter_kernel<<<launch_1d(1ll * z.C2 * z.R2 * z.S2 * (g.K / 8), 256, c), 256, 0, stream>>>(
+          g, z, static_cast<const uint4*>(F), F2);
+      NG_CHECK_LAUNCH();
+      const ng_conv_desc d2 = space_to_depth_desc(g, z);
+      return ng_conv_fprop(&d2, I2, F2, O, alpha, relu, NG_PATH_AUTO, stream_);
+    }
   }
   {
     // Few input channels where tap blocks do not apply: one tap per k-block would feed the tensor
@@ -883,6 +990,25 @@ int ng_conv_update(const ng_conv_desc* d, const void* I, const void* E, void* gr
   if ((path == NG_PATH_AUTO || path == NG_PATH_TENSOR) && g.C < 16 && g.N % kChunk == 0 && al) {
     const TapBlock tb = pick_tap_block(g);
     if (tb.ok) return update_tapblock(c, g, tb, I, E, gradF, out_f32, alpha, stream);
+  }
+  if (path == NG_PATH_AUTO && g.C < 16 && g.N % kChunk != 0 && al) {
+    const SpaceToDepth z = pick_space_to_depth(g);   // see there
+    if (z.ok) {
+      const size_t i2_bytes = round256(2ull * z.C2 * z.H2 * z.W2 * g.N), g2_bytes = round256(4ull * z.C2 * z.R2 * z.S2 * g.K);
+      void* aux = nullptr;
+      rc = ensure_aux(c, stream, i2_bytes + g2_bytes, &aux);
+      if (rc != NG_OK) return rc;
+      uint4* I2 = static_cast<uint4*>(aux);
+      float* G2 = reinterpret_cast<float*>(static_cast<uint8_t*>(aux) + i2_bytes);
+      s2d_input_kernel<<<z.C2 * z.H2, 256, 0, stream>>>(g, z, static_cast<const uint4*>(I), I2);
+      NG_CHECK_LAUNCH();
+      const ng_conv_desc d2 = space_to_depth_desc(g, z);
+      rc = ng_conv_update(&d2, I2, E, G2, 1, alpha, NG_PATH_AUTO, stream_);
+      if (rc != NG_OK) return rc;
+      s2d_filter_grad_kernel<<<launch_1d(g.sizeF(), 256, c), 256, 0, stream>>>(g, z, G2, gradF, out_f32);
+      NG_CHECK_LAUNCH();
+      return NG_OK;
+    }
   }
   if (direct) {
     TcParams p = {};

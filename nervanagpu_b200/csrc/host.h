@@ -24,6 +24,9 @@ struct DeviceCtx {
     size_t bytes = 0;
   };
   std::map<cudaStream_t, Scratch> scratch;
+  // second buffer per stream, for operands that a call re-lays-out before it hands them to another
+  // entry point of the library (which uses the first buffer as it likes)
+  std::map<cudaStream_t, Scratch> aux;
   float* ws = nullptr;
   size_t ws_bytes = 0;
   // Recorded sequences (CUDA graphs) keep the scratch pointers of the calls they recorded: while
@@ -39,13 +42,13 @@ struct DeviceCtx {
 // Tuning aids, read from the environment once per process (none is needed in normal use):
 // NG_TILE_ROWS=128|256, NG_TILE_COLS=128|192|256, NG_KB_ROWS=16|32|48|64, NG_MERGE_BOXES=0,
 // NG_SPLIT_TAIL=0, NG_LEAN_KERNELS=0, NG_REDUCE_LANES=<power of two>, NG_UPDATE_GROUPS=<n>,
-// NG_UPDATE_STACK=<n>, NG_UPDATE_MIN_STAGES=<n>, NG_UPDATE_SWAP=0, NG_PAIR_MMA=0|1, NG_CHAN_BLOCK=0|2 (never / always copy activations channel-blocked), NG_DEPENDENT_LAUNCH=0, NG_MAX_CTAS=<n>,
+// NG_UPDATE_STACK=<n>, NG_UPDATE_MIN_STAGES=<n>, NG_UPDATE_SWAP=0, NG_PAIR_MMA=0|1, NG_CHAN_BLOCK=0|2 (never / always copy activations channel-blocked), NG_DEPENDENT_LAUNCH=0, NG_SPACE_TO_DEPTH=0, NG_MAX_CTAS=<n>,
 // NG_CONV_SPLITS=<n> (partitions of the forward / backward reduction; 1 = never split). A field is 0
 // (or -1 for the on/off switches) when its variable is not set.
 struct Tuning {
   int tile_rows = 0, tile_cols = 0, kb_rows = 0, reduce_lanes = 0;
   int update_groups = 0, update_stack = 0, update_min_stages = 0, max_ctas = 0, conv_splits = -1, max_stages = 0, feed_bytes_per_ns = 0;
-  int merge_boxes = -1, split_tail = -1, lean_kernels = -1, update_swap = -1, pair_mma = -1, chan_block = -1, dependent_launch = -1;
+  int merge_boxes = -1, split_tail = -1, lean_kernels = -1, update_swap = -1, pair_mma = -1, chan_block = -1, dependent_launch = -1, space_to_depth = -1;
 };
 const Tuning& tuning();
 Tuning& tuning_mutable();   // ng_tune
@@ -79,6 +82,7 @@ DeviceCtx* current_ctx();
 // Ensure the workspace of `stream` holds at least `bytes` and make c->ws point at it; may
 // synchronise the device when it has to grow.
 int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes);
+int ensure_aux(DeviceCtx* c, cudaStream_t stream, size_t bytes, void** ptr);
 
 // Rank-5 tiled tensor map over fp16 (elem_bytes 2) data. dims[0] is the contiguous dimension;
 // strides_bytes[i] is the byte stride of dims[i+1]. Swizzle is chosen from the inner box width.

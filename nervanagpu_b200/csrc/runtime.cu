@@ -54,6 +54,7 @@ const Tuning& tuning() {
     t.update_swap = num("NG_UPDATE_SWAP", -1);
     t.pair_mma = num("NG_PAIR_MMA", -1);
     t.chan_block = num("NG_CHAN_BLOCK", -1);
+    t.space_to_depth = num("NG_SPACE_TO_DEPTH", -1);
     t.dependent_launch = num("NG_DEPENDENT_LAUNCH", -1);
     t.max_ctas = num("NG_MAX_CTAS", 0);
     t.conv_splits = num("NG_CONV_SPLITS", -1);
@@ -107,9 +108,8 @@ DeviceCtx* current_ctx() {
   return c;
 }
 
-int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes) {
-  // one scratch buffer per stream: calls queued on different streams may run at the same time
-  DeviceCtx::Scratch& s = c->scratch[stream];
+// grows one scratch buffer to at least `bytes`
+static int grow_scratch(DeviceCtx* c, DeviceCtx::Scratch& s, size_t bytes) {
   if (bytes > s.bytes) {
     if (c->capturing) {
       return fail(NG_ERR_UNSUPPORTED,
@@ -129,8 +129,24 @@ int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes) {
     NG_CUDA(cudaMalloc(&s.ptr, want));
     s.bytes = want;
   }
+  return NG_OK;
+}
+
+int ensure_workspace(DeviceCtx* c, cudaStream_t stream, size_t bytes) {
+  // one scratch buffer per stream: calls queued on different streams may run at the same time
+  DeviceCtx::Scratch& s = c->scratch[stream];
+  const int rc = grow_scratch(c, s, bytes);
+  if (rc != NG_OK) return rc;
   c->ws = s.ptr;
   c->ws_bytes = s.bytes;
+  return NG_OK;
+}
+
+int ensure_aux(DeviceCtx* c, cudaStream_t stream, size_t bytes, void** ptr) {
+  DeviceCtx::Scratch& s = c->aux[stream];
+  const int rc = grow_scratch(c, s, bytes);
+  if (rc != NG_OK) return rc;
+  *ptr = s.ptr;
   return NG_OK;
 }
 
@@ -372,7 +388,7 @@ int ng_tune(const char* name, int value) {
       {"reduce_lanes", &t.reduce_lanes}, {"update_groups", &t.update_groups}, {"update_stack", &t.update_stack},
       {"update_min_stages", &t.update_min_stages}, {"max_ctas", &t.max_ctas}, {"conv_splits", &t.conv_splits},
       {"max_stages", &t.max_stages}, {"feed_bytes_per_ns", &t.feed_bytes_per_ns}, {"merge_boxes", &t.merge_boxes}, {"split_tail", &t.split_tail},
-      {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}, {"chan_block", &t.chan_block}, {"dependent_launch", &t.dependent_launch}};
+      {"lean_kernels", &t.lean_kernels}, {"update_swap", &t.update_swap}, {"pair_mma", &t.pair_mma}, {"chan_block", &t.chan_block}, {"space_to_depth", &t.space_to_depth}, {"dependent_launch", &t.dependent_launch}};
   for (const Field& f : fields)
     if (strcmp(f.name, name) == 0) {
       *f.slot = value;

@@ -158,6 +158,51 @@ def test_channel_blocked_copies_change_nothing(ng, lib, name):
     _check(cd, blocked, I, F, E, ref, name + " (blocked)")
 
 
+STRIDED_FIRST_LAYERS = {
+    # AlexNet conv1 on the shard of one of 4 / 8 / 16 GPUs (smaller image, same filter geometry)
+    "alexnet_conv1_n32": (32, 3, 64, 1, 35, 35, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    "alexnet_conv1_n16": (16, 3, 64, 1, 39, 37, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    "alexnet_conv1_n8": (8, 3, 64, 1, 35, 35, 1, 11, 11, 0, 2, 2, 1, 4, 4),
+    # stride 2, 7x7 (a filter that is not a multiple of the stride), odd padding, 4 channels
+    "c4_7x7_stride2_n24": (24, 4, 96, 1, 21, 23, 1, 7, 7, 0, 3, 3, 1, 2, 2),
+    # stride 3 with a 5x5 filter and no padding: the last window ends before the image does
+    "c3_5x5_stride3_n40": (40, 3, 32, 1, 20, 20, 1, 5, 5, 0, 0, 0, 1, 3, 3),
+}
+
+
+@pytest.mark.parametrize("name", sorted(STRIDED_FIRST_LAYERS))
+def test_strided_first_layers_of_small_minibatches_run_as_space_to_depth(ng, lib, name):
+    """Fewer than 64 images, fewer than 16 channels, stride > 1: the layer is rewritten as a
+    unit-stride layer over st*st times the channels (copies of the input and the filters) and runs
+    on the tensor-core path; the weight gradient is gathered back into the filter's own shape."""
+    import ctypes
+    cfg = STRIDED_FIRST_LAYERS[name]
+    cd = rm.ConvDims(*cfg)
+    I, F, E = _inputs(cd, 1006)
+    ref = {"O": rm.conv_fprop_fast(cd, I, F, alpha=0.5, relu=True), "gradF": rm.conv_update_fast(cd, I, E, alpha=0.5)}
+    before = ctypes.c_ulonglong(0)
+    after = ctypes.c_ulonglong(0)
+    assert lib.ng_fallback_launch_count(ctypes.byref(before)) == 0
+    got = _run_all(ng, _layer(ng, cfg, "auto"), I, F, E, relu=True, alpha=0.5, ops="fu")
+    assert lib.ng_fallback_launch_count(ctypes.byref(after)) == 0
+    assert after.value == before.value, "left the tensor-core path"
+    _check(cd, got, I, F, E, ref, name)
+    # the same through the im2col form it replaces (switch off): same sums, other order
+    try:
+        assert lib.ng_tune(b"space_to_depth", 0) == 0
+        old = _run_all(ng, _layer(ng, cfg, "auto"), I, F, E, relu=True, alpha=0.5, ops="fu")
+    finally:
+        assert lib.ng_tune(b"space_to_depth", -1) == 0
+    _check(cd, old, I, F, E, ref, name + " (im2col)")
+    # fp16 weight gradient
+    layer = _layer(ng, cfg, "auto")
+    dU = ng.empty(layer.dimF)
+    ng.update_conv(layer, ng.array(I), ng.array(E), dU, alpha=0.5)
+    aU = _abs_terms(cd, I, F, E)[2]
+    M, P, Q = cd.MPQ
+    assert_close(dU.get(), ref["gradF"], f32_tol(aU, M * P * Q * cd.N) + 2.0 ** -11 * np.abs(ref["gradF"]), name + " fp16 dW")
+
+
 @pytest.mark.parametrize("name", sorted(SHARDED))
 def test_sharded_minibatch_shapes_run_on_the_tensor_core_path(ng, name):
     cfg = SHARDED[name]
