@@ -130,7 +130,7 @@ class ConvStack(object):
         self._comm_stream, self._comm_busy = None, False
         # Gradient buckets of the multi-GPU step, as ranges of the flat buffers: the upper layers
         # (most of the parameters) are summed over the GPUs as soon as the lowest of them has its
-        # gradient, while the layers below still compute; the small remainder goes last. Each
+        # gradient, while the layers below still compute; the small remainder follows. Each
         # bucket's SGD step runs on the communication stream right behind its sum.
         sizes = [l.sizeF for l in self.convs]
         split = 1
@@ -139,7 +139,10 @@ class ConvStack(object):
         self._conv_offsets = offsets
         self._flat_elems = total_f
         # (first conv index, one past the last conv index) per bucket, in the order they complete
-        self.comm_buckets = [(split, len(sizes)), (0, split)] if len(sizes) > 1 else [(0, 1)]
+        # (the layers below the big bucket go one by one: what is exposed at the end of the step
+        # is then the sum of the first layer's few weights only)
+        self.comm_buckets = [(split, len(sizes))] + [(i, i + 1) for i in range(split - 1, -1, -1)] \
+            if len(sizes) > 1 else [(0, 1)]
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)
