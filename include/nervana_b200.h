@@ -247,6 +247,21 @@ int ng_comm_allreduce_f32(void* comm, void* buf, size_t count, void* stream);
 int ng_comm_async_error(void* comm);
 int ng_comm_destroy(void* comm);
 
+/* Gradient sum over peer memory fused with the SGD step, for slices of at most ng_peer_max_bytes():
+ * grad[i] = sum over the GPUs of grad[i] (in rank order, the same bits everywhere), then, when
+ * weights_f16 is not null, w[i] = RN16(w[i] + lr * grad[i]). One process per GPU on one NVLink box:
+ * ng_peer_create allocates this GPU's staging buffer and returns its CUDA IPC handle
+ * (ng_peer_handle_bytes() bytes), the host exchanges the handles of all ranks (in rank order) and passes
+ * them to ng_peer_connect; every rank then calls ng_peer_sum_sgd_f32 with the same counts in the same order.
+ * Waits on peers are bounded (ng_set_wait_limit_ns); a rank that gives up reports through ng_device_status.
+ * Cites no reference interface: the reference is single-GPU (nervanagpu/nervanagpu.py:491). */
+int ng_peer_handle_bytes(void);
+size_t ng_peer_max_bytes(void);
+int ng_peer_create(void** group, int nranks, int rank, void* handle_out);
+int ng_peer_connect(void* group, const void* handles);
+int ng_peer_sum_sgd_f32(void* group, void* grad, void* weights_f16, size_t count, float lr, void* stream);
+int ng_peer_destroy(void* group);
+
 /* ---- the reference's own C interface ---------------------------------------------------------
  * Same names and signatures as nervanagpu/kernels/C_interface/nervana_c_api.h:31-128 (bool
  * result, message on stderr). CUstream is passed as void* here; the ABI is identical.

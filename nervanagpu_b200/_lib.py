@@ -115,6 +115,12 @@ SIGNATURES = {
     "ng_comm_allreduce_f32": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
     "ng_comm_async_error": (c_int, [c_void_p]),
     "ng_comm_destroy": (c_int, [c_void_p]),
+    "ng_peer_handle_bytes": (c_int, []),
+    "ng_peer_max_bytes": (c_size_t, []),
+    "ng_peer_create": (c_int, [ctypes.POINTER(c_void_p), c_int, c_int, c_void_p]),
+    "ng_peer_connect": (c_int, [c_void_p, c_void_p]),
+    "ng_peer_sum_sgd_f32": (c_int, [c_void_p, c_void_p, c_void_p, c_size_t, c_float, c_void_p]),
+    "ng_peer_destroy": (c_int, [c_void_p]),
     # the reference's own C interface (bool results)
     "nervana_loadKernels": (ctypes.c_bool, [c_char_p]),
     "nervana_unloadKernels": (ctypes.c_bool, []),

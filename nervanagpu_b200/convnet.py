@@ -70,6 +70,10 @@ class ConvStack(object):
             N = net["N"] // shard[1]
         self.N = N = net["N"] if N is None else N
         self.comm = comm                      # ng_comm handle or None (single GPU)
+        # ng_peer group (gradient sums over peer memory, fused with the SGD step) or None: used for
+        # the small, late buckets, whose cost is latency; the big first bucket stays with NCCL
+        self.peer = None
+        self.peer_max_bytes = 0
         self.lr = learning_rate
         rng = np.random.default_rng(seed)
         C, H, W = net["C"], net["H"], net["W"]
@@ -237,6 +241,13 @@ class ConvStack(object):
         _lib.check(lib.ng_event_record(self._comm_ev, after_stream))      # the bucket's last update
         _lib.check(lib.ng_event_record(self._w_free, ng.stream))          # its last reader of the weights
         _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._comm_ev))
+        if self.peer is not None and g.nbytes <= self.peer_max_bytes:
+            # one kernel per GPU: copy to the staging buffer the peers have mapped, sum their copies
+            # in rank order, apply the step (the weights must be free first)
+            _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._w_free))
+            _lib.check(lib.ng_peer_sum_sgd_f32(self.peer, g.ptr, w.ptr, g.size, self.lr, self._comm_stream))
+            self._comm_busy = True
+            return
         _lib.check(lib.ng_comm_allreduce_f32(self.comm, g.ptr, g.size, self._comm_stream))
         _lib.check(lib.ng_stream_wait_event(self._comm_stream, self._w_free))
         main, ng.stream = ng.stream, self._comm_stream

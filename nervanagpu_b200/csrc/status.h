@@ -17,3 +17,4 @@
 #define NG_DEV_TIMEOUT_EPILOGUE 103
 #define NG_DEV_TIMEOUT_ACC 104
 #define NG_DEV_TIMEOUT_TEST 105
+#define NG_DEV_TIMEOUT_PEER 106   /* a peer GPU's flag in the peer-memory gradient sum */
