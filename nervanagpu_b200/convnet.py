@@ -55,6 +55,21 @@ def bucket_layout(sizes, align=8):
     return offsets, total
 
 
+def comm_bucket_order(sizes):
+    """Gradient buckets of the multi-GPU step as (first layer, one past the last layer), in the
+    order in which the backward pass completes them: the upper layers, which hold most of the
+    parameters (everything above the lowest layers that together hold at most 15 %), form one
+    bucket; the layers below it go one by one, so that what is exposed at the end of the step is
+    the sum of the first layer's few weights only."""
+    n = len(sizes)
+    if n <= 1:
+        return [(0, n)] if n else []
+    split = 1
+    while split + 1 < n and sum(sizes[:split + 1]) <= 0.15 * sum(sizes):
+        split += 1
+    return [(split, n)] + [(i, i + 1) for i in range(split - 1, -1, -1)]
+
+
 class ConvStack(object):
     """A chain of ConvLayer / PoolLayer objects with their activations, deltas and weights."""
 
@@ -136,17 +151,9 @@ class ConvStack(object):
         # (most of the parameters) are summed over the GPUs as soon as the lowest of them has its
         # gradient, while the layers below still compute; the small remainder follows. Each
         # bucket's SGD step runs on the communication stream right behind its sum.
-        sizes = [l.sizeF for l in self.convs]
-        split = 1
-        while split + 1 < len(sizes) and sum(sizes[:split + 1]) <= 0.15 * sum(sizes):
-            split += 1
         self._conv_offsets = offsets
         self._flat_elems = total_f
-        # (first conv index, one past the last conv index) per bucket, in the order they complete
-        # (the layers below the big bucket go one by one: what is exposed at the end of the step
-        # is then the sum of the first layer's few weights only)
-        self.comm_buckets = [(split, len(sizes))] + [(i, i + 1) for i in range(split - 1, -1, -1)] \
-            if len(sizes) > 1 else [(0, 1)]
+        self.comm_buckets = comm_bucket_order([l.sizeF for l in self.convs])
 
         # work per step on this GPU: fprop + update for every conv, bprop for all but the first
         self.flops_fprop = sum(l.flops for l in self.convs)

@@ -92,3 +92,17 @@ def test_shard_and_bucket_helpers():
         shard_minibatch(x, 0, 3)
     offsets, total = bucket_layout([23232, 5, 8])
     assert offsets == [0, 23232, 23240] and total == 23248
+
+
+def test_gradient_buckets_cover_every_layer_once_in_completion_order():
+    from nervanagpu_b200.convnet import comm_bucket_order
+    alexnet = [23232, 307200, 663552, 884736, 589824]
+    vgg_a = [1728, 73728, 294912, 589824, 1179648, 2359296, 2359296, 2359296]
+    for sizes, want in ((alexnet, [(2, 5), (1, 2), (0, 1)]),
+                        (vgg_a, [(4, 8), (3, 4), (2, 3), (1, 2), (0, 1)]),
+                        ([7], [(0, 1)]), ([5, 5], [(1, 2), (0, 1)])):
+        got = comm_bucket_order(sizes)
+        assert got == want
+        covered = sorted(i for first, last in got for i in range(first, last))
+        assert covered == list(range(len(sizes)))
+        assert [b[0] for b in got] == sorted((b[0] for b in got), reverse=True)   # top of the stack first
