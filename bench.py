@@ -627,7 +627,11 @@ def main():
                 stack._recorded = None
         if with_replay:
             fn = stack.step_prefetched            # nothing prefetched yet: replays on the resident input
-            fn()
+            # the replayed form gets its warm-up too: the first replays of a recording upload it and,
+            # with several GPUs, let NCCL finish setting up its recorded collectives
+            for _ in range(max(args.warmup, 3)):
+                fn()
+            ng.synchronize()
         return fn, with_replay
 
     def timed_steps(fn):
