@@ -588,6 +588,9 @@ def main():
         stack = ConvStack(ng, net, seed=1003, comm=comm, shard=(rank, world))
     else:
         stack = ConvStack(ng, net, seed=1003, data_seed=2003 + rank, comm=comm)
+    if os.environ.get("NG_BUCKET_FRACTION"):     # measurement aid: where the first gradient bucket ends
+        from nervanagpu_b200.convnet import comm_bucket_order
+        stack.comm_buckets = comm_bucket_order([l.sizeF for l in stack.convs], float(os.environ["NG_BUCKET_FRACTION"]))
     stack.peer = make_peer(lib, ranks)
     stack.peer_max_bytes = lib.ng_peer_max_bytes() if stack.peer is not None else 0
     timer = StepTimer(ng)

@@ -55,17 +55,17 @@ def bucket_layout(sizes, align=8):
     return offsets, total
 
 
-def comm_bucket_order(sizes):
+def comm_bucket_order(sizes, small_fraction=0.15):
     """Gradient buckets of the multi-GPU step as (first layer, one past the last layer), in the
     order in which the backward pass completes them: the upper layers, which hold most of the
-    parameters (everything above the lowest layers that together hold at most 15 %), form one
+    parameters (everything above the lowest layers that together hold at most `small_fraction`), form one
     bucket; the layers below it go one by one, so that what is exposed at the end of the step is
     the sum of the first layer's few weights only."""
     n = len(sizes)
     if n <= 1:
         return [(0, n)] if n else []
     split = 1
-    while split + 1 < n and sum(sizes[:split + 1]) <= 0.15 * sum(sizes):
+    while split + 1 < n and sum(sizes[:split + 1]) <= small_fraction * sum(sizes):
         split += 1
     return [(split, n)] + [(i, i + 1) for i in range(split - 1, -1, -1)]
 
